@@ -1,0 +1,233 @@
+"""ctypes binding of the C ABI declared in include/asp_b200.h.
+
+The library must have been built (`python -c "import __graft_entry__ as g; g.build()"`);
+a missing library is an error, never a fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libasp_b200.so")
+
+ASP_MAX_BRANCH = 5
+U8, U16, U32, U64, F32, F64 = range(6)
+DTYPE_OF_NP = {np.dtype(np.uint8): U8, np.dtype(np.uint16): U16, np.dtype(np.uint32): U32, np.dtype(np.uint64): U64,
+               np.dtype(np.float32): F32, np.dtype(np.float64): F64}
+NP_OF_NAME = {"u8": np.uint8, "u16": np.uint16, "u32": np.uint32, "u64": np.uint64, "f32": np.float32, "f64": np.float64}
+COMPRESS = {"none": 0, "linear": 1, "constant": 2, "branch": 3, "cycle_linear": 4, "cycle_increase": 5}
+TEMPLATE = {"K1": 0, "K2": 1, "K3": 2, "K5": 3, "K6": 4, "K7": 5, "K8": 6, "K4": 7, "K9": 8, "K10": 9, "EMPTY": 10}
+TEMPLATE_NAME = {
+    0: "DIRECT_ATOM_TEMPLATE", 1: "DIRECT_ATOM_TEMPLATE_WARP_COMPRESS", 2: "DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS",
+    3: "SHARED_MEMORY_TEMPLATE", 4: "SHARED_MEMORY_TEMPLATE_WARP_COMPRESS", 5: "SHARED_MEMORY_LONG_ROW_TEMPLATE",
+    6: "SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE", 7: "DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE",
+    8: "UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE", 9: "UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE",
+    10: "EMPTY_TEMPLATE",
+}
+ROLE = {
+    "val_arr": 0, "col_index_arr": 1, "row_index_before_sort": 2, "global_row_index_of_thread_level_block": 3,
+    "block_begin_warp_index_offset": 4, "warp_begin_thread_index_offset": 5, "thread_block_size_in_warp": 6,
+    "block_nz_begin_offset": 7, "warp_nz_begin_offset": 8, "block_begin_thread_index_offset": 9,
+    "thread_block_size_in_block": 10, "global_row_index_of_warp_level_block": 11, "global_warp_nz_begin_offset": 12,
+    "row_offset_in_thread_tmp_result": 13, "block_first_row_index": 14, "row_index_of_block_level_block": 15,
+    "row_offset_in_warp_tmp_result": 16, "global_warp_block_first_nz": 17,
+    "global_first_row_index_of_warp_level_block": 18, "combine_meta_of_thread_level_block": 19,
+}
+SORT_NONE, SORT_GLOBAL, SORT_LOCAL = 0, 1, 2
+
+
+class ArrayDesc(C.Structure):
+    _fields_ = [("role", C.c_int32), ("dtype", C.c_int32), ("host_ptr", C.c_void_p), ("len", C.c_uint64),
+                ("compress", C.c_int32), ("n_branch", C.c_int32), ("coef", C.c_uint64), ("icpt", C.c_uint64),
+                ("cycle", C.c_uint64), ("branch_lo", C.c_uint64 * ASP_MAX_BRANCH), ("branch_hi", C.c_uint64 * ASP_MAX_BRANCH),
+                ("branch_val", C.c_uint64 * ASP_MAX_BRANCH)]
+
+
+class PlanDesc(C.Structure):
+    _fields_ = [("template_type", C.c_int32), ("val_dtype", C.c_int32), ("n_rows", C.c_uint64), ("n_cols", C.c_uint64),
+                ("first_row", C.c_uint64), ("first_col", C.c_uint64), ("true_nnz", C.c_uint64), ("n_arrays", C.c_int32),
+                ("arrays", C.POINTER(ArrayDesc)), ("effective_num", C.c_uint64), ("tlb_size", C.c_uint64),
+                ("bits_word", C.c_int32), ("bits_flag", C.c_int32), ("bits_row", C.c_int32), ("bits_off", C.c_int32),
+                ("is_atom_add", C.c_int32), ("sort_kind", C.c_int32), ("tblock_num", C.c_int64),
+                ("thread_num_in_block", C.c_int64), ("thread_num_of_row_reduce", C.c_int64)]
+
+
+EXPORTS = [
+    "asp_ctx_create", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_destroy",
+    "asp_plan_set_launch", "asp_plan_format_bytes", "asp_plan_launches", "asp_spmv", "asp_spmv_host", "asp_time",
+    "asp_synchronize", "asp_status_str", "asp_last_error", "asp_built_for_sm100a",
+]
+
+_lib = None
+
+
+class AspError(RuntimeError):
+    def __init__(self, status: int, msg: str):
+        super().__init__(f"asp status {status}: {msg}")
+        self.status = status
+
+
+def lib() -> C.CDLL:
+    """Load libasp_b200.so (once). Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FileNotFoundError(f"{LIB_PATH} is missing: build the CUDA library first (__graft_entry__.build()); there is no CPU fallback")
+    L = C.CDLL(LIB_PATH)
+    L.asp_ctx_create.argtypes = [C.c_int, C.POINTER(C.c_void_p)]
+    L.asp_ctx_create.restype = C.c_int
+    L.asp_ctx_destroy.argtypes = [C.c_void_p]
+    L.asp_ctx_destroy.restype = None
+    L.asp_ctx_stream.argtypes = [C.c_void_p]
+    L.asp_ctx_stream.restype = C.c_void_p
+    L.asp_plan_group_create.argtypes = [C.c_void_p, C.POINTER(PlanDesc), C.c_int, C.POINTER(C.c_void_p)]
+    L.asp_plan_group_create.restype = C.c_int
+    L.asp_plan_destroy.argtypes = [C.c_void_p]
+    L.asp_plan_destroy.restype = None
+    L.asp_plan_set_launch.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int64]
+    L.asp_plan_set_launch.restype = C.c_int
+    L.asp_plan_format_bytes.argtypes = [C.c_void_p]
+    L.asp_plan_format_bytes.restype = C.c_uint64
+    L.asp_plan_launches.argtypes = [C.c_void_p]
+    L.asp_plan_launches.restype = C.c_int
+    L.asp_spmv.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p, C.c_int]
+    L.asp_spmv.restype = C.c_int
+    L.asp_spmv_host.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p]
+    L.asp_spmv_host.restype = C.c_int
+    L.asp_time.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_double,
+                           C.POINTER(C.c_float), C.POINTER(C.c_float)]
+    L.asp_time.restype = C.c_int
+    L.asp_synchronize.argtypes = [C.c_void_p]
+    L.asp_synchronize.restype = C.c_int
+    L.asp_status_str.argtypes = [C.c_int]
+    L.asp_status_str.restype = C.c_char_p
+    L.asp_last_error.argtypes = []
+    L.asp_last_error.restype = C.c_char_p
+    L.asp_built_for_sm100a.argtypes = []
+    L.asp_built_for_sm100a.restype = C.c_int
+    _lib = L
+    return L
+
+
+def check(status: int) -> None:
+    if status != 0:
+        L = lib()
+        raise AspError(status, f"{L.asp_status_str(status).decode()}: {L.asp_last_error().decode()}")
+
+
+class Context:
+    """One per GPU: stream, events, scratch x / y (asp_ctx)."""
+
+    def __init__(self, device: int = 0):
+        self._h = C.c_void_p()
+        check(lib().asp_ctx_create(device, C.byref(self._h)))
+        self.device = device
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def stream(self) -> int:
+        return lib().asp_ctx_stream(self._h) or 0
+
+    def synchronize(self):
+        check(lib().asp_synchronize(self._h))
+
+    def close(self):
+        if self._h:
+            lib().asp_ctx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def make_array_desc(name: str, arr, compress: dict | None, length: int | None = None, dtype: int | None = None) -> ArrayDesc:
+    """Describe one template array. `arr` may be None for a closed form."""
+    d = ArrayDesc()
+    d.role = ROLE[name]
+    if arr is not None:
+        assert arr.flags["C_CONTIGUOUS"]
+        d.dtype = DTYPE_OF_NP[arr.dtype]
+        d.host_ptr = arr.ctypes.data
+        d.len = arr.shape[0] if length is None else length
+    else:
+        d.dtype = U32 if dtype is None else dtype
+        d.host_ptr = None
+        d.len = length or 0
+    c = compress or {"kind": "none"}
+    d.compress = COMPRESS[c["kind"]]
+    d.coef = int(c.get("coef", 0))
+    d.icpt = int(c.get("icpt", 0))
+    d.cycle = int(c.get("cycle", 0))
+    if c["kind"] == "branch":
+        d.n_branch = len(c["val"])
+        for i in range(d.n_branch):
+            d.branch_lo[i] = int(c["lo"][i])
+            d.branch_hi[i] = int(c["hi"][i])
+            d.branch_val[i] = int(c["val"][i])
+    return d
+
+
+class PlanGroup:
+    """All sub-matrix plans of one matrix (asp_plan_group_create). Keeps the host arrays alive
+    until upload has finished."""
+
+    def __init__(self, ctx: Context, descs: list[PlanDesc], keepalive=None):
+        self.ctx = ctx
+        n = len(descs)
+        self._descs = (PlanDesc * n)(*descs)
+        self._plans = (C.c_void_p * n)()
+        self._keep = keepalive
+        check(lib().asp_plan_group_create(ctx.handle, self._descs, n, self._plans))
+        self.n = n
+        self.val_dtype = np.float64 if descs[0].val_dtype == F64 else np.float32
+        self.n_rows = int(descs[0].n_rows)
+        self.n_cols = int(descs[0].n_cols)
+        self._keep = None
+
+    def set_launch(self, i: int, tblock: int, threads: int, reduce: int = 1):
+        check(lib().asp_plan_set_launch(self._plans[i], tblock, threads, reduce))
+
+    def format_bytes(self) -> int:
+        return sum(lib().asp_plan_format_bytes(self._plans[i]) for i in range(self.n))
+
+    def launches(self) -> int:
+        return sum(lib().asp_plan_launches(self._plans[i]) for i in range(self.n))
+
+    def spmv(self, d_x: int, d_y: int, zero_y: bool = True):
+        """Asynchronous y (+)= A x on device pointers (ints)."""
+        check(lib().asp_spmv(self.ctx.handle, self._plans, self.n, C.c_void_p(d_x), C.c_void_p(d_y), 1 if zero_y else 0))
+
+    def spmv_host(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=self.val_dtype)
+        assert x.shape[0] == self.n_cols
+        y = np.empty(self.n_rows, dtype=self.val_dtype)
+        check(lib().asp_spmv_host(self.ctx.handle, self._plans, self.n, C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data)))
+        return y
+
+    def time(self, warmup: int = 3, reps: int = 20, zero_y: bool = True, gflops_up_bound: float = 0.0):
+        ms = C.c_float()
+        gf = C.c_float()
+        check(lib().asp_time(self.ctx.handle, self._plans, self.n, warmup, reps, 1 if zero_y else 0, gflops_up_bound, C.byref(ms), C.byref(gf)))
+        return ms.value, gf.value
+
+    def close(self):
+        for i in range(self.n):
+            if self._plans[i]:
+                lib().asp_plan_destroy(self._plans[i])
+                self._plans[i] = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

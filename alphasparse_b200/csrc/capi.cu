@@ -1,0 +1,750 @@
+// C ABI over the kernel families: context, plan upload / validation, launch, timing.
+// Replaces the reference's "emit source -> nvcc -> a.out -> parse perf_result" executor
+// (executor.cc:6-260) and the generated main() (code_builder.cc:1471-1575).
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <map>
+#include <memory>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/asp_b200.h"
+#include "kernel_args.h"
+#include "kernels.h"
+
+namespace
+{
+thread_local std::string g_last_error;
+
+asp_status cuda_fail(cudaError_t e, const char *what)
+{
+    g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+    return ASP_ERR_CUDA;
+}
+asp_status fail(asp_status s, const std::string &msg)
+{
+    g_last_error = msg;
+    return s;
+}
+#define ASP_CUDA(call)                                      \
+    do                                                      \
+    {                                                       \
+        cudaError_t e__ = (call);                           \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+    } while (0)
+
+int dtype_size(int dt)
+{
+    switch (dt)
+    {
+    case ASP_U8: return 1;
+    case ASP_U16: return 2;
+    case ASP_U32: case ASP_F32: return 4;
+    case ASP_U64: case ASP_F64: return 8;
+    default: return 0;
+    }
+}
+
+// device memory shared by the plans of one group (one cudaMalloc per matrix)
+struct Arena
+{
+    void *base = nullptr;
+    size_t bytes = 0;
+    int device = 0;
+    ~Arena()
+    {
+        if (base) cudaFree(base);
+    }
+};
+
+// host copy of a metadata reference, for validation and shared-memory sizing
+struct HostMeta
+{
+    const void *p = nullptr;
+    int dtype = ASP_U32;
+    uint64_t len = 0;
+    int kind = ASP_COMPRESS_NONE;
+    uint64_t coef = 0, icpt = 0, cycle = 1;
+    int nb = 0;
+    uint64_t bhi[5] = {0, 0, 0, 0, 0}, bval[5] = {0, 0, 0, 0, 0};
+    bool present = false;
+    uint64_t get(uint64_t i) const
+    {
+        switch (kind)
+        {
+        case ASP_COMPRESS_NONE:
+            switch (dtype)
+            {
+            case ASP_U8: return ((const uint8_t *)p)[i];
+            case ASP_U16: return ((const uint16_t *)p)[i];
+            case ASP_U32: return ((const uint32_t *)p)[i];
+            default: return ((const uint64_t *)p)[i];
+            }
+        case ASP_COMPRESS_LINEAR: return i * coef + icpt;
+        case ASP_COMPRESS_CONSTANT: return icpt;
+        case ASP_COMPRESS_CYCLE_LINEAR: return (i % cycle) * coef + icpt;
+        case ASP_COMPRESS_CYCLE_INCREASE: return i / cycle + icpt;
+        default:
+        {
+            uint64_t v = bval[0];
+            for (int b = 1; b < nb; b++)
+                if (i > bhi[b - 1]) v = bval[b];
+            return v;
+        }
+        }
+    }
+};
+} // namespace
+
+struct asp_ctx
+{
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    int sm_count = 0;
+    int max_smem_optin = 0;
+    // scratch x / y used by asp_time and asp_spmv_host; grown on demand
+    void *x = nullptr, *y = nullptr;
+    size_t x_bytes = 0, y_bytes = 0;
+};
+
+struct asp_plan
+{
+    std::shared_ptr<Arena> arena;
+    asp::KArgs args;
+    int templ = 0;
+    int val_is_f64 = 0;
+    int col_width = 4;
+    uint64_t n_rows = 0, n_cols = 0, true_nnz = 0;
+    unsigned grid = 1, block = 32;
+    size_t smem = 0;
+    int vec = 1;
+    uint64_t fmt_bytes = 0;
+    uint64_t smem_elems = 0; // partial results per CTA (shared-memory family)
+    uint64_t units_for_grid = 0;
+    bool needs_zero = false;
+};
+
+namespace
+{
+int slot_of_role(int templ, int role)
+{
+    using namespace asp;
+    switch (role)
+    {
+    case ASP_ARR_GLOBAL_ROW_INDEX_OF_THREAD_LEVEL_BLOCK: return MS_ROW_OF_TLB;
+    case ASP_ARR_BLOCK_BEGIN_THREAD_INDEX_OFFSET: return MS_BLK_THR;
+    case ASP_ARR_BLOCK_NZ_BEGIN_OFFSET: return MS_BLK_NZ;
+    case ASP_ARR_THREAD_BLOCK_SIZE_IN_BLOCK:
+    case ASP_ARR_THREAD_BLOCK_SIZE_IN_WARP: return MS_TLB_SIZE;
+    case ASP_ARR_BLOCK_BEGIN_WARP_INDEX_OFFSET: return MS_BLK_WARP;
+    case ASP_ARR_WARP_BEGIN_THREAD_INDEX_OFFSET: return MS_WARP_THR;
+    case ASP_ARR_WARP_NZ_BEGIN_OFFSET:
+    case ASP_ARR_GLOBAL_WARP_NZ_BEGIN_OFFSET:
+    case ASP_ARR_GLOBAL_WARP_BLOCK_FIRST_NZ: return MS_WARP_NZ;
+    case ASP_ARR_ROW_OFFSET_IN_THREAD_TMP_RESULT:
+    case ASP_ARR_ROW_OFFSET_IN_WARP_TMP_RESULT: return MS_ROW_OFF;
+    case ASP_ARR_BLOCK_FIRST_ROW_INDEX: return MS_BLK_ROW;
+    case ASP_ARR_GLOBAL_ROW_INDEX_OF_WARP_LEVEL_BLOCK:
+    case ASP_ARR_ROW_INDEX_OF_BLOCK_LEVEL_BLOCK:
+    case ASP_ARR_GLOBAL_FIRST_ROW_INDEX_OF_WARP_LEVEL_BLOCK: return MS_ROW_OF_UNIT;
+    case ASP_ARR_COMBINE_META_OF_THREAD_LEVEL_BLOCK: return MS_COMBINE;
+    default: return -1;
+    }
+}
+
+// which metadata slots each template must provide
+std::vector<int> required_slots(int templ)
+{
+    using namespace asp;
+    switch (templ)
+    {
+    case ASP_DIRECT_ATOM_TEMPLATE: return {MS_ROW_OF_TLB, MS_BLK_WARP, MS_WARP_THR, MS_TLB_SIZE, MS_BLK_NZ, MS_WARP_NZ};
+    case ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS: return {MS_ROW_OF_TLB, MS_BLK_THR, MS_BLK_NZ, MS_TLB_SIZE};
+    case ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS: return {MS_ROW_OF_TLB};
+    case ASP_SHARED_MEMORY_TEMPLATE: return {MS_ROW_OFF, MS_BLK_ROW, MS_BLK_WARP, MS_WARP_THR, MS_TLB_SIZE, MS_BLK_NZ, MS_WARP_NZ};
+    case ASP_SHARED_MEMORY_TEMPLATE_WARP_COMPRESS: return {MS_ROW_OFF, MS_BLK_ROW, MS_BLK_THR, MS_TLB_SIZE, MS_BLK_NZ};
+    case ASP_SHARED_MEMORY_LONG_ROW_TEMPLATE: return {MS_ROW_OF_UNIT, MS_BLK_NZ};
+    case ASP_SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE: return {MS_ROW_OFF, MS_BLK_ROW, MS_BLK_WARP, MS_WARP_NZ};
+    case ASP_DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE: return {MS_ROW_OF_UNIT, MS_WARP_NZ};
+    case ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE:
+    case ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE: return {MS_ROW_OF_UNIT, MS_COMBINE};
+    default: return {};
+    }
+}
+
+bool is_smem_family(int t)
+{
+    return t == ASP_SHARED_MEMORY_TEMPLATE || t == ASP_SHARED_MEMORY_TEMPLATE_WARP_COMPRESS || t == ASP_SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE;
+}
+bool perm_on_device(int t)
+{
+    return is_smem_family(t) || t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE;
+}
+
+asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threads, int64_t reduce)
+{
+    if (threads <= 0 || threads > 1024) return fail(ASP_ERR_INVALID_ARG, "thread_num_in_block must be in 1..1024");
+    const int t = p->templ;
+    const bool warp_based = t != ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS && t != ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS;
+    if (warp_based && (threads % 32) != 0) return fail(ASP_ERR_INVALID_ARG, "thread_num_in_block must be a multiple of 32 for this template");
+    if (is_smem_family(t))
+    {
+        if (reduce <= 0) reduce = 1;
+        if (reduce > 32 || (reduce & (reduce - 1)) != 0) return fail(ASP_ERR_INVALID_ARG, "thread_num_of_row_reduce must be a power of two <= 32");
+        if ((threads % 32) != 0) return fail(ASP_ERR_INVALID_ARG, "thread_num_in_block must be a multiple of 32 for this template");
+        p->args.row_reduce = (int)reduce;
+    }
+    if (tblock <= 0) tblock = 1;
+    if (tblock > 2147483647LL) tblock = 2147483647LL;
+    p->grid = (unsigned)tblock;
+    p->block = (unsigned)threads;
+    return ASP_OK;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+asp_status ensure_xy(asp_ctx *ctx, size_t xb, size_t yb)
+{
+    if (ctx->x_bytes < xb)
+    {
+        if (ctx->x) cudaFree(ctx->x);
+        ctx->x = nullptr;
+        ctx->x_bytes = 0;
+        ASP_CUDA(cudaMalloc(&ctx->x, xb));
+        ctx->x_bytes = xb;
+    }
+    if (ctx->y_bytes < yb)
+    {
+        if (ctx->y) cudaFree(ctx->y);
+        ctx->y = nullptr;
+        ctx->y_bytes = 0;
+        ASP_CUDA(cudaMalloc(&ctx->y, yb));
+        ctx->y_bytes = yb;
+    }
+    return ASP_OK;
+}
+} // namespace
+
+extern "C" {
+
+const char *asp_status_str(asp_status s)
+{
+    switch (s)
+    {
+    case ASP_OK: return "ok";
+    case ASP_ERR_INVALID_ARG: return "invalid argument";
+    case ASP_ERR_UNSUPPORTED: return "unsupported";
+    case ASP_ERR_CUDA: return "CUDA error";
+    case ASP_ERR_ALLOC: return "allocation failed";
+    case ASP_ERR_BOUNDS: return "format array out of bounds";
+    case ASP_ERR_IMPLAUSIBLE: return "implausible throughput";
+    default: return "unknown";
+    }
+}
+
+const char *asp_last_error(void) { return g_last_error.c_str(); }
+
+int asp_built_for_sm100a(void)
+{
+#ifdef ASP_SM100A
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+asp_status asp_ctx_create(int device, asp_ctx **out)
+{
+    if (!out) return fail(ASP_ERR_INVALID_ARG, "out is NULL");
+    *out = nullptr;
+    int n = 0;
+    ASP_CUDA(cudaGetDeviceCount(&n));
+    if (device < 0 || device >= n) return fail(ASP_ERR_INVALID_ARG, "no such CUDA device");
+    ASP_CUDA(cudaSetDevice(device));
+    asp_ctx *c = new (std::nothrow) asp_ctx();
+    if (!c) return fail(ASP_ERR_ALLOC, "host allocation failed");
+    c->device = device;
+    cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreate(&c->ev0);
+    if (e == cudaSuccess) e = cudaEventCreate(&c->ev1);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    if (e != cudaSuccess)
+    {
+        asp_ctx_destroy(c);
+        return cuda_fail(e, "context setup");
+    }
+    *out = c;
+    return ASP_OK;
+}
+
+void asp_ctx_destroy(asp_ctx *c)
+{
+    if (!c) return;
+    cudaSetDevice(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    if (c->x) cudaFree(c->x);
+    if (c->y) cudaFree(c->y);
+    if (c->ev0) cudaEventDestroy(c->ev0);
+    if (c->ev1) cudaEventDestroy(c->ev1);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+void *asp_ctx_stream(asp_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
+
+asp_status asp_synchronize(asp_ctx *ctx)
+{
+    if (!ctx) return fail(ASP_ERR_INVALID_ARG, "ctx is NULL");
+    ASP_CUDA(cudaStreamSynchronize(ctx->stream));
+    return ASP_OK;
+}
+
+asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp_plan **out_plans)
+{
+    if (!ctx || !descs || !out_plans || n <= 0) return fail(ASP_ERR_INVALID_ARG, "NULL argument or n <= 0");
+    for (int i = 0; i < n; i++) out_plans[i] = nullptr;
+    ASP_CUDA(cudaSetDevice(ctx->device));
+
+    // ---- pass 1: validate descriptors, lay out the arena (arrays sharing a host pointer once)
+    struct Slot
+    {
+        size_t off, bytes;
+    };
+    std::map<const void *, Slot> placed;
+    size_t total = 0;
+    std::vector<std::vector<HostMeta>> metas(n, std::vector<HostMeta>(asp::MS_COUNT));
+    std::vector<HostMeta> perms(n);
+    std::vector<const asp_array_desc *> vals(n, nullptr), cols(n, nullptr);
+    for (int i = 0; i < n; i++)
+    {
+        const asp_plan_desc &d = descs[i];
+        if (d.template_type == ASP_EMPTY_TEMPLATE) continue;
+        if (d.template_type < 0 || d.template_type > ASP_EMPTY_TEMPLATE) return fail(ASP_ERR_INVALID_ARG, "unknown template_type");
+        if (d.val_dtype != ASP_F32 && d.val_dtype != ASP_F64) return fail(ASP_ERR_UNSUPPORTED, "val_dtype must be f32 or f64");
+        if (!d.arrays || d.n_arrays <= 0) return fail(ASP_ERR_INVALID_ARG, "plan without arrays");
+        if (d.first_row >= d.n_rows || d.first_col >= d.n_cols) return fail(ASP_ERR_BOUNDS, "first_row/first_col outside the matrix");
+        for (int k = 0; k < d.n_arrays; k++)
+        {
+            const asp_array_desc &ad = d.arrays[k];
+            if (ad.role < 0 || ad.role >= ASP_ARR_ROLE_COUNT) return fail(ASP_ERR_INVALID_ARG, "unknown array role");
+            const int es = dtype_size(ad.dtype);
+            if (es == 0) return fail(ASP_ERR_UNSUPPORTED, "unknown array dtype");
+            if (ad.compress < ASP_COMPRESS_NONE || ad.compress > ASP_COMPRESS_CYCLE_INCREASE) return fail(ASP_ERR_INVALID_ARG, "unknown compress kind");
+            if (ad.compress == ASP_COMPRESS_NONE && (!ad.host_ptr || ad.len == 0)) return fail(ASP_ERR_INVALID_ARG, "array without data");
+            if (ad.compress == ASP_COMPRESS_BRANCH && (ad.n_branch < 1 || ad.n_branch > ASP_MAX_BRANCH)) return fail(ASP_ERR_INVALID_ARG, "bad branch count");
+            if ((ad.compress == ASP_COMPRESS_CYCLE_LINEAR || ad.compress == ASP_COMPRESS_CYCLE_INCREASE) && ad.cycle == 0) return fail(ASP_ERR_INVALID_ARG, "cycle == 0");
+            if (ad.role == ASP_ARR_VAL)
+            {
+                if (ad.dtype != d.val_dtype) return fail(ASP_ERR_INVALID_ARG, "val_arr dtype differs from val_dtype");
+                vals[i] = &ad;
+            }
+            else if (ad.role == ASP_ARR_COL_INDEX)
+            {
+                if (ad.dtype != ASP_U8 && ad.dtype != ASP_U16 && ad.dtype != ASP_U32) return fail(ASP_ERR_UNSUPPORTED, "col_index_arr must be u8/u16/u32");
+                cols[i] = &ad;
+            }
+            else
+            {
+                if (ad.dtype == ASP_F32 || ad.dtype == ASP_F64) return fail(ASP_ERR_INVALID_ARG, "metadata array with float dtype");
+                HostMeta hm;
+                hm.p = ad.host_ptr;
+                hm.dtype = ad.dtype;
+                hm.len = ad.len;
+                hm.kind = ad.compress;
+                hm.coef = ad.coef;
+                hm.icpt = ad.icpt;
+                hm.cycle = ad.cycle ? ad.cycle : 1;
+                hm.nb = ad.n_branch;
+                for (int b = 0; b < ASP_MAX_BRANCH; b++)
+                {
+                    hm.bhi[b] = ad.branch_hi[b];
+                    hm.bval[b] = ad.branch_val[b];
+                }
+                hm.present = true;
+                if (ad.role == ASP_ARR_ROW_INDEX_BEFORE_SORT) perms[i] = hm;
+                else
+                {
+                    const int s = slot_of_role(d.template_type, ad.role);
+                    if (s < 0) return fail(ASP_ERR_INVALID_ARG, "array role not used by any template");
+                    metas[i][s] = hm;
+                }
+            }
+            if (ad.compress == ASP_COMPRESS_NONE && !placed.count(ad.host_ptr))
+            {
+                Slot s{total, (size_t)ad.len * es};
+                placed[ad.host_ptr] = s;
+                total = align_up(total + s.bytes + 32, 256); // 32 B of slack: vector loads may over-read masked tails
+            }
+        }
+        if (!vals[i] || !cols[i]) return fail(ASP_ERR_INVALID_ARG, "val_arr or col_index_arr missing");
+        if (vals[i]->len != cols[i]->len) return fail(ASP_ERR_INVALID_ARG, "val_arr and col_index_arr differ in length");
+        for (int s : required_slots(d.template_type))
+            if (!metas[i][s].present) return fail(ASP_ERR_INVALID_ARG, "a metadata array this template needs is missing");
+        if (perm_on_device(d.template_type) && d.sort_kind != ASP_SORT_NONE && !perms[i].present)
+            return fail(ASP_ERR_INVALID_ARG, "sorted plan without row_index_before_sort");
+    }
+
+    std::shared_ptr<Arena> arena(new (std::nothrow) Arena());
+    if (!arena) return fail(ASP_ERR_ALLOC, "host allocation failed");
+    arena->device = ctx->device;
+    arena->bytes = std::max<size_t>(total, 256);
+    {
+        cudaError_t e = cudaMalloc(&arena->base, arena->bytes);
+        if (e != cudaSuccess)
+        {
+            arena->base = nullptr;
+            cudaGetLastError();
+            return fail(ASP_ERR_ALLOC, std::string("cudaMalloc of the plan arena failed: ") + cudaGetErrorString(e));
+        }
+    }
+    for (auto &kv : placed)
+        ASP_CUDA(cudaMemcpyAsync((char *)arena->base + kv.second.off, kv.first, kv.second.bytes, cudaMemcpyHostToDevice, ctx->stream));
+
+    // ---- pass 2: build the kernel arguments
+    auto dev_meta = [&](const HostMeta &h) {
+        asp::Meta m;
+        memset(&m, 0, sizeof(m));
+        m.kind = h.kind;
+        m.width = dtype_size(h.dtype);
+        m.coef = h.coef;
+        m.icpt = h.icpt;
+        m.cycle = h.cycle;
+        m.nb = h.nb;
+        for (int b = 0; b < 5; b++)
+        {
+            m.bhi[b] = h.bhi[b];
+            m.bval[b] = h.bval[b];
+        }
+        m.p = (h.kind == ASP_COMPRESS_NONE && h.p) ? (const void *)((char *)arena->base + placed[h.p].off) : nullptr;
+        return m;
+    };
+
+    std::vector<asp_plan *> made;
+    auto cleanup = [&]() {
+        for (asp_plan *p : made) delete p;
+        for (int i = 0; i < n; i++) out_plans[i] = nullptr;
+    };
+    for (int i = 0; i < n; i++)
+    {
+        const asp_plan_desc &d = descs[i];
+        asp_plan *p = new (std::nothrow) asp_plan();
+        if (!p)
+        {
+            cleanup();
+            return fail(ASP_ERR_ALLOC, "host allocation failed");
+        }
+        made.push_back(p);
+        out_plans[i] = p;
+        p->arena = arena;
+        p->templ = d.template_type;
+        p->n_rows = d.n_rows;
+        p->n_cols = d.n_cols;
+        p->true_nnz = d.true_nnz;
+        memset(&p->args, 0, sizeof(p->args));
+        if (d.template_type == ASP_EMPTY_TEMPLATE) continue;
+        p->val_is_f64 = d.val_dtype == ASP_F64;
+        p->col_width = dtype_size(cols[i]->dtype);
+        asp::KArgs &a = p->args;
+        a.val = (char *)arena->base + placed[vals[i]->host_ptr].off;
+        a.col = (char *)arena->base + placed[cols[i]->host_ptr].off;
+        for (int s = 0; s < asp::MS_COUNT; s++)
+            if (metas[i][s].present) a.m[s] = dev_meta(metas[i][s]);
+        if (perms[i].present) a.perm = dev_meta(perms[i]);
+        a.first_row = d.first_row;
+        a.first_col = d.first_col;
+        a.tlb_size = (unsigned)d.tlb_size;
+        a.atomic = d.is_atom_add ? 1 : 0;
+        a.sort_kind = perm_on_device(d.template_type) ? d.sort_kind : 0;
+        a.row_add = (d.sort_kind == ASP_SORT_GLOBAL) ? 0 : 1;
+        a.row_reduce = 1;
+        a.bits_word = d.bits_word;
+        a.bits_flag = d.bits_flag;
+        a.bits_row = d.bits_row;
+        a.bits_off = d.bits_off;
+        const uint64_t nnz_pad = vals[i]->len;
+        const std::vector<HostMeta> &hm = metas[i];
+        uint64_t fmt = 0;
+        for (int k = 0; k < d.n_arrays; k++)
+            if (d.arrays[k].compress == ASP_COMPRESS_NONE) fmt += d.arrays[k].len * (uint64_t)dtype_size(d.arrays[k].dtype);
+        p->fmt_bytes = fmt;
+
+        std::string why;
+        asp_status st = ASP_OK;
+        switch (d.template_type)
+        {
+        case ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS:
+        {
+            const uint64_t P = hm[asp::MS_ROW_OF_TLB].len;
+            a.n_tlb = P;
+            a.n_units = P;
+            a.effective = d.effective_num ? std::min<uint64_t>(d.effective_num, P) : P;
+            if (d.tlb_size == 0 || P == 0 || P * d.tlb_size != nnz_pad) st = ASP_ERR_BOUNDS, why = "ELL-like: #TLB * TLB size != padded nnz";
+            // TLBs per thread: the widest group that keeps 16-byte alignment of every k-slice
+            int v = p->val_is_f64 ? 4 : 8;
+            while (v > 1 && (P % v) != 0) v >>= 1;
+            p->vec = v;
+            p->units_for_grid = (P + v - 1) / v;
+            break;
+        }
+        case ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS:
+        {
+            const uint64_t B = hm[asp::MS_BLK_NZ].len;
+            a.n_units = B;
+            const uint64_t T = hm[asp::MS_ROW_OF_TLB].len;
+            a.n_tlb = T;
+            a.effective = d.effective_num ? std::min<uint64_t>(d.effective_num, T) : T;
+            if (B == 0 || hm[asp::MS_BLK_THR].len != B + 1) st = ASP_ERR_BOUNDS, why = "SELL-like: block_begin_thread_index_offset must have #BLB + 1 entries";
+            else
+            {
+                for (uint64_t b = 0; b < B && st == ASP_OK; b++)
+                {
+                    const uint64_t t0 = hm[asp::MS_BLK_THR].get(b), t1 = hm[asp::MS_BLK_THR].get(b + 1);
+                    if (t1 < t0 || t1 > T || hm[asp::MS_BLK_NZ].get(b) + (t1 - t0) * hm[asp::MS_TLB_SIZE].get(b) > nnz_pad) st = ASP_ERR_BOUNDS, why = "SELL-like: a BLB reaches outside val_arr";
+                }
+            }
+            p->vec = p->val_is_f64 ? 2 : 4;
+            p->units_for_grid = B;
+            break;
+        }
+        case ASP_DIRECT_ATOM_TEMPLATE:
+        case ASP_SHARED_MEMORY_TEMPLATE:
+        {
+            const uint64_t B = hm[asp::MS_BLK_NZ].len;
+            a.n_units = B;
+            a.n_tlb = hm[asp::MS_WARP_THR].len ? hm[asp::MS_WARP_THR].get(hm[asp::MS_WARP_THR].len - 1) : 0;
+            a.effective = d.effective_num ? d.effective_num : ~0ull;
+            if (B == 0 || hm[asp::MS_BLK_WARP].len != B + 1) st = ASP_ERR_BOUNDS, why = "3-level: block_begin_warp_index_offset must have #BLB + 1 entries";
+            else
+            {
+                const uint64_t W = hm[asp::MS_WARP_NZ].len;
+                uint64_t mx = 0;
+                for (uint64_t b = 0; b < B && st == ASP_OK; b++)
+                {
+                    const uint64_t w0 = hm[asp::MS_BLK_WARP].get(b), w1 = hm[asp::MS_BLK_WARP].get(b + 1);
+                    if (w1 < w0 || w1 > W || w1 + 1 > hm[asp::MS_WARP_THR].len) { st = ASP_ERR_BOUNDS; why = "3-level: WLB range outside the WLB arrays"; break; }
+                    mx = std::max(mx, hm[asp::MS_WARP_THR].get(w1) - hm[asp::MS_WARP_THR].get(w0));
+                }
+                p->smem_elems = mx;
+            }
+            p->units_for_grid = B;
+            break;
+        }
+        case ASP_SHARED_MEMORY_TEMPLATE_WARP_COMPRESS:
+        {
+            const uint64_t B = hm[asp::MS_BLK_NZ].len;
+            a.n_units = B;
+            a.effective = d.effective_num ? d.effective_num : ~0ull;
+            if (B == 0 || hm[asp::MS_BLK_THR].len != B + 1 || hm[asp::MS_BLK_ROW].len != B + 1) st = ASP_ERR_BOUNDS, why = "row-grouped: offset arrays must have #BLB + 1 entries";
+            else
+            {
+                uint64_t mx = 0;
+                for (uint64_t b = 0; b < B && st == ASP_OK; b++)
+                {
+                    const uint64_t t0 = hm[asp::MS_BLK_THR].get(b), t1 = hm[asp::MS_BLK_THR].get(b + 1);
+                    if (t1 < t0 || hm[asp::MS_BLK_NZ].get(b) + (t1 - t0) * hm[asp::MS_TLB_SIZE].get(b) > nnz_pad) { st = ASP_ERR_BOUNDS; why = "row-grouped: a BLB reaches outside val_arr"; break; }
+                    mx = std::max(mx, t1 - t0);
+                }
+                p->smem_elems = mx;
+                if (hm[asp::MS_BLK_ROW].get(B) + 1 > hm[asp::MS_ROW_OFF].len) st = ASP_ERR_BOUNDS, why = "row-grouped: row offsets shorter than the row count";
+            }
+            p->units_for_grid = B;
+            break;
+        }
+        case ASP_SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE:
+        {
+            const uint64_t B = hm[asp::MS_BLK_ROW].len ? hm[asp::MS_BLK_ROW].len - 1 : 0;
+            a.n_units = B;
+            a.effective = d.effective_num ? d.effective_num : ~0ull;
+            if (B == 0 || hm[asp::MS_BLK_WARP].len != B + 1) st = ASP_ERR_BOUNDS, why = "warp-reduce smem: offset arrays must have #BLB + 1 entries";
+            else
+            {
+                uint64_t mx = 0;
+                const uint64_t W1 = hm[asp::MS_WARP_NZ].len;
+                for (uint64_t b = 0; b < B; b++)
+                {
+                    const uint64_t w0 = hm[asp::MS_BLK_WARP].get(b), w1 = hm[asp::MS_BLK_WARP].get(b + 1);
+                    if (w1 < w0 || w1 + 1 > W1) { st = ASP_ERR_BOUNDS; why = "warp-reduce smem: WLB range outside global_warp_block_first_nz"; break; }
+                    mx = std::max(mx, w1 - w0);
+                }
+                p->smem_elems = mx;
+                if (st == ASP_OK && hm[asp::MS_WARP_NZ].get(W1 - 1) > nnz_pad) st = ASP_ERR_BOUNDS, why = "warp-reduce smem: last nz offset outside val_arr";
+            }
+            p->units_for_grid = B;
+            break;
+        }
+        case ASP_SHARED_MEMORY_LONG_ROW_TEMPLATE:
+        {
+            const uint64_t B = hm[asp::MS_ROW_OF_UNIT].len;
+            a.n_units = B;
+            if (B == 0 || hm[asp::MS_BLK_NZ].len != B + 1) st = ASP_ERR_BOUNDS, why = "long-row: block_nz_begin_offset must have #BLB + 1 entries";
+            else if (hm[asp::MS_BLK_NZ].get(B) > nnz_pad) st = ASP_ERR_BOUNDS, why = "long-row: last nz offset outside val_arr";
+            p->units_for_grid = B;
+            break;
+        }
+        case ASP_DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE:
+        {
+            const uint64_t W = hm[asp::MS_ROW_OF_UNIT].len;
+            a.n_units = W;
+            a.effective = d.effective_num ? std::min<uint64_t>(d.effective_num, W) : W;
+            if (W == 0 || hm[asp::MS_WARP_NZ].len != W + 1) st = ASP_ERR_BOUNDS, why = "warp-per-row: global_warp_nz_begin_offset must have #WLB + 1 entries";
+            else if (hm[asp::MS_WARP_NZ].get(W) > nnz_pad) st = ASP_ERR_BOUNDS, why = "warp-per-row: last nz offset outside val_arr";
+            p->units_for_grid = W;
+            break;
+        }
+        case ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE:
+        case ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE:
+        {
+            const uint64_t T = hm[asp::MS_COMBINE].len;
+            const uint64_t W = T / 32;
+            a.n_units = W;
+            a.n_tlb = T;
+            a.warps_first_row_len = (int)std::min<uint64_t>(hm[asp::MS_ROW_OF_UNIT].len, 0x7fffffff);
+            if (hm[asp::MS_COMBINE].kind != ASP_COMPRESS_NONE) st = ASP_ERR_INVALID_ARG, why = "CSR5-like: combine meta must be an array";
+            else if (T == 0 || (T % 32) != 0 || d.tlb_size == 0 || T * d.tlb_size != nnz_pad) st = ASP_ERR_BOUNDS, why = "CSR5-like: #TLB * TLB size != padded nnz";
+            else if (hm[asp::MS_ROW_OF_UNIT].len < W) st = ASP_ERR_BOUNDS, why = "CSR5-like: first-row array shorter than #WLB";
+            else if (d.bits_word != 8 * dtype_size(hm[asp::MS_COMBINE].dtype) || d.bits_row <= 0 || d.bits_off <= 0 || (int)d.tlb_size + d.bits_row + d.bits_off > d.bits_word)
+                st = ASP_ERR_INVALID_ARG, why = "CSR5-like: inconsistent combine-meta bit layout";
+            p->units_for_grid = W;
+            break;
+        }
+        default: st = ASP_ERR_UNSUPPORTED; why = "template not implemented"; break;
+        }
+        if (st != ASP_OK)
+        {
+            cleanup();
+            return fail(st, why);
+        }
+        if (is_smem_family(d.template_type))
+        {
+            p->smem = align_up((size_t)p->smem_elems * (p->val_is_f64 ? 8 : 4), 16);
+            if (p->smem > (size_t)ctx->max_smem_optin)
+            {
+                cleanup();
+                return fail(ASP_ERR_UNSUPPORTED, "partial results of one BLB do not fit in shared memory");
+            }
+            cudaError_t e = asp::allow_dynamic_smem(d.template_type, p->val_is_f64, p->col_width, p->smem);
+            if (e != cudaSuccess)
+            {
+                cleanup();
+                return cuda_fail(e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+            }
+        }
+        p->needs_zero = a.atomic != 0 || d.template_type == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE ||
+                        d.template_type == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE;
+        st = apply_launch(ctx, p, d.tblock_num, d.thread_num_in_block > 0 ? d.thread_num_in_block : 256, d.thread_num_of_row_reduce);
+        if (st != ASP_OK)
+        {
+            cleanup();
+            return st;
+        }
+    }
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess)
+    {
+        cleanup();
+        return cuda_fail(e, "plan upload");
+    }
+    return ASP_OK;
+}
+
+void asp_plan_destroy(asp_plan *plan) { delete plan; }
+
+asp_status asp_plan_set_launch(asp_plan *plan, int64_t tblock_num, int64_t thread_num_in_block, int64_t thread_num_of_row_reduce)
+{
+    if (!plan) return fail(ASP_ERR_INVALID_ARG, "plan is NULL");
+    if (plan->templ == ASP_EMPTY_TEMPLATE) return ASP_OK;
+    return apply_launch(nullptr, plan, tblock_num, thread_num_in_block, thread_num_of_row_reduce);
+}
+
+uint64_t asp_plan_format_bytes(const asp_plan *plan) { return plan ? plan->fmt_bytes : 0; }
+int asp_plan_launches(const asp_plan *plan) { return (plan && plan->templ != ASP_EMPTY_TEMPLATE) ? 1 : 0; }
+
+asp_status asp_spmv(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *d_x, void *d_y, int zero_y)
+{
+    if (!ctx || !plans || n_plans <= 0 || !d_x || !d_y) return fail(ASP_ERR_INVALID_ARG, "NULL argument");
+    const asp_plan *first = nullptr;
+    for (int i = 0; i < n_plans; i++)
+    {
+        if (!plans[i]) return fail(ASP_ERR_INVALID_ARG, "NULL plan");
+        if (plans[i]->templ != ASP_EMPTY_TEMPLATE && !first) first = plans[i];
+    }
+    if (!first) return ASP_OK;
+    if (zero_y) ASP_CUDA(cudaMemsetAsync(d_y, 0, first->n_rows * (first->val_is_f64 ? 8 : 4), ctx->stream));
+    for (int i = 0; i < n_plans; i++)
+    {
+        asp_plan *p = plans[i];
+        if (p->templ == ASP_EMPTY_TEMPLATE) continue;
+        if (p->val_is_f64 != first->val_is_f64 || p->n_rows != first->n_rows || p->n_cols != first->n_cols)
+            return fail(ASP_ERR_INVALID_ARG, "plans of different matrices in one call");
+        p->args.x = d_x;
+        p->args.y = d_y;
+        ASP_CUDA(asp::launch_template(p->templ, p->val_is_f64, p->col_width, p->args, p->grid, p->block, p->smem, ctx->stream, p->vec));
+    }
+    return ASP_OK;
+}
+
+asp_status asp_spmv_host(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *h_x, void *h_y)
+{
+    if (!ctx || !plans || n_plans <= 0 || !plans[0] || !h_x || !h_y) return fail(ASP_ERR_INVALID_ARG, "NULL argument");
+    const size_t es = plans[0]->val_is_f64 ? 8 : 4;
+    const size_t xb = plans[0]->n_cols * es, yb = plans[0]->n_rows * es;
+    asp_status st = ensure_xy(ctx, xb, yb);
+    if (st != ASP_OK) return st;
+    ASP_CUDA(cudaMemcpyAsync(ctx->x, h_x, xb, cudaMemcpyHostToDevice, ctx->stream));
+    st = asp_spmv(ctx, plans, n_plans, ctx->x, ctx->y, 1);
+    if (st != ASP_OK) return st;
+    ASP_CUDA(cudaMemcpyAsync(h_y, ctx->y, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    ASP_CUDA(cudaStreamSynchronize(ctx->stream));
+    return ASP_OK;
+}
+
+asp_status asp_time(asp_ctx *ctx, asp_plan *const *plans, int n_plans, int warmup, int reps, int zero_y,
+                    double gflops_up_bound, float *ms_per_spmv, float *gflops)
+{
+    if (!ctx || !plans || n_plans <= 0 || !plans[0] || reps <= 0 || !ms_per_spmv) return fail(ASP_ERR_INVALID_ARG, "NULL argument or reps <= 0");
+    const size_t es = plans[0]->val_is_f64 ? 8 : 4;
+    const size_t xn = plans[0]->n_cols, yn = plans[0]->n_rows;
+    asp_status st = ensure_xy(ctx, xn * es, yn * es);
+    if (st != ASP_OK) return st;
+    {
+        // x = 100 everywhere, as the reference's generated main() sets it (code_builder.cc:1508-1509)
+        std::vector<char> hx(xn * es);
+        if (es == 8) std::fill((double *)hx.data(), (double *)hx.data() + xn, 100.0);
+        else std::fill((float *)hx.data(), (float *)hx.data() + xn, 100.0f);
+        ASP_CUDA(cudaMemcpyAsync(ctx->x, hx.data(), xn * es, cudaMemcpyHostToDevice, ctx->stream));
+        ASP_CUDA(cudaStreamSynchronize(ctx->stream));
+    }
+    for (int i = 0; i < warmup; i++)
+    {
+        st = asp_spmv(ctx, plans, n_plans, ctx->x, ctx->y, zero_y);
+        if (st != ASP_OK) return st;
+    }
+    ASP_CUDA(cudaStreamSynchronize(ctx->stream));
+    ASP_CUDA(cudaEventRecord(ctx->ev0, ctx->stream));
+    for (int i = 0; i < reps; i++)
+    {
+        st = asp_spmv(ctx, plans, n_plans, ctx->x, ctx->y, zero_y);
+        if (st != ASP_OK) return st;
+    }
+    ASP_CUDA(cudaEventRecord(ctx->ev1, ctx->stream));
+    ASP_CUDA(cudaEventSynchronize(ctx->ev1));
+    float ms = 0;
+    ASP_CUDA(cudaEventElapsedTime(&ms, ctx->ev0, ctx->ev1));
+    ms /= (float)reps;
+    *ms_per_spmv = ms;
+    uint64_t nnz = 0;
+    for (int i = 0; i < n_plans; i++) nnz += plans[i]->true_nnz;
+    const double g = ms > 0 ? 2.0 * (double)nnz * 1e-6 / ms : 0.0;
+    if (gflops) *gflops = (float)g;
+    if (gflops_up_bound > 0 && g > gflops_up_bound) return fail(ASP_ERR_IMPLAUSIBLE, "throughput above the configured GFLOPS_UP_BOUND");
+    return ASP_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,707 @@
+// Hand-written sm_100a SpMV kernels, one family per reduce operator ("template") of the
+// reference. Every family is parameterised at run time: value dtype and column-index width
+// are template parameters, every metadata array is a `Meta` (device array of width 1/2/4/8 or
+// a closed form), launch shape comes from the tuner.
+//
+// Array semantics follow the reference's emitted kernels (code_of_template_kernal in
+// direct_atom_op*.cc, shared_memory_*.cc, unaligned_warp_reduce_same_TLB_size_op*.cc); the
+// device code itself is new: vectorised streaming loads of values/indices, read-only-path
+// gathers of x, shuffle reductions, segmented warp scan without prefix-sum cancellation,
+// red.global atomics only where a row is shared.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernel_args.h"
+#include "kernels.h"
+
+namespace asp
+{
+
+typedef unsigned long long u64;
+typedef unsigned int u32;
+
+// ---------------------------------------------------------------------------------------------
+// metadata access
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ u64 mload(const void *p, int width, u64 i)
+{
+    switch (width)
+    {
+    case 1: return __ldg((const unsigned char *)p + i);
+    case 2: return __ldg((const unsigned short *)p + i);
+    case 4: return __ldg((const unsigned int *)p + i);
+    default: return __ldg((const u64 *)p + i);
+    }
+}
+
+__device__ __forceinline__ u64 mget(const Meta &m, u64 i)
+{
+    switch (m.kind)
+    {
+    case MK_ARRAY: return mload(m.p, m.width, i);
+    case MK_LINEAR: return i * m.coef + m.icpt;
+    case MK_CONSTANT: return m.icpt;
+    case MK_CYCLE_LINEAR: return (i % m.cycle) * m.coef + m.icpt;
+    case MK_CYCLE_INCREASE: return i / m.cycle + m.icpt;
+    default:
+    {
+        u64 v = m.bval[0];
+#pragma unroll
+        for (int b = 1; b < 5; b++)
+            if (b < m.nb && i > m.bhi[b - 1]) v = m.bval[b];
+        return v;
+    }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// streaming vector loads: values and column indices are touched once per SpMV, so they are
+// loaded with the evict-first policy and leave L1/L2 to the x gathers.
+// ---------------------------------------------------------------------------------------------
+template <class T, int V>
+struct alignas(sizeof(T) * V) Vec
+{
+    T v[V];
+};
+
+template <int BYTES>
+struct RawLoad;
+template <>
+struct RawLoad<1>
+{
+    typedef unsigned char type;
+};
+template <>
+struct RawLoad<2>
+{
+    typedef unsigned short type;
+};
+template <>
+struct RawLoad<4>
+{
+    typedef unsigned int type;
+};
+template <>
+struct RawLoad<8>
+{
+    typedef uint2 type;
+};
+template <>
+struct RawLoad<16>
+{
+    typedef uint4 type;
+};
+
+template <class T, int V>
+__device__ __forceinline__ Vec<T, V> ld_stream(const T *p)
+{
+    typedef typename RawLoad<sizeof(T) * V>::type R;
+    union
+    {
+        R r;
+        Vec<T, V> v;
+    } u;
+    u.r = __ldcs(reinterpret_cast<const R *>(p));
+    return u.v;
+}
+// 32-byte groups (8 x f32 / 4 x f64) are fetched as two 16-byte halves
+template <class T, int V>
+__device__ __forceinline__ void ld_stream_n(const T *p, T (&out)[V])
+{
+    if constexpr (sizeof(T) * V <= 16)
+    {
+        Vec<T, V> t = ld_stream<T, V>(p);
+#pragma unroll
+        for (int j = 0; j < V; j++) out[j] = t.v[j];
+    }
+    else
+    {
+        constexpr int H = 16 / sizeof(T);
+#pragma unroll
+        for (int h = 0; h < V / H; h++)
+        {
+            Vec<T, H> t = ld_stream<T, H>(p + h * H);
+#pragma unroll
+            for (int j = 0; j < H; j++) out[h * H + j] = t.v[j];
+        }
+    }
+}
+
+template <class VT>
+__device__ __forceinline__ void out_add(VT *y, u64 row, VT v, bool atomic)
+{
+    if (atomic)
+        atomicAdd(y + row, v); // result unused: compiles to red.global.add
+    else
+        y[row] = v;
+}
+
+// rows whose permutation is applied on the device (shared-memory and CSR5-like families)
+__device__ __forceinline__ u64 row_on_device(const KArgs &a, u64 r)
+{
+    if (a.sort_kind == 1) return mget(a.perm, r + a.first_row);
+    if (a.sort_kind == 2) return mget(a.perm, r) + a.first_row;
+    return r + a.first_row;
+}
+
+template <class VT>
+__device__ __forceinline__ VT warp_sum(VT v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS (ELL-like): thread t owns row map[t]; element k of
+// TLB t sits at t + k*P, P = padded TLB count. V adjacent TLBs per thread give 16-byte loads.
+// ---------------------------------------------------------------------------------------------
+template <class VT, class CT, int V>
+__global__ void __launch_bounds__(1024) k_ell(const KArgs a)
+{
+    const VT *__restrict__ val = (const VT *)a.val;
+    const CT *__restrict__ col = (const CT *)a.col;
+    const VT *__restrict__ x = (const VT *)a.x + a.first_col;
+    VT *__restrict__ y = (VT *)a.y;
+    const u64 P = a.n_tlb;
+    const u32 S = a.tlb_size;
+    const u64 ngroup = P / V;
+    const u64 stride = (u64)gridDim.x * blockDim.x;
+    for (u64 g = (u64)blockIdx.x * blockDim.x + threadIdx.x; g < ngroup; g += stride)
+    {
+        const u64 t0 = g * V;
+        if (t0 >= a.effective) break;
+        VT acc[V];
+#pragma unroll
+        for (int j = 0; j < V; j++) acc[j] = 0;
+        const VT *vp = val + t0;
+        const CT *cp = col + t0;
+#pragma unroll 4
+        for (u32 k = 0; k < S; k++)
+        {
+            VT v[V];
+            CT c[V];
+            ld_stream_n<VT, V>(vp, v);
+            ld_stream_n<CT, V>(cp, c);
+#pragma unroll
+            for (int j = 0; j < V; j++) acc[j] += v[j] * __ldg(x + c[j]);
+            vp += P;
+            cp += P;
+        }
+        const u64 radd = a.row_add ? a.first_row : 0;
+#pragma unroll
+        for (int j = 0; j < V; j++)
+        {
+            const u64 t = t0 + j;
+            if (t < a.effective) out_add(y, mget(a.m[MS_ROW_OF_TLB], t) + radd, acc[j], a.atomic != 0);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// DIRECT_ATOM_TEMPLATE_WARP_COMPRESS (SELL-like): CTA <-> BLB (row strip); inside the strip
+// element k of local TLB i sits at nz0 + i + k*n, n = TLBs of the strip.
+// ---------------------------------------------------------------------------------------------
+template <class VT, class CT, int V>
+__global__ void __launch_bounds__(1024) k_sell(const KArgs a)
+{
+    const VT *__restrict__ val = (const VT *)a.val;
+    const CT *__restrict__ col = (const CT *)a.col;
+    const VT *__restrict__ x = (const VT *)a.x + a.first_col;
+    VT *__restrict__ y = (VT *)a.y;
+    const u64 radd = a.row_add ? a.first_row : 0;
+    for (u64 b = blockIdx.x; b < a.n_units; b += gridDim.x)
+    {
+        const u64 nz0 = mget(a.m[MS_BLK_NZ], b);
+        const u64 t0 = mget(a.m[MS_BLK_THR], b);
+        const u64 t1 = mget(a.m[MS_BLK_THR], b + 1);
+        const u32 S = (u32)mget(a.m[MS_TLB_SIZE], b);
+        const u64 n = t1 - t0;
+        if (t0 >= a.effective) continue;
+        if (V > 1 && (n % V == 0) && (nz0 % V == 0))
+        {
+            for (u64 i = (u64)threadIdx.x * V; i < n; i += (u64)blockDim.x * V)
+            {
+                if (t0 + i >= a.effective) break;
+                VT acc[V];
+#pragma unroll
+                for (int j = 0; j < V; j++) acc[j] = 0;
+                const VT *vp = val + nz0 + i;
+                const CT *cp = col + nz0 + i;
+#pragma unroll 4
+                for (u32 k = 0; k < S; k++)
+                {
+                    VT v[V];
+                    CT c[V];
+                    ld_stream_n<VT, V>(vp, v);
+                    ld_stream_n<CT, V>(cp, c);
+#pragma unroll
+                    for (int j = 0; j < V; j++) acc[j] += v[j] * __ldg(x + c[j]);
+                    vp += n;
+                    cp += n;
+                }
+#pragma unroll
+                for (int j = 0; j < V; j++)
+                {
+                    const u64 t = t0 + i + j;
+                    if (t < a.effective) out_add(y, mget(a.m[MS_ROW_OF_TLB], t) + radd, acc[j], a.atomic != 0);
+                }
+            }
+        }
+        else
+        {
+            for (u64 i = threadIdx.x; i < n; i += blockDim.x)
+            {
+                const u64 t = t0 + i;
+                if (t >= a.effective) break;
+                VT acc = 0;
+                const VT *vp = val + nz0 + i;
+                const CT *cp = col + nz0 + i;
+#pragma unroll 4
+                for (u32 k = 0; k < S; k++)
+                {
+                    acc += __ldcs(vp) * __ldg(x + __ldcs(cp));
+                    vp += n;
+                    cp += n;
+                }
+                out_add(y, mget(a.m[MS_ROW_OF_TLB], t) + radd, acc, a.atomic != 0);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// DIRECT_ATOM_TEMPLATE: BLB -> WLB -> groups of 32 TLBs, values warp-staggered (element k of
+// lane l in group g at base + g*32*S + k*32 + l). The reference accumulates this template in
+// double and always adds atomically when rows are shared.
+// ---------------------------------------------------------------------------------------------
+template <class VT, class CT>
+__global__ void __launch_bounds__(1024) k_direct3(const KArgs a)
+{
+    const VT *__restrict__ val = (const VT *)a.val;
+    const CT *__restrict__ col = (const CT *)a.col;
+    const VT *__restrict__ x = (const VT *)a.x + a.first_col;
+    VT *__restrict__ y = (VT *)a.y;
+    const u32 lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wnum = blockDim.x >> 5;
+    const u64 radd = a.row_add ? a.first_row : 0;
+    for (u64 b = blockIdx.x; b < a.n_units; b += gridDim.x)
+    {
+        const u64 bnz = mget(a.m[MS_BLK_NZ], b);
+        const u64 w0 = mget(a.m[MS_BLK_WARP], b), w1 = mget(a.m[MS_BLK_WARP], b + 1);
+        for (u64 w = w0 + wid; w < w1; w += wnum)
+        {
+            const u64 wnz = bnz + mget(a.m[MS_WARP_NZ], w);
+            const u32 S = (u32)mget(a.m[MS_TLB_SIZE], w);
+            const u64 t0 = mget(a.m[MS_WARP_THR], w), t1 = mget(a.m[MS_WARP_THR], w + 1);
+            const u64 groups = (t1 - t0) >> 5;
+            for (u64 g = 0; g < groups; g++)
+            {
+                double acc = 0;
+                u64 nz = wnz + g * 32 * S + lane;
+                for (u32 k = 0; k < S; k++, nz += 32) acc += (double)(__ldcs(val + nz) * __ldg(x + __ldcs(col + nz)));
+                const u64 t = t0 + g * 32 + lane;
+                out_add(y, mget(a.m[MS_ROW_OF_TLB], t) + radd, (VT)acc, a.atomic != 0);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE (CSR-vector-like): warp <-> WLB = a chunk of one row.
+// ---------------------------------------------------------------------------------------------
+template <class VT, class CT>
+__device__ __forceinline__ VT warp_chunk_dot(const VT *__restrict__ val, const CT *__restrict__ col, const VT *__restrict__ x, u64 beg, u64 end, u32 lane)
+{
+    VT acc = 0;
+    constexpr int V = 16 / sizeof(VT) >= 4 ? 4 : 2; // 4 x f32 or 2 x f64 per lane and step
+    if (((beg | end) & (V - 1)) == 0 && end - beg >= 32 * V)
+    {
+        u64 i = beg + (u64)lane * V;
+        for (; i + V <= end; i += 32 * V)
+        {
+            VT v[V];
+            CT c[V];
+            ld_stream_n<VT, V>(val + i, v);
+            ld_stream_n<CT, V>(col + i, c);
+#pragma unroll
+            for (int j = 0; j < V; j++) acc += v[j] * __ldg(x + c[j]);
+        }
+    }
+    else
+    {
+        for (u64 i = beg + lane; i < end; i += 32) acc += __ldcs(val + i) * __ldg(x + __ldcs(col + i));
+    }
+    return acc;
+}
+
+template <class VT, class CT>
+__global__ void __launch_bounds__(1024) k_warp_row(const KArgs a)
+{
+    const VT *__restrict__ val = (const VT *)a.val;
+    const CT *__restrict__ col = (const CT *)a.col;
+    const VT *__restrict__ x = (const VT *)a.x + a.first_col;
+    VT *__restrict__ y = (VT *)a.y;
+    const u32 lane = threadIdx.x & 31;
+    const u64 wstride = ((u64)gridDim.x * blockDim.x) >> 5;
+    const u64 radd = a.row_add ? a.first_row : 0;
+    for (u64 w = ((u64)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < a.effective; w += wstride)
+    {
+        const u64 beg = mget(a.m[MS_WARP_NZ], w), end = mget(a.m[MS_WARP_NZ], w + 1);
+        VT acc = warp_sum(warp_chunk_dot<VT, CT>(val, col, x, beg, end, lane));
+        if (lane == 0) out_add(y, mget(a.m[MS_ROW_OF_UNIT], w) + radd, acc, a.atomic != 0);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SHARED_MEMORY_LONG_ROW_TEMPLATE: CTA <-> BLB = a chunk of one long row.
+// ---------------------------------------------------------------------------------------------
+template <class VT, class CT>
+__global__ void __launch_bounds__(1024) k_long_row(const KArgs a)
+{
+    __shared__ VT part[32];
+    const VT *__restrict__ val = (const VT *)a.val;
+    const CT *__restrict__ col = (const CT *)a.col;
+    const VT *__restrict__ x = (const VT *)a.x + a.first_col;
+    VT *__restrict__ y = (VT *)a.y;
+    const u32 lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wnum = blockDim.x >> 5;
+    const u64 radd = a.row_add ? a.first_row : 0;
+    constexpr int V = 16 / sizeof(VT) >= 4 ? 4 : 2;
+    for (u64 b = blockIdx.x; b < a.n_units; b += gridDim.x)
+    {
+        const u64 beg = mget(a.m[MS_BLK_NZ], b), end = mget(a.m[MS_BLK_NZ], b + 1);
+        VT acc = 0;
+        if (((beg | end) & (V - 1)) == 0)
+        {
+            for (u64 i = beg + (u64)threadIdx.x * V; i < end; i += (u64)blockDim.x * V)
+            {
+                VT v[V];
+                CT c[V];
+                ld_stream_n<VT, V>(val + i, v);
+                ld_stream_n<CT, V>(col + i, c);
+#pragma unroll
+                for (int j = 0; j < V; j++) acc += v[j] * __ldg(x + c[j]);
+            }
+        }
+        else
+        {
+            for (u64 i = beg + threadIdx.x; i < end; i += blockDim.x) acc += __ldcs(val + i) * __ldg(x + __ldcs(col + i));
+        }
+        acc = warp_sum(acc);
+        __syncthreads(); // previous iteration's readers are done with part[]
+        if (lane == 0) part[wid] = acc;
+        __syncthreads();
+        if (wid == 0)
+        {
+            VT s = lane < wnum ? part[lane] : (VT)0;
+            s = warp_sum(s);
+            if (lane == 0) out_add(y, mget(a.m[MS_ROW_OF_UNIT], b) + radd, s, a.atomic != 0);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// phase 2 of the shared-memory family: `w` lanes per row sum the row's slice of the CTA's
+// partial results (CSR over partials), combine by shuffle, lane 0 of the group writes y.
+// Every warp runs the same trip count so full-mask shuffles are legal.
+// ---------------------------------------------------------------------------------------------
+template <class VT>
+__device__ __forceinline__ void smem_row_reduce(const KArgs &a, const VT *part, VT *__restrict__ y, u64 r0, u64 r1, u64 g0)
+{
+    const u32 w = (u32)a.row_reduce;
+    const u32 lane = threadIdx.x & 31;
+    const u32 sub = lane & (w - 1);
+    const u32 rows_per_warp = 32 / w;
+    const u64 rows_per_cta = (u64)(blockDim.x >> 5) * rows_per_warp;
+    for (u64 rb = r0 + (u64)(threadIdx.x >> 5) * rows_per_warp; rb < r1; rb += rows_per_cta)
+    {
+        const u64 r = rb + lane / w;
+        const bool valid = r < r1;
+        VT s = 0;
+        if (valid)
+        {
+            const u64 lo = mget(a.m[MS_ROW_OFF], r) - g0, hi = mget(a.m[MS_ROW_OFF], r + 1) - g0;
+            for (u64 j = lo + sub; j < hi; j += w) s += part[j];
+        }
+        for (u32 o = w >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (valid && sub == 0 && r < a.effective) out_add(y, row_on_device(a, r), s, a.atomic != 0);
+    }
+}
+
+// SHARED_MEMORY_TEMPLATE_WARP_COMPRESS (row-grouped CSR): CTA <-> BLB; TLB partials in smem.
+template <class VT, class CT>
+__global__ void __launch_bounds__(1024) k_smem_tlb(const KArgs a)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    VT *part = reinterpret_cast<VT *>(smem_raw);
+    const VT *__restrict__ val = (const VT *)a.val;
+    const CT *__restrict__ col = (const CT *)a.col;
+    const VT *__restrict__ x = (const VT *)a.x + a.first_col;
+    VT *__restrict__ y = (VT *)a.y;
+    for (u64 b = blockIdx.x; b < a.n_units; b += gridDim.x)
+    {
+        const u64 nz0 = mget(a.m[MS_BLK_NZ], b);
+        const u64 t0 = mget(a.m[MS_BLK_THR], b), t1 = mget(a.m[MS_BLK_THR], b + 1);
+        const u64 r0 = mget(a.m[MS_BLK_ROW], b), r1 = mget(a.m[MS_BLK_ROW], b + 1);
+        const u32 S = (u32)mget(a.m[MS_TLB_SIZE], b);
+        const u64 n = t1 - t0;
+        const u64 g0 = mget(a.m[MS_ROW_OFF], r0);
+        __syncthreads(); // the previous strip's phase 2 has finished reading part[]
+        for (u64 i = threadIdx.x; i < n; i += blockDim.x)
+        {
+            VT acc = 0;
+            const VT *vp = val + nz0 + i;
+            const CT *cp = col + nz0 + i;
+#pragma unroll 4
+            for (u32 k = 0; k < S; k++)
+            {
+                acc += __ldcs(vp) * __ldg(x + __ldcs(cp));
+                vp += n;
+                cp += n;
+            }
+            part[i] = acc;
+        }
+        __syncthreads();
+        smem_row_reduce<VT>(a, part, y, r0, r1, g0);
+    }
+}
+
+// SHARED_MEMORY_TEMPLATE: BLB -> WLB -> TLB with WLB-level interleave (element k of local TLB i
+// of a WLB at bnz + wnz + i + k*n_w), partials of the whole BLB in smem, then the row reduce.
+template <class VT, class CT>
+__global__ void __launch_bounds__(1024) k_smem3(const KArgs a)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    VT *part = reinterpret_cast<VT *>(smem_raw);
+    const VT *__restrict__ val = (const VT *)a.val;
+    const CT *__restrict__ col = (const CT *)a.col;
+    const VT *__restrict__ x = (const VT *)a.x + a.first_col;
+    VT *__restrict__ y = (VT *)a.y;
+    const u32 lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wnum = blockDim.x >> 5;
+    for (u64 b = blockIdx.x; b < a.n_units; b += gridDim.x)
+    {
+        const u64 bnz = mget(a.m[MS_BLK_NZ], b);
+        const u64 w0 = mget(a.m[MS_BLK_WARP], b), w1 = mget(a.m[MS_BLK_WARP], b + 1);
+        const u64 r0 = mget(a.m[MS_BLK_ROW], b), r1 = mget(a.m[MS_BLK_ROW], b + 1);
+        const u64 tb0 = mget(a.m[MS_WARP_THR], w0);
+        const u64 g0 = mget(a.m[MS_ROW_OFF], r0);
+        __syncthreads();
+        for (u64 w = w0 + wid; w < w1; w += wnum)
+        {
+            const u64 wnz = bnz + mget(a.m[MS_WARP_NZ], w);
+            const u32 S = (u32)mget(a.m[MS_TLB_SIZE], w);
+            const u64 t0 = mget(a.m[MS_WARP_THR], w), t1 = mget(a.m[MS_WARP_THR], w + 1);
+            const u64 n = t1 - t0;
+            for (u64 i = lane; i < n; i += 32)
+            {
+                VT acc = 0;
+                u64 nz = wnz + i;
+                for (u32 k = 0; k < S; k++, nz += n) acc += __ldcs(val + nz) * __ldg(x + __ldcs(col + nz));
+                part[t0 + i - tb0] = acc;
+            }
+        }
+        __syncthreads();
+        smem_row_reduce<VT>(a, part, y, r0, r1, g0);
+    }
+}
+
+// SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE: CTA <-> BLB (a few rows); warp <-> WLB (chunk of
+// one row) reduced by shuffle into smem; then the row reduce over WLB partials.
+template <class VT, class CT>
+__global__ void __launch_bounds__(1024) k_smem_wlb(const KArgs a)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    VT *part = reinterpret_cast<VT *>(smem_raw);
+    const VT *__restrict__ val = (const VT *)a.val;
+    const CT *__restrict__ col = (const CT *)a.col;
+    const VT *__restrict__ x = (const VT *)a.x + a.first_col;
+    VT *__restrict__ y = (VT *)a.y;
+    const u32 lane = threadIdx.x & 31, wid = threadIdx.x >> 5, wnum = blockDim.x >> 5;
+    for (u64 b = blockIdx.x; b < a.n_units; b += gridDim.x)
+    {
+        const u64 w0 = mget(a.m[MS_BLK_WARP], b), w1 = mget(a.m[MS_BLK_WARP], b + 1);
+        const u64 r0 = mget(a.m[MS_BLK_ROW], b), r1 = mget(a.m[MS_BLK_ROW], b + 1);
+        const u64 g0 = mget(a.m[MS_ROW_OFF], r0);
+        __syncthreads();
+        for (u64 w = w0 + wid; w < w1; w += wnum)
+        {
+            const u64 beg = mget(a.m[MS_WARP_NZ], w), end = mget(a.m[MS_WARP_NZ], w + 1);
+            VT acc = warp_sum(warp_chunk_dot<VT, CT>(val, col, x, beg, end, lane));
+            if (lane == 0) part[w - w0] = acc;
+        }
+        __syncthreads();
+        smem_row_reduce<VT>(a, part, y, r0, r1, g0);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE[_WITH_WARP_REDUCE] (CSR5-like): every thread
+// owns S consecutive non-zeros regardless of row boundaries; the packed per-thread word holds
+// S row-start flags (MSB first), the count of following threads that continue this thread's
+// last row, and the first row (relative to the warp's first row) that starts in this thread.
+//
+// Cross-thread tails are combined with a flag-segmented suffix scan (no subtraction of prefix
+// sums), and the thread that holds a row's start writes the row's total. The reference's
+// emitted code writes the per-thread partial instead of the total for rows that span threads.
+// ---------------------------------------------------------------------------------------------
+template <class VT, class CT, bool WARP_FAST>
+__global__ void __launch_bounds__(1024) k_csr5(const KArgs a)
+{
+    const VT *__restrict__ val = (const VT *)a.val;
+    const CT *__restrict__ col = (const CT *)a.col;
+    const VT *__restrict__ x = (const VT *)a.x + a.first_col;
+    VT *__restrict__ y = (VT *)a.y;
+    const u32 lane = threadIdx.x & 31;
+    const u32 S = a.tlb_size;
+    const u64 wstride = ((u64)gridDim.x * blockDim.x) >> 5;
+    for (u64 w = ((u64)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < a.n_units; w += wstride)
+    {
+        const u64 R0 = mget(a.m[MS_ROW_OF_UNIT], w);
+        u64 nz = w * 32 * S + lane;
+        if (WARP_FAST)
+        {
+            // the first-row array of this template carries one sentinel entry past the last warp
+            const u64 R1 = (w + 1 < (u64)a.warps_first_row_len) ? mget(a.m[MS_ROW_OF_UNIT], w + 1) : R0 + 1;
+            if (R0 == R1)
+            {
+                VT s = 0;
+                for (u32 k = 0; k < S; k++, nz += 32) s += __ldcs(val + nz) * __ldg(x + __ldcs(col + nz));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (lane == 0) atomicAdd(y + row_on_device(a, R0), s);
+                continue;
+            }
+        }
+        const u64 meta = mload(a.m[MS_COMBINE].p, a.m[MS_COMBINE].width, w * 32 + lane);
+        const u32 frow = (u32)(meta & ((1ull << a.bits_row) - 1));
+        const u32 roff = (u32)((meta >> a.bits_row) & ((1ull << a.bits_off) - 1));
+        u32 yo = frow;
+        bool seen = false;
+        VT sum = 0, tail = 0;
+        for (u32 k = 0; k < S; k++, nz += 32)
+        {
+            const bool flag = (meta >> (a.bits_word - 1 - k)) & 1ull;
+            if (flag)
+            {
+                if (seen)
+                {
+                    // a row that starts and ends inside this thread; only the warp's very first
+                    // row can also receive contributions from the previous warp
+                    const bool at = a.atomic || (lane == 0 && yo == frow);
+                    out_add(y, row_on_device(a, R0 + yo), sum, at);
+                    yo++;
+                }
+                else
+                    tail = sum;
+                seen = true;
+                sum = 0;
+            }
+            sum += __ldcs(val + nz) * __ldg(x + __ldcs(col + nz));
+        }
+        if (!seen) tail = sum;
+        // suffix scan of the tails, segmented at threads that start a row: after the scan
+        // lane j holds the sum of tail[j..] up to and including the next row-starting lane.
+        const u32 heads = __ballot_sync(0xffffffffu, seen);
+        VT sc = tail;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1)
+        {
+            const VT o = __shfl_down_sync(0xffffffffu, sc, d);
+            // lanes [lane, lane+d) must contain no row start for lane+d to belong to my segment
+            const bool same = (lane + d < 32) && (((heads >> lane) & ((1u << d) - 1u)) == 0u);
+            if (same) sc += o;
+        }
+        VT extra = __shfl_down_sync(0xffffffffu, sc, 1);
+        if (lane == 31) extra = 0;
+        if (seen)
+        {
+            const bool at = a.atomic || (lane == 0 && yo == frow) || (lane + roff == 31);
+            out_add(y, row_on_device(a, R0 + yo), sum + extra, at);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// launch dispatch
+// ---------------------------------------------------------------------------------------------
+template <class VT, class CT>
+static cudaError_t launch_vc(int templ, const KArgs &a, dim3 grid, dim3 block, size_t smem, cudaStream_t st, int vec)
+{
+    switch (templ)
+    {
+    case 2: // ELL-like
+        if (vec >= 8) k_ell<VT, CT, 8><<<grid, block, 0, st>>>(a);
+        else if (vec >= 4) k_ell<VT, CT, 4><<<grid, block, 0, st>>>(a);
+        else if (vec == 2) k_ell<VT, CT, 2><<<grid, block, 0, st>>>(a);
+        else k_ell<VT, CT, 1><<<grid, block, 0, st>>>(a);
+        break;
+    case 1: // SELL-like
+        if (vec >= 4) k_sell<VT, CT, 4><<<grid, block, 0, st>>>(a);
+        else if (vec == 2) k_sell<VT, CT, 2><<<grid, block, 0, st>>>(a);
+        else k_sell<VT, CT, 1><<<grid, block, 0, st>>>(a);
+        break;
+    case 0: k_direct3<VT, CT><<<grid, block, 0, st>>>(a); break;
+    case 7: k_warp_row<VT, CT><<<grid, block, 0, st>>>(a); break;
+    case 5: k_long_row<VT, CT><<<grid, block, 0, st>>>(a); break;
+    case 4: k_smem_tlb<VT, CT><<<grid, block, smem, st>>>(a); break;
+    case 3: k_smem3<VT, CT><<<grid, block, smem, st>>>(a); break;
+    case 6: k_smem_wlb<VT, CT><<<grid, block, smem, st>>>(a); break;
+    case 8: k_csr5<VT, CT, false><<<grid, block, 0, st>>>(a); break;
+    case 9: k_csr5<VT, CT, true><<<grid, block, 0, st>>>(a); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+template <class VT>
+static cudaError_t launch_v(int templ, int col_width, const KArgs &a, dim3 grid, dim3 block, size_t smem, cudaStream_t st, int vec)
+{
+    switch (col_width)
+    {
+    case 1: return launch_vc<VT, unsigned char>(templ, a, grid, block, smem, st, vec);
+    case 2: return launch_vc<VT, unsigned short>(templ, a, grid, block, smem, st, vec);
+    case 4: return launch_vc<VT, unsigned int>(templ, a, grid, block, smem, st, vec);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_template(int templ, int val_is_f64, int col_width, const KArgs &a, unsigned grid, unsigned block, size_t smem, cudaStream_t st, int vec)
+{
+    if (val_is_f64) return launch_v<double>(templ, col_width, a, dim3(grid), dim3(block), smem, st, vec);
+    return launch_v<float>(templ, col_width, a, dim3(grid), dim3(block), smem, st, vec);
+}
+
+template <class VT, class CT>
+static cudaError_t smem_attr_vc(int templ, size_t smem)
+{
+    const void *f = NULL;
+    switch (templ)
+    {
+    case 4: f = (const void *)k_smem_tlb<VT, CT>; break;
+    case 3: f = (const void *)k_smem3<VT, CT>; break;
+    case 6: f = (const void *)k_smem_wlb<VT, CT>; break;
+    default: return cudaSuccess;
+    }
+    return cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+}
+
+// opt in to more than 48 KB of dynamic shared memory for the shared-memory family
+cudaError_t allow_dynamic_smem(int templ, int val_is_f64, int col_width, size_t smem)
+{
+    if (smem <= 48 * 1024) return cudaSuccess;
+#define ASP_SMEM_CASE(VT)                                                      \
+    switch (col_width)                                                         \
+    {                                                                          \
+    case 1: return smem_attr_vc<VT, unsigned char>(templ, smem);               \
+    case 2: return smem_attr_vc<VT, unsigned short>(templ, smem);              \
+    case 4: return smem_attr_vc<VT, unsigned int>(templ, smem);                \
+    default: return cudaErrorInvalidValue;                                     \
+    }
+    if (val_is_f64)
+    {
+        ASP_SMEM_CASE(double)
+    }
+    ASP_SMEM_CASE(float)
+#undef ASP_SMEM_CASE
+}
+
+} // namespace asp

@@ -1,0 +1,196 @@
+/*
+ * asp_b200.h -- C ABI of the B200-native SpMV path for AlphaSparse's machine-designed formats.
+ *
+ * This boundary replaces the reference's executor seam: where the reference wrote text files,
+ * emitted template.cu / template.h, shelled out to nvcc and ran ./a.out to time y = A*x
+ * (executor.hpp:12-22, executor.cc:6-260, code_builder.cc:1471-1575), a caller now hands the
+ * per-sub-matrix template arrays to asp_plan_group_create() once and launches / times
+ * precompiled sm_100a kernels.
+ *
+ * All entry points use C linkage, plain pointers and sizes, return an asp_status and never
+ * throw or abort. Handles are opaque. One asp_ctx per GPU and per host thread.
+ */
+#ifndef ASP_B200_H
+#define ASP_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum asp_status
+{
+    ASP_OK = 0,
+    ASP_ERR_INVALID_ARG = 1, /* NULL pointer, bad length, inconsistent descriptor          */
+    ASP_ERR_UNSUPPORTED = 2, /* a dtype / template / width the kernels do not implement     */
+    ASP_ERR_CUDA = 3,        /* a CUDA runtime call failed; asp_last_error() has the text   */
+    ASP_ERR_ALLOC = 4,       /* host or device allocation failed                            */
+    ASP_ERR_BOUNDS = 5,      /* a format array refers outside val/col/x/y                   */
+    ASP_ERR_IMPLAUSIBLE = 6  /* measured throughput above the configured sanity bound       */
+} asp_status;
+
+/* element types of format arrays; the reference narrows every index array to the smallest
+ * unsigned type that holds its maximum (op_manager.cc:1103-1134). */
+typedef enum asp_dtype
+{
+    ASP_U8 = 0,
+    ASP_U16 = 1,
+    ASP_U32 = 2,
+    ASP_U64 = 3,
+    ASP_F32 = 4,
+    ASP_F64 = 5
+} asp_dtype;
+
+/* closed forms that stand in for a metadata array (arr_optimization.hpp:12-81). The
+ * reference bakes them into the emitted source; here they are kernel parameters. */
+typedef enum asp_compress_kind
+{
+    ASP_COMPRESS_NONE = 0,           /* a[i] is loaded                       */
+    ASP_COMPRESS_LINEAR = 1,         /* a[i] = i*coef + icpt                 */
+    ASP_COMPRESS_CONSTANT = 2,       /* a[i] = icpt                          */
+    ASP_COMPRESS_BRANCH = 3,         /* a[i] = val[b] for lo[b] <= i <= hi[b]*/
+    ASP_COMPRESS_CYCLE_LINEAR = 4,   /* a[i] = (i % cycle)*coef + icpt       */
+    ASP_COMPRESS_CYCLE_INCREASE = 5  /* a[i] = i / cycle + icpt              */
+} asp_compress_kind;
+
+/* same order as the reference's template_type (code_builder.hpp:15-29) */
+typedef enum asp_template_type
+{
+    ASP_DIRECT_ATOM_TEMPLATE = 0,
+    ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS = 1,
+    ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS = 2,
+    ASP_SHARED_MEMORY_TEMPLATE = 3,
+    ASP_SHARED_MEMORY_TEMPLATE_WARP_COMPRESS = 4,
+    ASP_SHARED_MEMORY_LONG_ROW_TEMPLATE = 5,
+    ASP_SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE = 6,
+    ASP_DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE = 7,
+    ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE = 8,
+    ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE = 9,
+    ASP_EMPTY_TEMPLATE = 10
+} asp_template_type;
+
+/* role of an array inside a template; names are the reference's struct field names
+ * (direct_atom_op.hpp, shared_memory_op_warp_compress.hpp, ... one struct per template). */
+typedef enum asp_array_role
+{
+    ASP_ARR_VAL = 0,
+    ASP_ARR_COL_INDEX = 1,
+    ASP_ARR_ROW_INDEX_BEFORE_SORT = 2,
+    ASP_ARR_GLOBAL_ROW_INDEX_OF_THREAD_LEVEL_BLOCK = 3,
+    ASP_ARR_BLOCK_BEGIN_WARP_INDEX_OFFSET = 4,
+    ASP_ARR_WARP_BEGIN_THREAD_INDEX_OFFSET = 5,
+    ASP_ARR_THREAD_BLOCK_SIZE_IN_WARP = 6,
+    ASP_ARR_BLOCK_NZ_BEGIN_OFFSET = 7,
+    ASP_ARR_WARP_NZ_BEGIN_OFFSET = 8,
+    ASP_ARR_BLOCK_BEGIN_THREAD_INDEX_OFFSET = 9,
+    ASP_ARR_THREAD_BLOCK_SIZE_IN_BLOCK = 10,
+    ASP_ARR_GLOBAL_ROW_INDEX_OF_WARP_LEVEL_BLOCK = 11,
+    ASP_ARR_GLOBAL_WARP_NZ_BEGIN_OFFSET = 12,
+    ASP_ARR_ROW_OFFSET_IN_THREAD_TMP_RESULT = 13,
+    ASP_ARR_BLOCK_FIRST_ROW_INDEX = 14,
+    ASP_ARR_ROW_INDEX_OF_BLOCK_LEVEL_BLOCK = 15,
+    ASP_ARR_ROW_OFFSET_IN_WARP_TMP_RESULT = 16,
+    ASP_ARR_GLOBAL_WARP_BLOCK_FIRST_NZ = 17,
+    ASP_ARR_GLOBAL_FIRST_ROW_INDEX_OF_WARP_LEVEL_BLOCK = 18,
+    ASP_ARR_COMBINE_META_OF_THREAD_LEVEL_BLOCK = 19,
+    ASP_ARR_ROLE_COUNT = 20
+} asp_array_role;
+
+#define ASP_MAX_BRANCH 5 /* BRANCH_COMPRESS_MAX_SIZE of the reference's global_config.json */
+
+/* one (ptr, dtype, size) triple of a template struct plus its arr_compress_type + meta */
+typedef struct asp_array_desc
+{
+    int32_t role;           /* asp_array_role */
+    int32_t dtype;          /* asp_dtype */
+    const void *host_ptr;   /* may be NULL when compress != NONE */
+    uint64_t len;           /* elements */
+    int32_t compress;       /* asp_compress_kind */
+    int32_t n_branch;
+    uint64_t coef, icpt, cycle;
+    uint64_t branch_lo[ASP_MAX_BRANCH], branch_hi[ASP_MAX_BRANCH], branch_val[ASP_MAX_BRANCH];
+} asp_array_desc;
+
+typedef enum asp_sort_kind
+{
+    ASP_SORT_NONE = 0,
+    ASP_SORT_GLOBAL = 1, /* matrix->sorted_row_index, indexed by row + first_row */
+    ASP_SORT_LOCAL = 2   /* per sub-matrix y_write_index, indexed by row         */
+} asp_sort_kind;
+
+/* everything one template struct of the reference carries for one sub-matrix */
+typedef struct asp_plan_desc
+{
+    int32_t template_type;   /* asp_template_type */
+    int32_t val_dtype;       /* ASP_F32 | ASP_F64 */
+    uint64_t n_rows, n_cols; /* of the WHOLE matrix: lengths of y and x */
+    uint64_t first_row;      /* kernal_first_row_index */
+    uint64_t first_col;      /* kernal_first_col_index */
+    uint64_t true_nnz;       /* nnz of this sub-matrix before padding (for GFLOP/s) */
+    int32_t n_arrays;
+    const asp_array_desc *arrays;
+    /* scalars */
+    uint64_t effective_num;  /* effective_TLB_num | effective_WLB_num | effective_row_num; 0 = all */
+    uint64_t tlb_size;       /* thread_block_size_in_block (ELL-like) | global_thread_level_block_size (CSR5-like) */
+    int32_t bits_word, bits_flag, bits_row, bits_off; /* combine-meta layout, CSR5-like templates */
+    int32_t is_atom_add;     /* is_atom_add | is_all_force_atom_add */
+    int32_t sort_kind;       /* asp_sort_kind */
+    /* launch parameters, as the tuner sets them */
+    int64_t tblock_num, thread_num_in_block, thread_num_of_row_reduce;
+} asp_plan_desc;
+
+typedef struct asp_ctx asp_ctx;
+typedef struct asp_plan asp_plan;
+
+/* replaces cudaSetDevice(DEFAULT_DEVICE_ID) + stream creation of the generated main()
+ * (code_builder.cc:1483-1518). */
+asp_status asp_ctx_create(int device, asp_ctx **out);
+void asp_ctx_destroy(asp_ctx *ctx);
+/* raw cudaStream_t the context launches on (for callers that enqueue their own work) */
+void *asp_ctx_stream(asp_ctx *ctx);
+
+/* replaces store_code_builder_data + read_dense_block_k_from_file + the cudaMalloc/cudaMemcpy
+ * block (code_builder.cc:2429-2517, 2119-2129; e.g. direct_atom_op.cc:289-370,1524-1692):
+ * validates and uploads all sub-matrix templates of one matrix. Arrays that share a host
+ * pointer (the global row permutation) are uploaded once. */
+asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp_plan **out_plans);
+void asp_plan_destroy(asp_plan *plan);
+
+/* replaces re-emitting + recompiling the program for every launch-parameter trial
+ * (default_auto_tuner.cc:449-2030): tblock_num / thread_num_in_block / thread_num_of_row_reduce. */
+asp_status asp_plan_set_launch(asp_plan *plan, int64_t tblock_num, int64_t thread_num_in_block, int64_t thread_num_of_row_reduce);
+/* bytes of device memory the plan's format arrays occupy (B_fmt without x and y) */
+uint64_t asp_plan_format_bytes(const asp_plan *plan);
+/* number of kernel launches one asp_spmv over this plan issues (excluding the y clear) */
+int asp_plan_launches(const asp_plan *plan);
+
+/* replaces the spmv_<k><<<...>>> calls of the generated main() (code_builder.cc:1534-1550):
+ * y (+)= A*x over all sub-matrix plans of one matrix; d_x and d_y are device pointers of
+ * the value dtype, lengths n_cols and n_rows. zero_y != 0 clears y first (needed whenever a
+ * plan accumulates with atomics; the reference never clears y between repeats). Asynchronous
+ * on the context's stream. */
+asp_status asp_spmv(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *d_x, void *d_y, int zero_y);
+
+/* same with HOST x and y: copies x in, runs, copies y out, waits. This is the shape of the
+ * reference's a.out run (host arrays in, host y out) without the text files. */
+asp_status asp_spmv_host(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *h_x, void *h_y);
+
+/* replaces execute_binary + perf_result parsing (executor.cc:6-59): CUDA-event timing of
+ * `reps` SpMVs after `warmup`, x and y internal (x = 100 everywhere, as the generated main()
+ * does). gflops = 2*sum(true_nnz)*1e-6/ms. Returns ASP_ERR_IMPLAUSIBLE when gflops exceeds
+ * gflops_up_bound > 0 (the reference's GFLOPS_UP_BOUND check, executor.cc:51-56). */
+asp_status asp_time(asp_ctx *ctx, asp_plan *const *plans, int n_plans, int warmup, int reps, int zero_y,
+                    double gflops_up_bound, float *ms_per_spmv, float *gflops);
+
+asp_status asp_synchronize(asp_ctx *ctx);
+const char *asp_status_str(asp_status s);
+/* text of the last CUDA error seen by this thread ("" if none) */
+const char *asp_last_error(void);
+/* 1 when the library was built with device code for sm_100a */
+int asp_built_for_sm100a(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASP_B200_H */
