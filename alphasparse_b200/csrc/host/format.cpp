@@ -1,0 +1,659 @@
+// Dense-view and compressed-view format operators (see format.hpp).
+#include "format.hpp"
+
+#include <string.h>
+
+#include <algorithm>
+#include <fstream>
+#include <map>
+#include <numeric>
+#include <set>
+#include <sstream>
+
+namespace asp
+{
+namespace host
+{
+
+int suitable_dtype(u64 v)
+{
+    if (v <= 255ull) return ASP_U8;
+    if (v <= 65535ull) return ASP_U16;
+    if (v <= 4294967295ull) return ASP_U32;
+    return ASP_U64;
+}
+
+int dtype_bytes(int dt)
+{
+    switch (dt)
+    {
+    case ASP_U8: return 1;
+    case ASP_U16: return 2;
+    case ASP_U32: case ASP_F32: return 4;
+    default: return 8;
+    }
+}
+
+const TemplateArray *TemplateData::find(int role) const
+{
+    for (const TemplateArray &a : arrays)
+        if (a.role == role) return &a;
+    return nullptr;
+}
+
+// ---------------------------------------------------------------------------------------------
+// input
+// ---------------------------------------------------------------------------------------------
+std::unique_ptr<Matrix> matrix_from_csr(u64 n_rows, u64 n_cols, const int64_t *indptr, const u32 *indices, const void *values, int val_dt)
+{
+    std::unique_ptr<Matrix> m(new Matrix());
+    m->n_rows = n_rows;
+    m->n_cols = n_cols;
+    m->nnz = (u64)indptr[n_rows];
+    m->val_dt = val_dt;
+    m->rowptr.resize(n_rows + 1);
+    for (u64 i = 0; i <= n_rows; i++) m->rowptr[i] = (u64)indptr[i];
+    m->col.assign(indices, indices + m->nnz);
+    m->val.es = dtype_bytes(val_dt);
+    m->val.b.assign((const uint8_t *)values, (const uint8_t *)values + m->nnz * m->val.es);
+    return m;
+}
+
+std::unique_ptr<Matrix> matrix_from_coo_file(const std::string &path, int val_dt, std::string &err)
+{
+    std::ifstream f(path);
+    if (!f)
+    {
+        err = "cannot open " + path;
+        return nullptr;
+    }
+    std::string line;
+    u64 n_rows = 0, n_cols = 0;
+    bool have_head = false;
+    std::vector<u64> rows;
+    std::vector<u32> cols;
+    std::vector<double> vals;
+    u64 last_row = 0;
+    while (std::getline(f, line))
+    {
+        if (line.empty() || line[0] == ' ' || line[0] == '\t' || line[0] == '\r') continue; // lines that start with white space are skipped
+        std::istringstream is(line);
+        if (!have_head)
+        {
+            if (!(is >> n_rows >> n_cols))
+            {
+                err = "bad header line";
+                return nullptr;
+            }
+            have_head = true;
+            continue;
+        }
+        u64 r, c;
+        double v;
+        if (!(is >> r >> c >> v) || r == 0 || c == 0 || r > n_rows || c > n_cols)
+        {
+            err = "bad entry: " + line;
+            return nullptr;
+        }
+        if (r < last_row)
+        {
+            err = "rows are not non-decreasing";
+            return nullptr;
+        }
+        last_row = r;
+        rows.push_back(r - 1);
+        cols.push_back((u32)(c - 1));
+        vals.push_back(v);
+    }
+    std::unique_ptr<Matrix> m(new Matrix());
+    m->n_rows = n_rows;
+    m->n_cols = n_cols;
+    m->nnz = rows.size();
+    m->val_dt = val_dt;
+    m->rowptr.assign(n_rows + 1, 0);
+    for (u64 r : rows) m->rowptr[r + 1]++;
+    for (u64 i = 0; i < n_rows; i++) m->rowptr[i + 1] += m->rowptr[i];
+    m->col.swap(cols);
+    m->val.es = dtype_bytes(val_dt);
+    m->val.resize(m->nnz);
+    if (val_dt == ASP_F64) memcpy(m->val.b.data(), vals.data(), m->nnz * 8);
+    else
+        for (u64 i = 0; i < m->nnz; i++) ((float *)m->val.b.data())[i] = (float)vals[i];
+    return m;
+}
+
+// ---------------------------------------------------------------------------------------------
+// dense view
+// ---------------------------------------------------------------------------------------------
+void dense_row_coarse_sort(Matrix &m, u64 step)
+{
+    const u64 R = m.n_rows;
+    std::vector<u64> len(R);
+    u64 mn = ~0ull, mx = 0;
+    for (u64 r = 0; r < R; r++)
+    {
+        len[r] = m.rowptr[r + 1] - m.rowptr[r];
+        mn = std::min(mn, len[r]);
+        mx = std::max(mx, len[r]);
+    }
+    // bin low bounds (execute_dense_row_coarse_sort_fixed_param_strategy, parameter_set_strategy.cc:441):
+    // step 1 -> one bin per distinct row length, the smallest bound replaced by 0
+    std::vector<u64> low;
+    if (step == 1)
+    {
+        std::vector<u64> d(len);
+        std::sort(d.begin(), d.end());
+        d.erase(std::unique(d.begin(), d.end()), d.end());
+        for (size_t i = 0; i < d.size(); i++) low.push_back(i == 0 ? 0 : d[i]);
+    }
+    else
+        for (u64 i = mn; i <= mx; i += step) low.push_back(i == mn ? 0 : i);
+    const size_t nb = low.size();
+    auto bin_of = [&](u64 l) { return (size_t)(std::upper_bound(low.begin(), low.end(), l) - low.begin()) - 1; };
+    // stable counting sort of the non-empty rows by bin, largest bin first; empty rows keep their
+    // order and go last
+    std::vector<u64> cnt(nb + 1, 0);
+    std::vector<size_t> bin(R);
+    u64 n_empty = 0;
+    for (u64 r = 0; r < R; r++)
+    {
+        if (len[r] == 0)
+        {
+            n_empty++;
+            continue;
+        }
+        bin[r] = bin_of(len[r]);
+        cnt[bin[r]]++;
+    }
+    std::vector<u64> start(nb, 0);
+    u64 acc = 0;
+    for (size_t b = nb; b-- > 0;)
+    {
+        start[b] = acc;
+        acc += cnt[b];
+    }
+    m.perm.assign(R, 0);
+    u64 epos = acc;
+    for (u64 r = 0; r < R; r++)
+    {
+        if (len[r] == 0) m.perm[epos++] = r;
+        else m.perm[start[bin[r]]++] = r;
+    }
+    // rewrite the dense view in the new row order
+    std::vector<u64> nrp(R + 1, 0);
+    for (u64 i = 0; i < R; i++) nrp[i + 1] = nrp[i] + len[m.perm[i]];
+    std::vector<u32> ncol(m.nnz);
+    ValBuf nval;
+    nval.es = m.val.es;
+    nval.b.resize(m.val.b.size());
+    const int es = m.val.es;
+#pragma omp parallel for schedule(dynamic, 4096)
+    for (u64 i = 0; i < R; i++)
+    {
+        const u64 o = m.perm[i], n = len[o];
+        if (n == 0) continue;
+        memcpy(&ncol[nrp[i]], &m.col[m.rowptr[o]], n * sizeof(u32));
+        memcpy(&nval.b[nrp[i] * es], &m.val.b[m.rowptr[o] * es], n * es);
+    }
+    m.rowptr.swap(nrp);
+    m.col.swap(ncol);
+    m.val.b.swap(nval.b);
+    m.is_sorted = true;
+    m.perm_dt = suitable_dtype(R);
+    const int pb = dtype_bytes(m.perm_dt);
+    m.sorted_row_index.reset(new std::vector<uint8_t>(R * pb));
+    uint8_t *p = m.sorted_row_index->data();
+    for (u64 i = 0; i < R; i++) memcpy(p + i * pb, &m.perm[i], pb); // little endian narrowing
+}
+
+std::vector<u64> row_div_position_exponential(const Matrix &m, u64 lowest, u64 highest, u64 rate)
+{
+    std::vector<u64> range;
+    range.push_back(0);
+    for (u64 b = lowest; b <= highest; b *= rate) range.push_back(b);
+    if (range.back() != highest) range.push_back(highest);
+    auto range_of = [&](u64 l) { return (size_t)(std::upper_bound(range.begin(), range.end(), l) - range.begin()) - 1; };
+    std::vector<u64> pos;
+    pos.push_back(0);
+    size_t last = range_of(m.rowptr[1] - m.rowptr[0]);
+    for (u64 r = 1; r < m.n_rows; r++)
+    {
+        const size_t cur = range_of(m.rowptr[r + 1] - m.rowptr[r]);
+        if (cur != last)
+        {
+            pos.push_back(r);
+            last = cur;
+        }
+    }
+    pos.push_back(m.n_rows);
+    return pos;
+}
+
+void dense_row_div(Matrix &m, const std::vector<u64> &pos)
+{
+    // strips without non-zeros are dropped (var_len_row_div, op_manager.cc:370)
+    m.ranges.clear();
+    for (size_t i = 0; i + 1 < pos.size(); i++)
+    {
+        const u64 r0 = pos[i], r1 = std::min<u64>(pos[i + 1], m.n_rows);
+        if (r1 <= r0) continue;
+        const u64 b = m.rowptr[r0], e = m.rowptr[r1];
+        if (e <= b) continue;
+        m.ranges.push_back({r0, r1 - 1, b, e - 1});
+    }
+    m.is_blocked = true;
+}
+
+void compress_dense_view(Matrix &m)
+{
+    if (!m.is_blocked && m.ranges.empty()) m.ranges.push_back({0, m.n_rows - 1, 0, m.nnz - 1});
+    m.blocks.clear();
+    m.blocks.resize(m.ranges.size());
+    for (size_t i = 0; i < m.ranges.size(); i++)
+    {
+        const Matrix::BlockRange &rg = m.ranges[i];
+        CompressedBlock &b = m.blocks[i];
+        b.min_row = rg.min_row;
+        b.max_row = rg.max_row;
+        b.min_col = 0;
+        b.max_col = m.n_cols - 1;
+        b.begin_coo = rg.begin_coo;
+        b.end_coo = rg.end_coo;
+        b.n_rows = rg.max_row - rg.min_row + 1;
+        b.row_dt = suitable_dtype(b.n_rows);                 // counts, not maxima: 65536 rows -> u32
+        b.col_dt = suitable_dtype(b.max_col - b.min_col + 1);
+        b.rowptr.resize(b.n_rows + 1);
+        for (u64 r = 0; r <= b.n_rows; r++) b.rowptr[r] = m.rowptr[rg.min_row + r] - rg.begin_coo;
+        const u64 n = rg.end_coo - rg.begin_coo + 1;
+        b.col.assign(m.col.begin() + rg.begin_coo, m.col.begin() + rg.begin_coo + n);
+        b.val.es = m.val.es;
+        // every block holds ITS slice of the values; the reference copies from offset 0 for every
+        // block (op_manager.cc:1077-1087), which is only right for the first one
+        b.val.b.assign(m.val.b.begin() + rg.begin_coo * m.val.es, m.val.b.begin() + (rg.begin_coo + n) * m.val.es);
+    }
+    m.is_compressed = true;
+}
+
+// ---------------------------------------------------------------------------------------------
+// compressed view
+// ---------------------------------------------------------------------------------------------
+void row_padding(CompressedBlock &b, u64 multiple, u64 plen)
+{
+    const u64 rows = b.max_row - b.min_row + 1;
+    if (rows % multiple == 0) return;
+    const u64 target = (rows / multiple + 1) * multiple;
+    const u64 add = target - rows;
+    const u64 old_nnz = b.col.size();
+    b.col.resize(old_nnz + add * plen, 0); // fake rows: `plen` zeros at (relative) column 0
+    b.val.b.resize((old_nnz + add * plen) * b.val.es, 0);
+    b.rowptr.resize(target + 1);
+    for (u64 r = rows; r < target; r++) b.rowptr[r + 1] = b.rowptr[r] + plen;
+    b.n_rows = target;
+    b.row_dt = suitable_dtype(target);
+}
+
+std::vector<u64> blb_rows_evenly(const CompressedBlock &b, u64 n)
+{
+    std::vector<u64> out(b.n_rows / n, n);
+    if (b.n_rows % n) out.push_back(b.n_rows % n);
+    return out;
+}
+
+std::vector<u64> blb_rows_by_nnz_low_bound(const CompressedBlock &b, u64 low)
+{
+    std::vector<u64> out;
+    u64 rows = 0, nnz = 0;
+    for (u64 r = 0; r < b.n_rows; r++)
+    {
+        nnz += b.rowptr[r + 1] - b.rowptr[r];
+        rows++;
+        if (nnz >= low)
+        {
+            out.push_back(rows);
+            rows = 0;
+            nnz = 0;
+        }
+    }
+    if (rows > 0)
+    {
+        if (nnz == 0)
+        {
+            if (!out.empty()) out.back() += rows;
+        }
+        else
+            out.push_back(rows);
+    }
+    return out;
+}
+
+void sep_tblock_level_row_csr(CompressedBlock &b, const std::vector<u64> &rows_of)
+{
+    Level &L = b.blb;
+    L = Level();
+    u64 sum = 0, mx = 0;
+    for (u64 n : rows_of)
+    {
+        sum += n;
+        mx = std::max(mx, n);
+    }
+    L.first_row.dt = suitable_dtype(sum + 1);
+    L.row_num.dt = suitable_dtype(mx);
+    L.coo_begin.dt = suitable_dtype(b.col.size());
+    u64 r = 0;
+    for (u64 n : rows_of)
+    {
+        const u64 r1 = std::min(r + n, b.n_rows);
+        if (r < b.n_rows && b.rowptr[r1] > b.rowptr[r]) // blocks without non-zeros are dropped
+        {
+            L.first_row.v.push_back(r);
+            L.row_num.v.push_back(n);
+            L.coo_begin.v.push_back(b.rowptr[r]);
+        }
+        r += n;
+    }
+    L.coo_begin.v.push_back(b.col.size());
+    L.block_num = L.first_row.v.size();
+    L.built = true;
+}
+
+void sep_tblock_level_col_fixed(CompressedBlock &b, u64 c)
+{
+    // one BLB per non-empty row first (one_row_sep_tblock_level_row_csr), then every row is cut at
+    // the cumulative chunk sizes of col_block_size_of_each_row and at its end
+    Level &L = b.blb;
+    L = Level();
+    L.first_row.dt = suitable_dtype(b.n_rows + 1);
+    L.row_num.dt = ASP_U8;
+    L.coo_begin.dt = suitable_dtype(b.col.size());
+    for (u64 r = 0; r < b.n_rows; r++)
+    {
+        const u64 n = b.rowptr[r + 1] - b.rowptr[r];
+        if (n == 0) continue;
+        const u64 full = n / c, rem = n % c;
+        // nominal sizes: `full` chunks of c; remainder >= c/2 -> one more chunk; else merged into the
+        // last chunk (or the only one)
+        std::vector<u64> sizes(full, c);
+        if (rem >= c / 2) sizes.push_back(c);
+        else if (sizes.empty()) sizes.push_back(c);
+        else sizes.back() = 2 * c;
+        u64 beg = b.rowptr[r], k = 0, acc = 0;
+        for (u64 i = 0; i < n; i++)
+        {
+            if (i == acc + sizes[k] - 1)
+            {
+                L.first_row.v.push_back(r);
+                L.coo_begin.v.push_back(beg);
+                beg = b.rowptr[r] + i + 1;
+                acc += sizes[k];
+                k++;
+                if (k >= sizes.size() && i + 1 < n) k = sizes.size() - 1; // not reached with the sizes above
+            }
+        }
+        if (beg != b.rowptr[r + 1])
+        {
+            L.first_row.v.push_back(r);
+            L.coo_begin.v.push_back(beg);
+        }
+    }
+    L.row_num.v.assign(L.first_row.v.size(), 1);
+    L.coo_begin.v.push_back(b.col.size());
+    L.block_num = L.first_row.v.size();
+    L.built = true;
+    b.share_row_with_other_block = true;
+}
+
+void sep_warp_level_row_csr(CompressedBlock &b, const std::vector<std::vector<u64>> &rows_of)
+{
+    Level &B = b.blb;
+    Level &W = b.wlb;
+    W = Level();
+    u64 max_first_row = 0, max_coo_begin = 0, max_size = 0;
+    B.index.v.assign(1, 0);
+    for (u64 i = 0; i < B.block_num; i++)
+    {
+        const u64 br0 = B.first_row.v[i];
+        const u64 c0 = B.coo_begin.v[i], c1 = B.coo_begin.v[i + 1];
+        u64 made = 0;
+        if (i < rows_of.size())
+        {
+            // WLBs that own at least one non-zero, in row order
+            u64 r = 0;
+            for (u64 n : rows_of[i])
+            {
+                const u64 g0 = std::min(br0 + r, b.n_rows), g1 = std::min(br0 + r + n, b.n_rows);
+                const u64 a = std::max(b.rowptr[g0], c0), e = std::min(b.rowptr[g1], c1);
+                if (e > a)
+                {
+                    W.first_row.v.push_back(r);
+                    W.row_num.v.push_back(n);
+                    W.coo_begin.v.push_back(a - c0);
+                    max_first_row = std::max(max_first_row, r);
+                    max_coo_begin = std::max(max_coo_begin, a - c0);
+                    made++;
+                }
+                r += n;
+            }
+        }
+        else
+        {
+            W.first_row.v.push_back(0);
+            W.row_num.v.push_back(B.row_num.v[i]);
+            W.coo_begin.v.push_back(0);
+            made = 1;
+        }
+        B.index.v.push_back(B.index.v.back() + made);
+    }
+    W.block_num = W.first_row.v.size();
+    // block sizes: distance to the next WLB of the same BLB, the last one takes the rest
+    W.coo_size.v.resize(W.block_num);
+    for (u64 i = 0; i < B.block_num; i++)
+    {
+        const u64 nnz_b = B.coo_begin.v[i + 1] - B.coo_begin.v[i];
+        for (u64 w = B.index.v[i]; w < B.index.v[i + 1]; w++)
+        {
+            const u64 e = (w + 1 < B.index.v[i + 1]) ? W.coo_begin.v[w + 1] : nnz_b;
+            W.coo_size.v[w] = e - W.coo_begin.v[w];
+            max_size = std::max(max_size, W.coo_size.v[w]);
+        }
+    }
+    B.index.dt = suitable_dtype(B.index.v.back());
+    W.first_row.dt = suitable_dtype(max_first_row + 1);
+    W.row_num.dt = suitable_dtype(max_size);
+    W.coo_begin.dt = suitable_dtype(max_coo_begin);
+    W.coo_size.dt = suitable_dtype(max_size);
+    W.built = true;
+}
+
+std::vector<std::vector<u64>> wlb_rows_evenly(const CompressedBlock &b, u64 rows)
+{
+    std::vector<std::vector<u64>> out;
+    for (u64 i = 0; i < b.blb.block_num; i++)
+    {
+        const u64 n = b.blb.row_num.v[i];
+        std::vector<u64> v(n / rows, rows);
+        if (n % rows) v.push_back(n % rows);
+        out.push_back(v);
+    }
+    return out;
+}
+
+void sep_warp_level_col_fixed(CompressedBlock &b, u64 c)
+{
+    // one WLB per non-empty row of every BLB first (one_row_sep_warp_level_row_csr), then every row is
+    // cut into chunks of c non-zeros, the last chunk taking what is left
+    Level &B = b.blb;
+    Level &W = b.wlb;
+    W = Level();
+    u64 max_first_row = 0, max_coo_begin = 0, max_size = 0;
+    B.index.v.assign(1, 0);
+    for (u64 i = 0; i < B.block_num; i++)
+    {
+        const u64 br0 = B.first_row.v[i], rows = B.row_num.v[i];
+        const u64 c0 = B.coo_begin.v[i], c1 = B.coo_begin.v[i + 1];
+        u64 made = 0;
+        for (u64 r = 0; r < rows && br0 + r < b.n_rows; r++)
+        {
+            const u64 a = std::max(b.rowptr[br0 + r], c0), e = std::min(b.rowptr[br0 + r + 1], c1);
+            for (u64 p = a; p < e; p += c)
+            {
+                const u64 sz = std::min(c, e - p);
+                W.first_row.v.push_back(r);
+                W.coo_begin.v.push_back(p - c0);
+                W.coo_size.v.push_back(sz);
+                max_first_row = std::max(max_first_row, r);
+                if (made > 0) max_coo_begin = std::max(max_coo_begin, p - c0);
+                max_size = std::max(max_size, sz);
+                made++;
+            }
+        }
+        B.index.v.push_back(B.index.v.back() + made);
+    }
+    W.block_num = W.first_row.v.size();
+    W.row_num.v.assign(W.block_num, 1);
+    B.index.dt = suitable_dtype(B.index.v.back());
+    W.first_row.dt = suitable_dtype(max_first_row + 1);
+    W.row_num.dt = ASP_U8;
+    W.coo_begin.dt = suitable_dtype(max_coo_begin);
+    W.coo_size.dt = suitable_dtype(max_size);
+    W.built = true;
+    b.share_row_with_other_warp = true;
+}
+
+void sep_thread_level_col_ell_with_padding(CompressedBlock &b, u64 tlb_size)
+{
+    Level &B = b.blb;
+    Level &W = b.wlb;
+    Level &T = b.tlb;
+    T = Level();
+    const int es = b.val.es;
+    // pass 1: per WLB the TLB size, TLBs per row (rounded up, then round-robin fillers from the
+    // WLB's first row until the WLB holds a multiple of 32 TLBs), padded sizes
+    std::vector<u64> wlb_S(W.block_num), wlb_tlb0(W.block_num + 1, 0), wlb_pad0(W.block_num + 1, 0);
+    std::vector<u64> blb_first(B.block_num + 1, 0);
+    u64 max_S = 0;
+    bool share_thread = tlb_size != 0;
+    for (u64 i = 0; i < B.block_num; i++)
+    {
+        for (u64 w = B.index.v[i]; w < B.index.v[i + 1]; w++)
+        {
+            const u64 r0 = B.first_row.v[i] + W.first_row.v[w], rows = W.row_num.v[w];
+            const u64 a = B.coo_begin.v[i] + W.coo_begin.v[w], e = a + W.coo_size.v[w];
+            u64 S = tlb_size;
+            if (S == 0)
+            {
+                for (u64 r = 0; r < rows; r++)
+                {
+                    const u64 lo = std::max(b.rowptr[std::min(r0 + r, b.n_rows)], a), hi = std::min(b.rowptr[std::min(r0 + r + 1, b.n_rows)], e);
+                    if (hi > lo) S = std::max(S, hi - lo);
+                }
+            }
+            u64 tl = 0;
+            for (u64 r = 0; r < rows; r++)
+            {
+                const u64 lo = std::max(b.rowptr[std::min(r0 + r, b.n_rows)], a), hi = std::min(b.rowptr[std::min(r0 + r + 1, b.n_rows)], e);
+                const u64 n = hi > lo ? hi - lo : 0;
+                tl += (n + S - 1) / S;
+            }
+            const u64 target = (tl + 31) / 32 * 32;
+            wlb_S[w] = S;
+            wlb_tlb0[w + 1] = wlb_tlb0[w] + target;
+            wlb_pad0[w + 1] = wlb_pad0[w] + target * S;
+            max_S = std::max(max_S, S);
+        }
+        blb_first[i + 1] = wlb_pad0[B.index.v[i + 1]];
+    }
+    const u64 n_tlb = wlb_tlb0[W.block_num], n_pad = wlb_pad0[W.block_num];
+    b.pad_col.assign(n_pad, 0);
+    b.pad_val.es = es;
+    b.pad_val.resize(n_pad);
+    T.first_row.v.resize(n_tlb);
+    u64 max_thread_first_row = 0, max_w_coo_begin = 0, max_w_size = 0;
+    std::vector<u64> new_w_begin(W.block_num), new_w_size(W.block_num);
+    // pass 2: fill the padded arrays (row-major inside the WLB) and the per-TLB first rows
+    for (u64 i = 0; i < B.block_num; i++)
+    {
+        for (u64 w = B.index.v[i]; w < B.index.v[i + 1]; w++)
+        {
+            const u64 r0 = B.first_row.v[i] + W.first_row.v[w], rows = W.row_num.v[w];
+            const u64 a = B.coo_begin.v[i] + W.coo_begin.v[w], e = a + W.coo_size.v[w];
+            const u64 S = wlb_S[w];
+            std::vector<u64> per_row(rows);
+            u64 tl = 0;
+            for (u64 r = 0; r < rows; r++)
+            {
+                const u64 lo = std::max(b.rowptr[std::min(r0 + r, b.n_rows)], a), hi = std::min(b.rowptr[std::min(r0 + r + 1, b.n_rows)], e);
+                const u64 n = hi > lo ? hi - lo : 0;
+                per_row[r] = (n + S - 1) / S;
+                tl += per_row[r];
+            }
+            const u64 target = wlb_tlb0[w + 1] - wlb_tlb0[w];
+            for (u64 k = 0, rr = 0; k < target - tl; k++, rr = (rr + 1) % rows) per_row[rr]++;
+            u64 out = wlb_pad0[w], t = wlb_tlb0[w];
+            for (u64 r = 0; r < rows; r++)
+            {
+                const u64 lo = std::max(b.rowptr[std::min(r0 + r, b.n_rows)], a), hi = std::min(b.rowptr[std::min(r0 + r + 1, b.n_rows)], e);
+                const u64 n = hi > lo ? hi - lo : 0;
+                const u64 tgt = per_row[r] * S;
+                if (n > 0)
+                {
+                    memcpy(&b.pad_col[out], &b.col[lo], n * sizeof(u32));
+                    memcpy(&b.pad_val.b[out * es], &b.val.b[lo * es], n * es);
+                    const u32 last = b.col[hi - 1];
+                    for (u64 k = n; k < tgt; k++) b.pad_col[out + k] = last; // value stays 0
+                }
+                else
+                    for (u64 k = 0; k < tgt; k++) b.pad_col[out + k] = (u32)b.min_col;
+                out += tgt;
+                if (per_row[r] >= 2) share_thread = true;
+                for (u64 k = 0; k < per_row[r]; k++) T.first_row.v[t++] = r;
+                if (per_row[r] > 0) max_thread_first_row = std::max(max_thread_first_row, r);
+            }
+            new_w_size[w] = target * S;
+            new_w_begin[w] = (w == B.index.v[i]) ? 0 : new_w_begin[w - 1] + new_w_size[w - 1];
+            if (w != B.index.v[i]) max_w_coo_begin = std::max(max_w_coo_begin, new_w_begin[w]);
+            max_w_size = std::max(max_w_size, new_w_size[w]);
+        }
+    }
+    // the BLB / WLB offsets now refer to the padded arrays (op_manager.cc:3639-3680)
+    B.coo_begin.v = blb_first;
+    B.coo_begin.dt = suitable_dtype(n_pad);
+    W.coo_begin.v = new_w_begin;
+    W.coo_begin.dt = suitable_dtype(max_w_coo_begin);
+    W.coo_size.v = new_w_size;
+    W.coo_size.dt = suitable_dtype(max_w_size);
+    W.index.v = wlb_tlb0;
+    W.index.dt = suitable_dtype(n_tlb);
+    T.block_num = n_tlb;
+    T.first_row.dt = suitable_dtype(max_thread_first_row + 1);
+    T.coo_size.v = wlb_S;
+    T.coo_size.dt = suitable_dtype(max_S);
+    T.built = true;
+    b.padded = true;
+    b.tlb_is_nnz_div = false;
+    if (share_thread) b.share_row_with_other_thread = true;
+}
+
+void sep_thread_level_acc_to_nnz(CompressedBlock &b, u64 S)
+{
+    // equal-nnz TLBs regardless of row boundaries; columns and values are used as they are (no padding
+    // here: the CSR5-like templates pad to whole warps themselves)
+    Level &T = b.tlb;
+    T = Level();
+    const u64 nnz = b.col.size();
+    T.block_num = (nnz + S - 1) / S;
+    T.coo_size.v.assign(b.wlb.block_num, S);
+    T.coo_size.dt = suitable_dtype(S);
+    T.built = true;
+    b.tlb_is_nnz_div = true;
+    b.padded = false;
+}
+
+void complete_each_level_blocking(CompressedBlock &b)
+{
+    if (!b.blb.built) sep_tblock_level_row_csr(b, std::vector<u64>(1, b.n_rows));
+    if (!b.wlb.built) sep_warp_level_row_csr(b, std::vector<std::vector<u64>>());
+    if (!b.tlb.built) sep_thread_level_col_ell_with_padding(b, 1);
+}
+
+} // namespace host
+} // namespace asp

@@ -1,0 +1,416 @@
+// C ABI of the host side (include/asp_b200_host.h): matrix construction, Operator Graph
+// execution from a textual spec, access to the lowered templates.
+#include <string.h>
+
+#include <map>
+#include <new>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../../include/asp_b200_host.h"
+#include "format.hpp"
+
+using namespace asp::host;
+
+struct asp_matrix
+{
+    std::unique_ptr<Matrix> m;
+};
+
+struct asp_format
+{
+    std::unique_ptr<Matrix> m; // the transformed copy (owns the shared permutation)
+    std::vector<TemplateData> subs;
+    std::vector<std::vector<asp_array_desc>> descs;
+};
+
+namespace
+{
+thread_local std::string g_host_error;
+asp_status hfail(asp_status s, const std::string &msg)
+{
+    g_host_error = msg;
+    return s;
+}
+
+struct SubSpec
+{
+    std::vector<std::vector<std::string>> nodes;
+    std::string templ;
+    long tblock = -1, threads = -1, reduce = -1;
+};
+
+int template_of_name(const std::string &k)
+{
+    static const std::map<std::string, int> tab = {
+        {"K1", ASP_DIRECT_ATOM_TEMPLATE},
+        {"K2", ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS},
+        {"K3", ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS},
+        {"K4", ASP_DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE},
+        {"K5", ASP_SHARED_MEMORY_TEMPLATE},
+        {"K6", ASP_SHARED_MEMORY_TEMPLATE_WARP_COMPRESS},
+        {"K7", ASP_SHARED_MEMORY_LONG_ROW_TEMPLATE},
+        {"K8", ASP_SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE},
+        {"K9", ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE},
+        {"K10", ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE},
+        {"EMPTY", ASP_EMPTY_TEMPLATE},
+    };
+    auto it = tab.find(k);
+    return it == tab.end() ? -1 : it->second;
+}
+
+bool apply_sub_node(CompressedBlock &b, const std::vector<std::string> &tok, std::string &err)
+{
+    auto L = [&](size_t i) -> u64 { return i < tok.size() ? strtoull(tok[i].c_str(), nullptr, 10) : 0; };
+    const std::string &op = tok[0];
+    // the reference inserts the default tilings of the upper levels before a lower-level node
+    auto need_blb = [&]() {
+        if (!b.blb.built) sep_tblock_level_row_csr(b, std::vector<u64>(1, b.n_rows));
+    };
+    auto need_wlb = [&]() {
+        need_blb();
+        if (!b.wlb.built) sep_warp_level_row_csr(b, std::vector<std::vector<u64>>());
+    };
+    if (op == "row_padding")
+    {
+        if (L(1) == 0 || L(2) == 0 || b.blb.built) return err = "row_padding needs <multiple> <row_len> and must come first", false;
+        row_padding(b, L(1), L(2));
+    }
+    else if (op == "blb_row_evenly")
+    {
+        if (L(1) == 0 || b.blb.built) return err = "bad blb_row_evenly", false;
+        sep_tblock_level_row_csr(b, blb_rows_evenly(b, L(1)));
+    }
+    else if (op == "blb_row_nnz")
+    {
+        if (L(1) == 0 || b.blb.built) return err = "bad blb_row_nnz", false;
+        sep_tblock_level_row_csr(b, blb_rows_by_nnz_low_bound(b, L(1)));
+    }
+    else if (op == "blb_col_fixed")
+    {
+        if (L(1) == 0 || b.blb.built) return err = "bad blb_col_fixed", false;
+        sep_tblock_level_col_fixed(b, L(1));
+    }
+    else if (op == "wlb_row_evenly")
+    {
+        if (L(1) == 0 || b.wlb.built) return err = "bad wlb_row_evenly", false;
+        need_blb();
+        sep_warp_level_row_csr(b, wlb_rows_evenly(b, L(1)));
+    }
+    else if (op == "wlb_col_fixed")
+    {
+        if (L(1) == 0 || b.wlb.built) return err = "bad wlb_col_fixed", false;
+        need_blb();
+        sep_warp_level_col_fixed(b, L(1));
+    }
+    else if (op == "tlb_row")
+    {
+        if (b.tlb.built) return err = "TLB level already tiled", false;
+        need_wlb();
+        sep_thread_level_col_ell_with_padding(b, 0);
+    }
+    else if (op == "tlb_col_fixed")
+    {
+        if (L(1) == 0 || b.tlb.built) return err = "bad tlb_col_fixed", false;
+        need_wlb();
+        sep_thread_level_col_ell_with_padding(b, L(1));
+    }
+    else if (op == "tlb_nnz")
+    {
+        if (L(1) == 0 || b.blb.built || b.wlb.built || b.tlb.built) return err = "tlb_nnz needs an untiled sub-matrix", false;
+        need_wlb();
+        sep_thread_level_acc_to_nnz(b, L(1));
+    }
+    else
+        return err = "unknown compressed-view node " + op, false;
+    return true;
+}
+} // namespace
+
+extern "C" {
+
+const char *asp_host_last_error(void) { return g_host_error.c_str(); }
+
+asp_status asp_matrix_from_csr(uint64_t n_rows, uint64_t n_cols, const int64_t *indptr, const uint32_t *indices, const void *values, int val_dtype, asp_matrix **out)
+{
+    if (!out || !indptr || (!indices && indptr[n_rows] > 0) || (!values && indptr[n_rows] > 0)) return hfail(ASP_ERR_INVALID_ARG, "NULL argument");
+    *out = nullptr;
+    if (val_dtype != ASP_F32 && val_dtype != ASP_F64) return hfail(ASP_ERR_UNSUPPORTED, "values must be f32 or f64");
+    if (n_rows == 0 || n_cols == 0 || n_cols > 0xffffffffull) return hfail(ASP_ERR_INVALID_ARG, "bad shape");
+    if (indptr[0] != 0) return hfail(ASP_ERR_INVALID_ARG, "indptr[0] != 0");
+    for (uint64_t r = 0; r < n_rows; r++)
+    {
+        if (indptr[r + 1] < indptr[r]) return hfail(ASP_ERR_INVALID_ARG, "indptr decreases");
+        for (int64_t k = indptr[r]; k < indptr[r + 1]; k++)
+        {
+            if (indices[k] >= n_cols) return hfail(ASP_ERR_BOUNDS, "column index outside the matrix");
+            if (k > indptr[r] && indices[k] < indices[k - 1]) return hfail(ASP_ERR_INVALID_ARG, "columns are not sorted inside a row");
+        }
+    }
+    if (indptr[n_rows] == 0) return hfail(ASP_ERR_INVALID_ARG, "matrix without non-zeros");
+    asp_matrix *h = new (std::nothrow) asp_matrix();
+    if (!h) return hfail(ASP_ERR_ALLOC, "host allocation failed");
+    try
+    {
+        h->m = matrix_from_csr(n_rows, n_cols, indptr, indices, values, val_dtype);
+    }
+    catch (const std::bad_alloc &)
+    {
+        delete h;
+        return hfail(ASP_ERR_ALLOC, "host allocation failed");
+    }
+    *out = h;
+    return ASP_OK;
+}
+
+asp_status asp_matrix_from_coo_file(const char *path, int val_dtype, asp_matrix **out)
+{
+    if (!out || !path) return hfail(ASP_ERR_INVALID_ARG, "NULL argument");
+    *out = nullptr;
+    if (val_dtype != ASP_F32 && val_dtype != ASP_F64) return hfail(ASP_ERR_UNSUPPORTED, "values must be f32 or f64");
+    std::string err;
+    std::unique_ptr<Matrix> m;
+    try
+    {
+        m = matrix_from_coo_file(path, val_dtype, err);
+    }
+    catch (const std::bad_alloc &)
+    {
+        return hfail(ASP_ERR_ALLOC, "host allocation failed");
+    }
+    if (!m) return hfail(ASP_ERR_INVALID_ARG, err);
+    if (m->nnz == 0) return hfail(ASP_ERR_INVALID_ARG, "matrix without non-zeros");
+    asp_matrix *h = new (std::nothrow) asp_matrix();
+    if (!h) return hfail(ASP_ERR_ALLOC, "host allocation failed");
+    h->m = std::move(m);
+    *out = h;
+    return ASP_OK;
+}
+
+void asp_matrix_destroy(asp_matrix *m) { delete m; }
+uint64_t asp_matrix_rows(const asp_matrix *m) { return m ? m->m->n_rows : 0; }
+uint64_t asp_matrix_cols(const asp_matrix *m) { return m ? m->m->n_cols : 0; }
+uint64_t asp_matrix_nnz(const asp_matrix *m) { return m ? m->m->nnz : 0; }
+
+asp_status asp_graph_execute(const asp_matrix *in, const char *spec, asp_format **out)
+{
+    if (!in || !spec || !out) return hfail(ASP_ERR_INVALID_ARG, "NULL argument");
+    *out = nullptr;
+    std::vector<std::vector<std::string>> dense_ops;
+    std::map<long, SubSpec> subs;
+    {
+        std::istringstream f(spec);
+        std::string line;
+        while (std::getline(f, line))
+        {
+            const size_t h = line.find('#');
+            if (h != std::string::npos) line = line.substr(0, h);
+            std::istringstream is(line);
+            std::vector<std::string> tok;
+            std::string w;
+            while (is >> w) tok.push_back(w);
+            if (tok.empty()) continue;
+            if (tok[0] == "dtype" || tok[0] == "fix_values") continue; // oracle-driver directives
+            if (tok[0] == "dense" && tok.size() >= 2) dense_ops.push_back(std::vector<std::string>(tok.begin() + 1, tok.end()));
+            else if (tok[0] == "sub" && tok.size() >= 3)
+            {
+                const long id = tok[1] == "all" ? -1 : atol(tok[1].c_str());
+                SubSpec &s = subs[id];
+                if (tok[2] == "template")
+                {
+                    if (tok.size() < 4) return hfail(ASP_ERR_INVALID_ARG, "template without a name");
+                    s.templ = tok[3];
+                    if (tok.size() > 4) s.tblock = atol(tok[4].c_str());
+                    if (tok.size() > 5) s.threads = atol(tok[5].c_str());
+                    if (tok.size() > 6) s.reduce = atol(tok[6].c_str());
+                }
+                else
+                    s.nodes.push_back(std::vector<std::string>(tok.begin() + 2, tok.end()));
+            }
+            else
+                return hfail(ASP_ERR_INVALID_ARG, "bad directive: " + line);
+        }
+    }
+    try
+    {
+        std::unique_ptr<asp_format> F(new asp_format());
+        F->m.reset(new Matrix(*in->m));
+        Matrix &m = *F->m;
+        bool compressed = false;
+        for (const std::vector<std::string> &tok : dense_ops)
+        {
+            if (compressed) return hfail(ASP_ERR_INVALID_ARG, "dense-view node after compress");
+            if (tok[0] == "sort")
+            {
+                const u64 step = tok.size() > 1 ? strtoull(tok[1].c_str(), nullptr, 10) : 1;
+                if (step == 0 || m.is_sorted || m.is_blocked) return hfail(ASP_ERR_INVALID_ARG, "bad dense sort");
+                dense_row_coarse_sort(m, step);
+            }
+            else if (tok[0] == "rowdiv_exp")
+            {
+                if (tok.size() < 4 || m.is_blocked) return hfail(ASP_ERR_INVALID_ARG, "bad dense rowdiv_exp");
+                const u64 lo = strtoull(tok[1].c_str(), nullptr, 10), hi = strtoull(tok[2].c_str(), nullptr, 10), rate = strtoull(tok[3].c_str(), nullptr, 10);
+                if (lo == 0 || hi < lo || rate < 2) return hfail(ASP_ERR_INVALID_ARG, "bad dense rowdiv_exp parameters");
+                dense_row_div(m, row_div_position_exponential(m, lo, hi, rate));
+            }
+            else if (tok[0] == "compress")
+            {
+                compress_dense_view(m);
+                compressed = true;
+            }
+            else
+                return hfail(ASP_ERR_INVALID_ARG, "unknown dense-view node " + tok[0]);
+        }
+        if (!compressed) compress_dense_view(m);
+        // the dense view is no longer needed once every block holds its slice
+        std::vector<u32>().swap(m.col);
+        std::vector<uint8_t>().swap(m.val.b);
+        const size_t nsub = m.blocks.size();
+        F->subs.resize(nsub);
+        for (size_t i = 0; i < nsub; i++)
+        {
+            const SubSpec *s = nullptr;
+            if (subs.count((long)i)) s = &subs[(long)i];
+            else if (subs.count(-1)) s = &subs[-1];
+            else return hfail(ASP_ERR_INVALID_ARG, "no spec for sub-matrix " + std::to_string(i));
+            CompressedBlock &b = m.blocks[i];
+            std::string err;
+            for (const std::vector<std::string> &tok : s->nodes)
+                if (!apply_sub_node(b, tok, err)) return hfail(ASP_ERR_INVALID_ARG, err);
+            complete_each_level_blocking(b);
+            const int type = template_of_name(s->templ);
+            if (type < 0) return hfail(ASP_ERR_INVALID_ARG, "unknown template " + s->templ);
+            if (type == ASP_EMPTY_TEMPLATE)
+            {
+                F->subs[i] = TemplateData();
+                continue;
+            }
+            if (!init_template(m, i, type, F->subs[i], err)) return hfail(ASP_ERR_UNSUPPORTED, err);
+            if (s->tblock > 0) F->subs[i].tblock_num = s->tblock;
+            if (s->threads > 0) F->subs[i].thread_num_in_block = s->threads;
+            if (s->reduce > 0) F->subs[i].thread_num_of_row_reduce = s->reduce;
+            // the tiled intermediate is not needed once the template owns its arrays
+            std::vector<u32>().swap(b.pad_col);
+            std::vector<uint8_t>().swap(b.pad_val.b);
+            std::vector<u32>().swap(b.col);
+            std::vector<uint8_t>().swap(b.val.b);
+            std::vector<u64>().swap(b.tlb.first_row.v);
+        }
+        // C-ABI descriptors over the template arrays
+        F->descs.resize(nsub);
+        for (size_t i = 0; i < nsub; i++)
+        {
+            for (const TemplateArray &a : F->subs[i].arrays)
+            {
+                asp_array_desc d;
+                memset(&d, 0, sizeof(d));
+                d.role = a.role;
+                d.dtype = a.dt;
+                d.host_ptr = a.data();
+                d.len = a.len;
+                d.compress = a.comp.kind;
+                d.coef = a.comp.coef;
+                d.icpt = a.comp.icpt;
+                d.cycle = a.comp.cycle;
+                d.n_branch = (int32_t)a.comp.val.size();
+                for (size_t k = 0; k < a.comp.val.size() && k < ASP_MAX_BRANCH; k++)
+                {
+                    d.branch_lo[k] = a.comp.lo[k];
+                    d.branch_hi[k] = a.comp.hi[k];
+                    d.branch_val[k] = a.comp.val[k];
+                }
+                F->descs[i].push_back(d);
+            }
+        }
+        *out = F.release();
+    }
+    catch (const std::bad_alloc &)
+    {
+        return hfail(ASP_ERR_ALLOC, "host allocation failed");
+    }
+    return ASP_OK;
+}
+
+void asp_format_destroy(asp_format *f) { delete f; }
+int asp_format_num_subs(const asp_format *f) { return f ? (int)f->subs.size() : 0; }
+
+asp_status asp_format_global_perm(const asp_format *f, const void **ptr, int *dtype, uint64_t *len)
+{
+    if (!f || !ptr || !dtype || !len) return hfail(ASP_ERR_INVALID_ARG, "NULL argument");
+    if (f->m->is_sorted)
+    {
+        *ptr = f->m->sorted_row_index->data();
+        *dtype = f->m->perm_dt;
+        *len = f->m->n_rows;
+    }
+    else
+    {
+        *ptr = nullptr;
+        *dtype = ASP_U8;
+        *len = 0;
+    }
+    return ASP_OK;
+}
+
+asp_status asp_format_sub_info(const asp_format *f, int sub, asp_sub_info *out)
+{
+    if (!f || !out || sub < 0 || sub >= (int)f->subs.size()) return hfail(ASP_ERR_INVALID_ARG, "bad sub-matrix id");
+    const CompressedBlock &b = f->m->blocks[sub];
+    const TemplateData &t = f->subs[sub];
+    out->min_row = b.min_row;
+    out->max_row = b.max_row;
+    out->min_col = b.min_col;
+    out->max_col = b.max_col;
+    out->begin_coo = b.begin_coo;
+    out->end_coo = b.end_coo;
+    out->n_blb = b.blb.block_num;
+    out->n_wlb = b.wlb.block_num;
+    out->n_tlb = b.tlb.block_num;
+    out->template_type = t.template_type;
+    out->n_arrays = (int32_t)t.arrays.size();
+    return ASP_OK;
+}
+
+asp_status asp_format_plan_descs(const asp_format *f, asp_plan_desc *descs)
+{
+    if (!f || !descs) return hfail(ASP_ERR_INVALID_ARG, "NULL argument");
+    for (size_t i = 0; i < f->subs.size(); i++)
+    {
+        const TemplateData &t = f->subs[i];
+        asp_plan_desc &d = descs[i];
+        memset(&d, 0, sizeof(d));
+        d.template_type = t.template_type;
+        d.val_dtype = f->m->val_dt;
+        d.n_rows = f->m->n_rows;
+        d.n_cols = f->m->n_cols;
+        d.first_row = t.first_row;
+        d.first_col = t.first_col;
+        d.true_nnz = t.true_nnz;
+        d.n_arrays = (int32_t)f->descs[i].size();
+        d.arrays = f->descs[i].data();
+        d.effective_num = t.effective_num;
+        d.tlb_size = t.tlb_size;
+        d.bits_word = t.bits_word;
+        d.bits_flag = t.bits_flag;
+        d.bits_row = t.bits_row;
+        d.bits_off = t.bits_off;
+        d.is_atom_add = t.is_atom_add ? 1 : 0;
+        d.sort_kind = t.sort_kind;
+        d.tblock_num = t.tblock_num;
+        d.thread_num_in_block = t.thread_num_in_block;
+        d.thread_num_of_row_reduce = t.thread_num_of_row_reduce;
+    }
+    return ASP_OK;
+}
+
+double asp_format_padding_rate(const asp_format *f, int sub)
+{
+    if (!f || sub < 0 || sub >= (int)f->subs.size()) return 0.0;
+    const TemplateData &t = f->subs[sub];
+    const TemplateArray *v = t.find(ASP_ARR_VAL);
+    if (!v || t.true_nnz == 0) return 0.0;
+    return (double)v->len / (double)t.true_nnz;
+}
+
+} // extern "C"

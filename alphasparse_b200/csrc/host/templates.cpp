@@ -1,0 +1,429 @@
+// init_<template> + try_all_compress for the ten reduce templates: flatten a tiled sub-matrix into
+// the arrays a kernel family reads, apply the row permutation where the reference applies it on
+// the host, re-interleave values / column indices, detect closed forms. Array contents, element
+// types and closed forms equal the reference's (the ten *_op*.cc files and arr_optimization.cc).
+#include <string.h>
+
+#include <algorithm>
+
+#include "format.hpp"
+
+namespace asp
+{
+namespace host
+{
+
+// ---------------------------------------------------------------------------------------------
+// closed forms (arr_optimization.cc)
+// ---------------------------------------------------------------------------------------------
+bool detect_linear(const std::vector<u64> &a, ClosedForm &out)
+{
+    if (a.size() <= 1) return false;
+    if (a[1] < a[0]) return false;
+    const u64 coef = a[1] - a[0];
+    for (size_t i = 0; i + 1 < a.size(); i++)
+        if (a[i + 1] < a[i] || a[i + 1] - a[i] != coef) return false;
+    out = ClosedForm();
+    out.kind = ASP_COMPRESS_LINEAR;
+    out.coef = coef;
+    out.icpt = a[0];
+    return true;
+}
+
+bool detect_constant(const std::vector<u64> &a, ClosedForm &out)
+{
+    if (a.empty()) return false;
+    for (u64 v : a)
+        if (v != a[0]) return false;
+    out = ClosedForm();
+    out.kind = ASP_COMPRESS_CONSTANT;
+    out.icpt = a[0];
+    return true;
+}
+
+bool detect_branch(const std::vector<u64> &a, ClosedForm &out)
+{
+    // the reference asserts arr_size > 2 here (arr_optimization.cc:117) and aborts on shorter arrays;
+    // shorter arrays simply stay uncompressed
+    if (a.size() <= 2) return false;
+    ClosedForm f;
+    f.kind = ASP_COMPRESS_BRANCH;
+    f.lo.push_back(0);
+    f.val.push_back(a[0]);
+    for (size_t i = 0; i < a.size(); i++)
+    {
+        if (a[i] != f.val.back())
+        {
+            f.hi.push_back(i - 1);
+            f.lo.push_back(i);
+            f.val.push_back(a[i]);
+            if (f.hi.size() >= ASP_MAX_BRANCH) return false;
+        }
+    }
+    f.hi.push_back(a.size() - 1);
+    out = f;
+    return true;
+}
+
+bool detect_cycle_linear(const std::vector<u64> &a, u64 cycle, ClosedForm &out)
+{
+    if (!(cycle < a.size()) || a.size() % cycle != 0 || cycle <= 1) return false;
+    const u64 icpt = a[0], coef = a[1] - a[0];
+    for (size_t i = 0; i < a.size(); i++)
+    {
+        const u64 k = i % cycle;
+        if (k == 0) continue;
+        // the reference asserts divisibility inside this check (arr_optimization.cc:271); a
+        // mismatch is a plain "no" here
+        if (a[i] < icpt || (a[i] - icpt) % k != 0 || (a[i] - icpt) / k != coef) return false;
+    }
+    out = ClosedForm();
+    out.kind = ASP_COMPRESS_CYCLE_LINEAR;
+    out.cycle = cycle;
+    out.coef = coef;
+    out.icpt = icpt;
+    return true;
+}
+
+bool detect_cycle_increase(const std::vector<u64> &a, ClosedForm &out)
+{
+    if (a.size() <= 2) return false;
+    u64 cycle = 0;
+    for (size_t i = 0; i < a.size(); i++)
+        if (a[i] != a[0])
+        {
+            if (a[i] < a[0]) return false;
+            cycle = i;
+            break;
+        }
+    if (cycle == 0) return false; // all equal: the reference asserts here
+    if (a.size() % cycle != 0) return false;
+    for (size_t i = 0; i < a.size(); i++)
+        if (a[i] != a[0] + i / cycle) return false;
+    out = ClosedForm();
+    out.kind = ASP_COMPRESS_CYCLE_INCREASE;
+    out.cycle = cycle;
+    out.icpt = a[0];
+    return true;
+}
+
+namespace
+{
+std::vector<uint8_t> narrow(const std::vector<u64> &v, int dt)
+{
+    const int es = dtype_bytes(dt);
+    std::vector<uint8_t> out(v.size() * es);
+    switch (es)
+    {
+    case 1:
+        for (size_t i = 0; i < v.size(); i++) out[i] = (uint8_t)v[i];
+        break;
+    case 2:
+        for (size_t i = 0; i < v.size(); i++) ((uint16_t *)out.data())[i] = (uint16_t)v[i];
+        break;
+    case 4:
+        for (size_t i = 0; i < v.size(); i++) ((uint32_t *)out.data())[i] = (uint32_t)v[i];
+        break;
+    default: memcpy(out.data(), v.data(), v.size() * 8);
+    }
+    return out;
+}
+
+TemplateArray &add_meta(TemplateData &t, int role, const std::vector<u64> &v, int dt)
+{
+    t.arrays.emplace_back();
+    TemplateArray &a = t.arrays.back();
+    a.role = role;
+    a.dt = dt;
+    a.len = v.size();
+    a.bytes = narrow(v, dt);
+    return a;
+}
+
+// dst[k*n + i] = src[i*S + k] for one strip of n TLBs of size S (row-major -> TLB-interleaved)
+template <class D, class S_>
+void interleave_strip(D *dst, const S_ *src, u64 n, u64 S)
+{
+    const u64 TB = 256;
+#pragma omp parallel for schedule(static) if (n * S > (1u << 20))
+    for (u64 i0 = 0; i0 < n; i0 += TB)
+    {
+        const u64 i1 = std::min(n, i0 + TB);
+        for (u64 k = 0; k < S; k++)
+            for (u64 i = i0; i < i1; i++) dst[k * n + i] = (D)src[i * S + k];
+    }
+}
+
+struct NnzArrays
+{
+    std::vector<uint8_t> col, val;
+};
+
+void interleave_cols(uint8_t *dst, int col_dt, const u32 *src, u64 n, u64 S)
+{
+    switch (col_dt)
+    {
+    case ASP_U8: interleave_strip((uint8_t *)dst, src, n, S); break;
+    case ASP_U16: interleave_strip((uint16_t *)dst, src, n, S); break;
+    case ASP_U32: interleave_strip((uint32_t *)dst, src, n, S); break;
+    default: interleave_strip((uint64_t *)dst, src, n, S); break;
+    }
+}
+void interleave_vals(uint8_t *dst, int es, const uint8_t *src, u64 n, u64 S)
+{
+    if (es == 4) interleave_strip((uint32_t *)dst, (const uint32_t *)src, n, S);
+    else interleave_strip((uint64_t *)dst, (const uint64_t *)src, n, S);
+}
+
+void add_nnz_arrays(TemplateData &t, const CompressedBlock &b, std::vector<uint8_t> &col, std::vector<uint8_t> &val, u64 n)
+{
+    t.arrays.emplace_back();
+    TemplateArray &v = t.arrays.back();
+    v.role = ASP_ARR_VAL;
+    v.dt = t.val_dt;
+    v.len = n;
+    v.bytes.swap(val);
+    t.arrays.emplace_back();
+    TemplateArray &c = t.arrays.back();
+    c.role = ASP_ARR_COL_INDEX;
+    c.dt = b.col_dt;
+    c.len = n;
+    c.bytes.swap(col);
+}
+
+// global row (relative to the sub-matrix) of every TLB, in TLB order
+std::vector<u64> tlb_global_rows(const CompressedBlock &b, bool &adjacent_equal)
+{
+    const Level &B = b.blb, &W = b.wlb, &T = b.tlb;
+    std::vector<u64> rows(T.block_num);
+    for (u64 i = 0; i < B.block_num; i++)
+        for (u64 w = B.index.v[i]; w < B.index.v[i + 1]; w++)
+        {
+            const u64 base = B.first_row.v[i] + W.first_row.v[w];
+            for (u64 t = W.index.v[w]; t < W.index.v[w + 1]; t++) rows[t] = base + T.first_row.v[t];
+        }
+    adjacent_equal = false;
+    for (u64 t = 1; t < rows.size(); t++)
+        if (rows[t] == rows[t - 1])
+        {
+            adjacent_equal = true;
+            break;
+        }
+    return rows;
+}
+
+void common_head(const Matrix &m, const CompressedBlock &b, int type, TemplateData &t)
+{
+    t = TemplateData();
+    t.arrays.reserve(16); // references returned by add_meta stay valid while arrays are appended
+    t.template_type = type;
+    t.val_dt = m.val_dt;
+    t.first_row = b.min_row;
+    t.first_col = b.min_col;
+    t.true_nnz = b.end_coo - b.begin_coo + 1;
+    t.sort_kind = m.is_sorted ? ASP_SORT_GLOBAL : ASP_SORT_NONE;
+    t.n_blb = b.blb.block_num;
+    t.n_wlb = b.wlb.block_num;
+    t.n_tlb = b.tlb.block_num;
+    // sub-matrices that do not span all columns always accumulate atomically
+    t.is_atom_add = !(b.min_col == 0 && b.max_col == m.n_cols - 1);
+}
+
+void add_perm(const Matrix &m, TemplateData &t)
+{
+    if (!m.is_sorted) return;
+    t.arrays.emplace_back();
+    TemplateArray &a = t.arrays.back();
+    a.role = ASP_ARR_ROW_INDEX_BEFORE_SORT;
+    a.dt = m.perm_dt;
+    a.len = m.n_rows;
+    a.shared = m.sorted_row_index;
+}
+
+// effective unit count + host-side permutation of a row map (templates whose kernels do not read
+// row_index_before_sort): rows >= the dense row count belong to COMPRESSED_ROW_PADDING
+u64 effective_and_permute(const Matrix &m, const CompressedBlock &b, std::vector<u64> &rows)
+{
+    const u64 dense_rows = b.max_row - b.min_row + 1;
+    u64 eff = rows.size();
+    if (b.n_rows > dense_rows)
+        for (u64 i = 0; i < rows.size(); i++)
+            if (rows[i] >= dense_rows)
+            {
+                eff = i;
+                break;
+            }
+    if (m.is_sorted)
+        for (u64 i = 0; i < eff; i++) rows[i] = m.perm[rows[i] + b.min_row];
+    return eff;
+}
+
+void try_linear_then_cycle_increase(TemplateArray &a, const std::vector<u64> &v)
+{
+    if (!detect_linear(v, a.comp)) detect_cycle_increase(v, a.comp);
+}
+
+// ---- DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS (direct_atom_op_warp_block_compress.cc) --------
+bool init_k3(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::string &err)
+{
+    common_head(m, b, ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS, t);
+    const u64 S = b.tlb.coo_size.v[0];
+    for (u64 s : b.tlb.coo_size.v)
+        if (s != S)
+        {
+            err = "ELL-like template needs one global TLB size";
+            return false;
+        }
+    bool adj = false;
+    std::vector<u64> rows = tlb_global_rows(b, adj);
+    if (adj) t.is_atom_add = true;
+    const u64 n_pad = b.pad_col.size(), P = n_pad / S;
+    std::vector<uint8_t> col(n_pad * dtype_bytes(b.col_dt)), val(n_pad * b.val.es);
+    interleave_cols(col.data(), b.col_dt, b.pad_col.data(), P, S);
+    interleave_vals(val.data(), b.val.es, b.pad_val.b.data(), P, S);
+    t.effective_num = effective_and_permute(m, b, rows);
+    t.tlb_size = S;
+    u64 mx = 0;
+    for (u64 r : rows) mx = std::max(mx, r);
+    TemplateArray &rm = add_meta(t, ASP_ARR_GLOBAL_ROW_INDEX_OF_THREAD_LEVEL_BLOCK, rows, suitable_dtype(mx));
+    try_linear_then_cycle_increase(rm, rows);
+    add_perm(m, t);
+    add_nnz_arrays(t, b, col, val, n_pad);
+    return true;
+}
+
+// per-BLB view shared by the SELL-like and the row-grouped templates: TLB range and TLB size
+bool blb_tlb_ranges(const CompressedBlock &b, std::vector<u64> &thr, std::vector<u64> &size, std::string &err)
+{
+    const Level &B = b.blb, &W = b.wlb, &T = b.tlb;
+    thr.resize(B.block_num + 1);
+    size.resize(B.block_num);
+    for (u64 i = 0; i < B.block_num; i++)
+    {
+        const u64 w0 = B.index.v[i];
+        thr[i] = W.index.v[w0];
+        size[i] = T.coo_size.v[w0];
+        for (u64 w = w0; w < B.index.v[i + 1]; w++)
+            if (T.coo_size.v[w] != size[i])
+            {
+                err = "TLB size differs inside a BLB";
+                return false;
+            }
+    }
+    thr[B.block_num] = W.index.v[W.block_num];
+    return true;
+}
+
+void interleave_per_blb(const CompressedBlock &b, const std::vector<u64> &thr, const std::vector<u64> &size, std::vector<uint8_t> &col, std::vector<uint8_t> &val)
+{
+    const u64 n_pad = b.pad_col.size();
+    const int cb = dtype_bytes(b.col_dt), es = b.val.es;
+    col.assign(n_pad * cb, 0);
+    val.assign(n_pad * es, 0);
+    const u64 nb = b.blb.block_num;
+#pragma omp parallel for schedule(dynamic, 64)
+    for (u64 i = 0; i < nb; i++)
+    {
+        const u64 nz0 = b.blb.coo_begin.v[i], n = thr[i + 1] - thr[i];
+        interleave_cols(col.data() + nz0 * cb, b.col_dt, b.pad_col.data() + nz0, n, size[i]);
+        interleave_vals(val.data() + nz0 * es, es, b.pad_val.b.data() + nz0 * es, n, size[i]);
+    }
+}
+
+// ---- DIRECT_ATOM_TEMPLATE_WARP_COMPRESS (direct_atom_op_warp_compress.cc) --------------------
+bool init_k2(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::string &err)
+{
+    common_head(m, b, ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS, t);
+    std::vector<u64> thr, size;
+    if (!blb_tlb_ranges(b, thr, size, err)) return false;
+    bool adj = false;
+    std::vector<u64> rows = tlb_global_rows(b, adj);
+    if (adj) t.is_atom_add = true;
+    std::vector<uint8_t> col, val;
+    interleave_per_blb(b, thr, size, col, val);
+    t.effective_num = effective_and_permute(m, b, rows);
+    u64 mx = 0;
+    for (u64 r : rows) mx = std::max(mx, r);
+    TemplateArray &rm = add_meta(t, ASP_ARR_GLOBAL_ROW_INDEX_OF_THREAD_LEVEL_BLOCK, rows, suitable_dtype(mx));
+    try_linear_then_cycle_increase(rm, rows);
+    TemplateArray &bt = add_meta(t, ASP_ARR_BLOCK_BEGIN_THREAD_INDEX_OFFSET, thr, suitable_dtype(thr.back()));
+    detect_linear(thr, bt.comp);
+    std::vector<u64> bnz(b.blb.coo_begin.v.begin(), b.blb.coo_begin.v.begin() + b.blb.block_num);
+    TemplateArray &bn = add_meta(t, ASP_ARR_BLOCK_NZ_BEGIN_OFFSET, bnz, b.blb.coo_begin.dt);
+    detect_linear(bnz, bn.comp);
+    TemplateArray &ts = add_meta(t, ASP_ARR_THREAD_BLOCK_SIZE_IN_BLOCK, size, suitable_dtype(size.back()));
+    if (!detect_constant(size, ts.comp)) detect_branch(size, ts.comp);
+    add_perm(m, t);
+    add_nnz_arrays(t, b, col, val, b.pad_col.size());
+    return true;
+}
+
+// ---- SHARED_MEMORY_TEMPLATE_WARP_COMPRESS (shared_memory_op_warp_compress.cc) ----------------
+bool init_k6(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::string &err)
+{
+    common_head(m, b, ASP_SHARED_MEMORY_TEMPLATE_WARP_COMPRESS, t);
+    const Level &B = b.blb;
+    std::vector<u64> thr, size;
+    if (!blb_tlb_ranges(b, thr, size, err)) return false;
+    // BLBs that overlap in rows (column-divided BLBs) force atomics
+    u64 gmax = B.first_row.v[0] + B.row_num.v[0] - 1;
+    for (u64 i = 1; i < B.block_num; i++)
+    {
+        if (B.first_row.v[i] <= gmax)
+        {
+            t.is_atom_add = true;
+            break;
+        }
+        gmax = std::max(gmax, B.first_row.v[i] + B.row_num.v[i] - 1);
+    }
+    t.effective_num = b.max_row - b.min_row + 1;
+    bool adj = false;
+    std::vector<u64> rows = tlb_global_rows(b, adj);
+    std::vector<u64> roff(b.n_rows + 1, 0);
+    for (u64 r : rows) roff[r + 1]++;
+    for (u64 r = 0; r < b.n_rows; r++) roff[r + 1] += roff[r];
+    std::vector<uint8_t> col, val;
+    interleave_per_blb(b, thr, size, col, val); // every BLB, the last one included (the reference skips it)
+    TemplateArray &ro = add_meta(t, ASP_ARR_ROW_OFFSET_IN_THREAD_TMP_RESULT, roff, suitable_dtype(roff.back()));
+    std::vector<u64> brow(B.first_row.v);
+    brow.push_back(b.n_rows);
+    TemplateArray &br = add_meta(t, ASP_ARR_BLOCK_FIRST_ROW_INDEX, brow, suitable_dtype(b.n_rows));
+    TemplateArray &bt = add_meta(t, ASP_ARR_BLOCK_BEGIN_THREAD_INDEX_OFFSET, thr, suitable_dtype(thr.back()));
+    TemplateArray &ts = add_meta(t, ASP_ARR_THREAD_BLOCK_SIZE_IN_BLOCK, size, b.tlb.coo_size.dt);
+    std::vector<u64> bnz(B.coo_begin.v.begin(), B.coo_begin.v.begin() + B.block_num);
+    TemplateArray &bn = add_meta(t, ASP_ARR_BLOCK_NZ_BEGIN_OFFSET, bnz, B.coo_begin.dt);
+    detect_linear(thr, bt.comp);
+    if (!detect_constant(size, ts.comp)) detect_branch(size, ts.comp);
+    detect_linear(bnz, bn.comp);
+    detect_linear(brow, br.comp);
+    detect_linear(roff, ro.comp);
+    add_perm(m, t);
+    add_nnz_arrays(t, b, col, val, b.pad_col.size());
+    return true;
+}
+} // namespace
+
+bool init_template(const Matrix &m, size_t sub, int type, TemplateData &out, std::string &err)
+{
+    if (sub >= m.blocks.size())
+    {
+        err = "no such sub-matrix";
+        return false;
+    }
+    const CompressedBlock &b = m.blocks[sub];
+    if (!(b.blb.built && b.wlb.built && b.tlb.built))
+    {
+        err = "sub-matrix is not tiled at all three levels";
+        return false;
+    }
+    switch (type)
+    {
+    case ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS: return init_k3(m, b, out, err);
+    case ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS: return init_k2(m, b, out, err);
+    case ASP_SHARED_MEMORY_TEMPLATE_WARP_COMPRESS: return init_k6(m, b, out, err);
+    default: err = "template not implemented by the host lowering"; return false;
+    }
+}
+
+} // namespace host
+} // namespace asp
