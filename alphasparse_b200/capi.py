@@ -203,9 +203,11 @@ class PlanGroup:
     def launches(self) -> int:
         return sum(lib().asp_plan_launches(self._plans[i]) for i in range(self.n))
 
-    def spmv(self, d_x: int, d_y: int, zero_y: bool = True):
-        """Asynchronous y (+)= A x on device pointers (ints)."""
-        check(lib().asp_spmv(self.ctx.handle, self._plans, self.n, C.c_void_p(d_x), C.c_void_p(d_y), 1 if zero_y else 0))
+    def spmv(self, d_x: int, d_y: int, zero_y=True):
+        """Asynchronous y (+)= A x on device pointers (ints). zero_y: False / True / "auto"
+        (clear y only when a plan accumulates with atomics)."""
+        z = 2 if zero_y == "auto" else (1 if zero_y else 0)
+        check(lib().asp_spmv(self.ctx.handle, self._plans, self.n, C.c_void_p(d_x), C.c_void_p(d_y), z))
 
     def spmv_host(self, x: np.ndarray) -> np.ndarray:
         x = np.ascontiguousarray(x, dtype=self.val_dtype)
@@ -214,10 +216,11 @@ class PlanGroup:
         check(lib().asp_spmv_host(self.ctx.handle, self._plans, self.n, C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data)))
         return y
 
-    def time(self, warmup: int = 3, reps: int = 20, zero_y: bool = True, gflops_up_bound: float = 0.0):
+    def time(self, warmup: int = 3, reps: int = 20, zero_y="auto", gflops_up_bound: float = 0.0):
         ms = C.c_float()
         gf = C.c_float()
-        check(lib().asp_time(self.ctx.handle, self._plans, self.n, warmup, reps, 1 if zero_y else 0, gflops_up_bound, C.byref(ms), C.byref(gf)))
+        z = 2 if zero_y == "auto" else (1 if zero_y else 0)
+        check(lib().asp_time(self.ctx.handle, self._plans, self.n, warmup, reps, z, gflops_up_bound, C.byref(ms), C.byref(gf)))
         return ms.value, gf.value
 
     def close(self):

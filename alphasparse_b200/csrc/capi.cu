@@ -202,6 +202,20 @@ asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threa
     }
     if (tblock <= 0) tblock = 1;
     if (tblock > 2147483647LL) tblock = 2147483647LL;
+    if (t == ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS)
+    {
+        // the ELL-like kernel handles `vec` TLBs per thread and is compiled for at most 512 threads
+        // per CTA: fold wider requests into more CTAs and never launch CTAs without work
+        if (threads > 512)
+        {
+            tblock *= (threads + 511) / 512;
+            threads = 512;
+        }
+        const int64_t needed = (int64_t)((p->units_for_grid + (uint64_t)threads - 1) / (uint64_t)threads);
+        if (tblock > needed) tblock = needed > 0 ? needed : 1;
+        static const char *cap = getenv("ASP_ELL_MAX_GRID");
+        if (cap && atoll(cap) > 0 && tblock > atoll(cap)) tblock = atoll(cap);
+    }
     p->grid = (unsigned)tblock;
     p->block = (unsigned)threads;
     return ASP_OK;
@@ -487,7 +501,8 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
             a.effective = d.effective_num ? std::min<uint64_t>(d.effective_num, P) : P;
             if (d.tlb_size == 0 || P == 0 || P * d.tlb_size != nnz_pad) st = ASP_ERR_BOUNDS, why = "ELL-like: #TLB * TLB size != padded nnz";
             // TLBs per thread: the widest group that keeps 16-byte alignment of every k-slice
-            int v = p->val_is_f64 ? 4 : 8;
+            int v = 4;
+            if (const char *e = getenv("ASP_ELL_VEC")) v = atoi(e) > 0 ? atoi(e) : v;
             while (v > 1 && (P % v) != 0) v >>= 1;
             p->vec = v;
             p->units_for_grid = (P + v - 1) / v;
@@ -676,7 +691,10 @@ asp_status asp_spmv(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const voi
         if (plans[i]->templ != ASP_EMPTY_TEMPLATE && !first) first = plans[i];
     }
     if (!first) return ASP_OK;
-    if (zero_y) ASP_CUDA(cudaMemsetAsync(d_y, 0, first->n_rows * (first->val_is_f64 ? 8 : 4), ctx->stream));
+    bool clear = zero_y == 1;
+    if (zero_y == 2)
+        for (int i = 0; i < n_plans; i++) clear = clear || (plans[i]->templ != ASP_EMPTY_TEMPLATE && plans[i]->needs_zero);
+    if (clear) ASP_CUDA(cudaMemsetAsync(d_y, 0, first->n_rows * (first->val_is_f64 ? 8 : 4), ctx->stream));
     for (int i = 0; i < n_plans; i++)
     {
         asp_plan *p = plans[i];

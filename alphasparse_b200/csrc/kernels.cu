@@ -156,17 +156,46 @@ __device__ __forceinline__ VT warp_sum(VT v)
 // DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS (ELL-like): thread t owns row map[t]; element k of
 // TLB t sits at t + k*P, P = padded TLB count. V adjacent TLBs per thread give 16-byte loads.
 // ---------------------------------------------------------------------------------------------
-template <class VT, class CT, int V>
-__global__ void __launch_bounds__(1024) k_ell(const KArgs a)
+// KS > 0: the TLB size is a compile-time constant, so every value / index load of a thread is in
+// flight before the first gather of x is issued. KS == 0: any size, in predicated chunks of 4.
+template <class VT, int V>
+__device__ __forceinline__ void store_rows(VT *__restrict__ y, u64 row0, const VT (&acc)[V])
+{
+    if constexpr (sizeof(VT) * V >= 16)
+    {
+        constexpr int H = 16 / sizeof(VT);
+        typedef Vec<VT, H> P16;
+#pragma unroll
+        for (int h = 0; h < V / H; h++)
+        {
+            P16 t;
+#pragma unroll
+            for (int j = 0; j < H; j++) t.v[j] = acc[h * H + j];
+            *reinterpret_cast<P16 *>(y + row0 + h * H) = t;
+        }
+    }
+    else
+    {
+#pragma unroll
+        for (int j = 0; j < V; j++) y[row0 + j] = acc[j];
+    }
+}
+
+template <class VT, class CT, int V, int KS>
+__global__ void __launch_bounds__(512) k_ell(const KArgs a)
 {
     const VT *__restrict__ val = (const VT *)a.val;
     const CT *__restrict__ col = (const CT *)a.col;
     const VT *__restrict__ x = (const VT *)a.x + a.first_col;
     VT *__restrict__ y = (VT *)a.y;
     const u64 P = a.n_tlb;
-    const u32 S = a.tlb_size;
+    const u32 S = KS > 0 ? (u32)KS : a.tlb_size;
     const u64 ngroup = P / V;
     const u64 stride = (u64)gridDim.x * blockDim.x;
+    const u64 radd = a.row_add ? a.first_row : 0;
+    // consecutive TLBs map to consecutive rows: whole groups can be stored as vectors
+    const bool unit_rows = a.m[MS_ROW_OF_TLB].kind == MK_LINEAR && a.m[MS_ROW_OF_TLB].coef == 1 && !a.atomic &&
+                           ((a.m[MS_ROW_OF_TLB].icpt + radd) % V) == 0;
     for (u64 g = (u64)blockIdx.x * blockDim.x + threadIdx.x; g < ngroup; g += stride)
     {
         const u64 t0 = g * V;
@@ -176,24 +205,54 @@ __global__ void __launch_bounds__(1024) k_ell(const KArgs a)
         for (int j = 0; j < V; j++) acc[j] = 0;
         const VT *vp = val + t0;
         const CT *cp = col + t0;
-#pragma unroll 4
-        for (u32 k = 0; k < S; k++)
+        if constexpr (KS > 0)
         {
-            VT v[V];
-            CT c[V];
-            ld_stream_n<VT, V>(vp, v);
-            ld_stream_n<CT, V>(cp, c);
+            VT v[KS][V];
+            CT c[KS][V];
 #pragma unroll
-            for (int j = 0; j < V; j++) acc[j] += v[j] * __ldg(x + c[j]);
-            vp += P;
-            cp += P;
+            for (int k = 0; k < KS; k++)
+            {
+                ld_stream_n<VT, V>(vp + (u64)k * P, v[k]);
+                ld_stream_n<CT, V>(cp + (u64)k * P, c[k]);
+            }
+#pragma unroll
+            for (int k = 0; k < KS; k++)
+#pragma unroll
+                for (int j = 0; j < V; j++) acc[j] += v[k][j] * __ldg(x + c[k][j]);
         }
-        const u64 radd = a.row_add ? a.first_row : 0;
-#pragma unroll
-        for (int j = 0; j < V; j++)
+        else
         {
-            const u64 t = t0 + j;
-            if (t < a.effective) out_add(y, mget(a.m[MS_ROW_OF_TLB], t) + radd, acc[j], a.atomic != 0);
+            constexpr int U = 4;
+            for (u32 k0 = 0; k0 < S; k0 += U)
+            {
+                VT v[U][V];
+                CT c[U][V];
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (k0 + u < S)
+                    {
+                        ld_stream_n<VT, V>(vp + (u64)(k0 + u) * P, v[u]);
+                        ld_stream_n<CT, V>(cp + (u64)(k0 + u) * P, c[u]);
+                    }
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (k0 + u < S)
+                    {
+#pragma unroll
+                        for (int j = 0; j < V; j++) acc[j] += v[u][j] * __ldg(x + c[u][j]);
+                    }
+            }
+        }
+        if (unit_rows && t0 + V <= a.effective)
+            store_rows<VT, V>(y, t0 + a.m[MS_ROW_OF_TLB].icpt + radd, acc);
+        else
+        {
+#pragma unroll
+            for (int j = 0; j < V; j++)
+            {
+                const u64 t = t0 + j;
+                if (t < a.effective) out_add(y, mget(a.m[MS_ROW_OF_TLB], t) + radd, acc[j], a.atomic != 0);
+            }
         }
     }
 }
@@ -623,16 +682,43 @@ __global__ void __launch_bounds__(1024) k_csr5(const KArgs a)
 // ---------------------------------------------------------------------------------------------
 // launch dispatch
 // ---------------------------------------------------------------------------------------------
+template <class VT, class CT, int V>
+static void launch_ell_v(const KArgs &a, dim3 grid, dim3 block, cudaStream_t st)
+{
+    if constexpr (V == 2 || V == 4)
+    {
+        switch (a.tlb_size)
+        {
+        case 1: k_ell<VT, CT, V, 1><<<grid, block, 0, st>>>(a); return;
+        case 2: k_ell<VT, CT, V, 2><<<grid, block, 0, st>>>(a); return;
+        case 3: k_ell<VT, CT, V, 3><<<grid, block, 0, st>>>(a); return;
+        case 4: k_ell<VT, CT, V, 4><<<grid, block, 0, st>>>(a); return;
+        case 5: k_ell<VT, CT, V, 5><<<grid, block, 0, st>>>(a); return;
+        case 6: k_ell<VT, CT, V, 6><<<grid, block, 0, st>>>(a); return;
+        case 7: k_ell<VT, CT, V, 7><<<grid, block, 0, st>>>(a); return;
+        case 8: k_ell<VT, CT, V, 8><<<grid, block, 0, st>>>(a); return;
+        default: break;
+        }
+    }
+    k_ell<VT, CT, V, 0><<<grid, block, 0, st>>>(a);
+}
+
+template <class VT, class CT>
+static void launch_ell(const KArgs &a, dim3 grid, dim3 block, cudaStream_t st, int vec)
+{
+    if (vec >= 8) launch_ell_v<VT, CT, 8>(a, grid, block, st);
+    else if (vec >= 4) launch_ell_v<VT, CT, 4>(a, grid, block, st);
+    else if (vec == 2) launch_ell_v<VT, CT, 2>(a, grid, block, st);
+    else launch_ell_v<VT, CT, 1>(a, grid, block, st);
+}
+
 template <class VT, class CT>
 static cudaError_t launch_vc(int templ, const KArgs &a, dim3 grid, dim3 block, size_t smem, cudaStream_t st, int vec)
 {
     switch (templ)
     {
     case 2: // ELL-like
-        if (vec >= 8) k_ell<VT, CT, 8><<<grid, block, 0, st>>>(a);
-        else if (vec >= 4) k_ell<VT, CT, 4><<<grid, block, 0, st>>>(a);
-        else if (vec == 2) k_ell<VT, CT, 2><<<grid, block, 0, st>>>(a);
-        else k_ell<VT, CT, 1><<<grid, block, 0, st>>>(a);
+        launch_ell<VT, CT>(a, grid, block, st, vec);
         break;
     case 1: // SELL-like
         if (vec >= 4) k_sell<VT, CT, 4><<<grid, block, 0, st>>>(a);

@@ -1,0 +1,297 @@
+"""Benchmark of the SpMV hot path: y = A x over the machine-designed formats.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c4|c4s] [--impl reference]
+
+A step is one SpMV over the whole matrix. The default workload is the 5-point Laplacian on a
+2048 x 2048 grid in fp64 (4,194,304 rows, 20,963,328 non-zeros); with N > 1 every rank owns a
+row block of that size of a 2048 x (2048 N) grid (weak scaling, x replicated, no collective on
+the data path). Prints ONE JSON line on rank 0.
+
+--impl reference times the CPU restatement of the reference's SpMV (oracle/csr_spmv.c, OpenMP
+over all host cores) on the same workload: the reference has no host SpMV of its own and its
+GPU path needs nvcc at run time plus a per-matrix generated program.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from alphasparse_b200 import matrices  # noqa: E402
+
+WORKLOADS = {
+    "c1": ("uniform random 4096^2 fp32, Poisson(16) per row, seed 0", lambda: matrices.uniform_random(4096, 16, 0)),
+    "c2": ("5-point Laplacian 2048x2048 fp64, seed 1", lambda: matrices.laplacian_2d(2048, 1)),
+    "c3": ("power-law 8388608^2 fp32, Zipf(2.1) rows capped at 500000, seed 2", lambda: matrices.power_law(8_388_608, 2.1, 500_000, 2)),
+    "c4": ("3x3-block FEM-like fp64, 1048576 block rows x 27 blocks, seed 3", lambda: matrices.block_fem(1_048_576, 27, 4096, 3)),
+    "c4s": ("3x3-block FEM-like fp64, 1048576 block rows x 9 blocks, seed 3", lambda: matrices.block_fem(1_048_576, 9, 4096, 3)),
+}
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, device: int):
+        super().__init__(daemon=True)
+        self.device = device
+        self.stop_flag = threading.Event()
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+
+    def run(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.device}", f"--query-gpu={q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip().splitlines()
+                if out:
+                    f = [s.strip() for s in out[0].split(",")]
+                    self.samples.append(float(f[0]))
+                    self.max_mhz = float(f[1])
+                    for n, v in zip(names, f[2:]):
+                        if v.lower().startswith("active"):
+                            self.reasons.add(n)
+            except Exception:
+                pass
+            self.stop_flag.wait(0.2)
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def oracle_lib():
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import refdump
+
+    return refdump
+
+
+def cpu_baseline(m, x, budget_s: float = 15.0, reps_min: int = 3):
+    """The CPU restatement of the reference's SpMV, timed on all host cores over repeated passes
+    of the same matrix until `budget_s` is used. Returns (GFLOP/s, threads, passes)."""
+    rd = oracle_lib()
+    L = rd.oracle_lib()
+    threads = int(L.asp_oracle_max_threads())
+    rd.csr_native(m, x)  # warm-up and page touch
+    t0 = time.perf_counter()
+    n = 0
+    times = []
+    while n < reps_min or (time.perf_counter() - t0 < budget_s and n < 200):
+        s = time.perf_counter()
+        rd.csr_native(m, x)
+        times.append(time.perf_counter() - s)
+        n += 1
+    med = float(np.median(times))
+    return 2.0 * m.nnz / med * 1e-9, threads, n, med
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    desc, gen = WORKLOADS[args.workload]
+    m, x = gen()
+    W, K = max(args.warmup, 1), max(args.steps, 1)
+    rd = oracle_lib()
+    for _ in range(W):
+        rd.csr_native(m, x)
+    t0 = time.perf_counter()
+    for _ in range(K):
+        rd.csr_native(m, x)
+    dt = (time.perf_counter() - t0) / K
+    threads = int(rd.oracle_lib().asp_oracle_max_threads())
+    gf = 2.0 * m.nnz / dt * 1e-9
+    line = {
+        "impl": "reference", "metric": "SpMV GFLOP/s", "value": gf, "unit": "GFLOP/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f64" if m.values.dtype == np.float64 else "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "description": desc, "rows": m.n_rows, "nnz": m.nnz},
+        "cpu_baseline": {"value": gf, "unit": "GFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"{K} full SpMV passes of the {args.workload} matrix, OpenMP row-parallel CSR loop"},
+        "e2e": {"value": gf, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--no-search", action="store_true", help="use the first candidate graph instead of timing all of them")
+    ap.add_argument("--spec", default=None, help="run exactly this compressed-view graph (name from the candidate list)")
+    ap.add_argument("--threads", type=int, default=0, help="with --spec: thread_num_in_block")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--verbose", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+
+    from alphasparse_b200 import capi, tuner
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+
+        dist = dist_
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    W, K = max(args.warmup, 3), max(args.steps, 1)
+    desc, gen = WORKLOADS[args.workload]
+    if args.workload == "c2" and world > 1:
+        # weak scaling: this rank's row block of the 2048 x (2048*world) grid, x replicated
+        full_rows = 2048 * 2048 * world
+        mfull, xfull = matrices.laplacian_2d(2048, 1, grid_y=2048 * world)
+        r0 = rank * 2048 * 2048
+        m = mfull.row_slice(r0, r0 + 2048 * 2048)
+        x = xfull
+        del mfull
+    else:
+        m, x = gen()
+    log = (lambda s: print(f"[rank {rank}] {s}", file=sys.stderr)) if args.verbose else None
+
+    ctx = capi.Context(local_rank)
+    cands = tuner.compressed_candidates(m)
+    if args.spec:
+        cands = [c for c in cands if c.name == args.spec]
+        if args.threads:
+            for c in cands:
+                c.launches = [(None, args.threads, l[2]) for l in c.launches[:1]]
+    if args.no_search:
+        cands = cands[:1]
+        cands[0].launches = cands[0].launches[-1:]
+    t_s = time.perf_counter()
+    fmt, group, trials = tuner.search(ctx, m, cands, log=log)
+    search_s = time.perf_counter() - t_s
+    best = min(trials, key=lambda t: t.ms)
+
+    val_t = torch.float64 if m.values.dtype == np.float64 else torch.float32
+    dx = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    dy = torch.zeros(m.n_rows, dtype=val_t, device="cuda")
+    stream = torch.cuda.ExternalStream(ctx.stream)
+    zero_y = "auto" if int(m.row_lengths().min()) > 0 else True  # rows without non-zeros are never stored by a kernel
+
+    def step():
+        group.spmv(dx.data_ptr(), dy.data_ptr(), zero_y)
+
+    torch.cuda.synchronize()
+    for _ in range(W):
+        step()
+    ctx.synchronize()
+    if dist:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(K):
+        step()
+    e1.record(stream)
+    e1.synchronize()
+    torch.cuda.synchronize()
+    ms_total = e0.elapsed_time(e1)
+    if dist:
+        t = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / K
+
+    # end to end through the host-buffer entry point: pinned x in, y out, every step
+    hx = torch.from_numpy(np.ascontiguousarray(x)).pin_memory()
+    hy = torch.empty(m.n_rows, dtype=val_t).pin_memory()
+    plans = group._plans
+    Ke = max(3, min(K, 30))
+    for _ in range(2):
+        capi.check(capi.lib().asp_spmv_host(ctx.handle, plans, group.n, C.c_void_p(hx.data_ptr()), C.c_void_p(hy.data_ptr())))
+    if dist:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(Ke):
+        capi.check(capi.lib().asp_spmv_host(ctx.handle, plans, group.n, C.c_void_p(hx.data_ptr()), C.c_void_p(hy.data_ptr())))
+    e2e_s = (time.perf_counter() - t0) / Ke
+    if dist:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    sampler.stop_flag.set()
+
+    # parity of what was just timed, against the CPU oracle on rank 0 (bounded: c2-sized matrices take ~0.1 s)
+    parity = None
+    if rank == 0 and m.nnz <= 300_000_000:
+        rd = oracle_lib()
+        y_ref, scale = rd.csr_ref(m, x)
+        parity = rd.rel_err(hy.numpy(), y_ref, scale)
+
+    nnz_total = m.nnz * world
+    gflops = 2.0 * nnz_total / (ms_step * 1e-3) * 1e-9
+    b_alg = m.algorithmic_bytes()
+    achieved = b_alg / (ms_step * 1e-3) * 1e-9
+    peak, peak_kind = measured_peak_gbs()
+    if rank == 0:
+        es = m.values.dtype.itemsize
+        line = {
+            "metric": "SpMV GFLOP/s", "value": gflops, "unit": "GFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f64" if es == 8 else "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "description": desc, "rows_per_gpu": m.n_rows, "nnz_per_gpu": m.nnz,
+                       "graph": best.name, "launch": {"threads": best.launch[1], "row_reduce": best.launch[2]},
+                       "l2": "inputs larger than L2 (format arrays %.0f MB)" % (group.format_bytes() / 1e6),
+                       "search_s": round(search_s, 2), "trials": len(trials), "padding_rate": round(best.padding_rate, 4)},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind, "algorithmic_bytes": b_alg,
+                         "format_bytes": int(group.format_bytes() + es * (m.n_cols + m.n_rows))},
+            "e2e": {"value": 2.0 * nnz_total / e2e_s * 1e-9, "unit": "GFLOP/s", "h2d_bytes_per_step": int(es * m.n_cols),
+                    "d2h_bytes_per_step": int(es * m.n_rows), "ms_per_step": e2e_s * 1e3},
+            "gpu_launches": int(K * group.launches()),
+            "clocks": sampler.summary(),
+            "parity_max_rel_err": parity,
+        }
+        if not args.no_cpu_baseline:
+            gf, threads, passes, med = cpu_baseline(m, x)
+            line["cpu_baseline"] = {"value": gf, "unit": "GFLOP/s", "cores": threads, "kind": "port",
+                                    "sample": f"{passes} full SpMV passes of this matrix (median {med * 1e3:.2f} ms), OpenMP row-parallel CSR loop"}
+        print(json.dumps(line))
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -167,9 +167,10 @@ int asp_plan_launches(const asp_plan *plan);
 
 /* replaces the spmv_<k><<<...>>> calls of the generated main() (code_builder.cc:1534-1550):
  * y (+)= A*x over all sub-matrix plans of one matrix; d_x and d_y are device pointers of
- * the value dtype, lengths n_cols and n_rows. zero_y != 0 clears y first (needed whenever a
- * plan accumulates with atomics; the reference never clears y between repeats). Asynchronous
- * on the context's stream. */
+ * the value dtype, lengths n_cols and n_rows. zero_y: 0 = leave y as it is (the reference
+ * never clears y between repeats), 1 = clear y first, 2 = clear y only when one of the plans
+ * accumulates with atomics (plans that store every row of a matrix without empty rows
+ * overwrite y completely). Asynchronous on the context's stream. */
 asp_status asp_spmv(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *d_x, void *d_y, int zero_y);
 
 /* same with HOST x and y: copies x in, runs, copies y out, waits. This is the shape of the
