@@ -58,7 +58,8 @@ class PlanDesc(C.Structure):
 EXPORTS = [
     "asp_ctx_create", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_destroy",
     "asp_plan_set_launch", "asp_plan_format_bytes", "asp_plan_launches", "asp_spmv", "asp_spmv_host", "asp_time",
-    "asp_synchronize", "asp_status_str", "asp_last_error", "asp_built_for_sm100a",
+    "asp_synchronize", "asp_status_str", "asp_last_error", "asp_built_for_sm100a", "asp_spmv_host_static",
+    "asp_static_stage_bytes",
 ]
 
 _lib = None
@@ -98,6 +99,10 @@ def lib() -> C.CDLL:
     L.asp_spmv.restype = C.c_int
     L.asp_spmv_host.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p]
     L.asp_spmv_host.restype = C.c_int
+    L.asp_spmv_host_static.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p]
+    L.asp_spmv_host_static.restype = C.c_int
+    L.asp_static_stage_bytes.argtypes = []
+    L.asp_static_stage_bytes.restype = C.c_uint64
     L.asp_time.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_double,
                            C.POINTER(C.c_float), C.POINTER(C.c_float)]
     L.asp_time.restype = C.c_int
@@ -214,6 +219,16 @@ class PlanGroup:
         assert x.shape[0] == self.n_cols
         y = np.empty(self.n_rows, dtype=self.val_dtype)
         check(lib().asp_spmv_host(self.ctx.handle, self._plans, self.n, C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data)))
+        return y
+
+    def spmv_host_static(self, x: np.ndarray) -> np.ndarray:
+        """spmv_host without any device allocation: x and y are staged in the library's fixed
+        device array (see asp_spmv_host_static in include/asp_b200.h for who needs this and for
+        the size limit)."""
+        x = np.ascontiguousarray(x, dtype=self.val_dtype)
+        assert x.shape[0] == self.n_cols
+        y = np.empty(self.n_rows, dtype=self.val_dtype)
+        check(lib().asp_spmv_host_static(self.ctx.handle, self._plans, self.n, C.c_void_p(x.ctypes.data), C.c_void_p(y.ctypes.data)))
         return y
 
     def time(self, warmup: int = 3, reps: int = 20, zero_y="auto", gflops_up_bound: float = 0.0):

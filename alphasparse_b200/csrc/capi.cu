@@ -723,6 +723,71 @@ asp_status asp_spmv_host(asp_ctx *ctx, asp_plan *const *plans, int n_plans, cons
     return ASP_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// asp_spmv_host_static: the host-buffer SpMV without any allocation.
+//
+// Who needs it: a solver that has handed the whole device to its own memory pool (a cudaMalloc
+// from this library would fail, or break the pool's accounting), and a control loop that cannot
+// tolerate the device-wide synchronisation cudaMalloc / cudaFree imply. asp_spmv_host stages x
+// and y in buffers it allocates on first use and grows on demand; this variant stages them in the
+// fixed array below instead. Every GPU that loads the library holds the array until the process
+// exits, which is why it is kept modest: x lives in the first half, y in the second, so
+// n_cols * sizeof(value) and n_rows * sizeof(value) must each fit in ASP_STATIC_STAGE_BYTES / 2.
+//
+// In host code `g_static_stage` is only a handle for the device symbol, not a device address; the
+// address is looked up with cudaGetSymbolAddress once per device (with that device current) on
+// the first call made for that device, and cached. That first call should therefore be made
+// during set-up, before any stream capture is started.
+//
+// All calls share the array and it keeps whatever the previous call left in it: the y half is
+// cleared at the start of every call, the x half is overwritten. Two calls that overlap in time
+// on one GPU (different contexts or host threads) race on it; serialise them.
+// ---------------------------------------------------------------------------------------------
+#define ASP_STATIC_STAGE_BYTES (16u << 20)
+static __device__ __align__(256) unsigned char g_static_stage[ASP_STATIC_STAGE_BYTES];
+
+namespace
+{
+const int kMaxDevices = 64;
+unsigned char *g_static_stage_addr[kMaxDevices]; // per device, filled on first use
+
+asp_status static_stage_address(asp_ctx *ctx, unsigned char **out)
+{
+    if (ctx->device < 0 || ctx->device >= kMaxDevices) return fail(ASP_ERR_UNSUPPORTED, "device ordinal too large for the static staging table");
+    if (!g_static_stage_addr[ctx->device])
+    {
+        ASP_CUDA(cudaSetDevice(ctx->device));
+        void *p = nullptr;
+        ASP_CUDA(cudaGetSymbolAddress(&p, g_static_stage));
+        g_static_stage_addr[ctx->device] = (unsigned char *)p;
+    }
+    *out = g_static_stage_addr[ctx->device];
+    return ASP_OK;
+}
+} // namespace
+
+asp_status asp_spmv_host_static(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *h_x, void *h_y)
+{
+    if (!ctx || !plans || n_plans <= 0 || !plans[0] || !h_x || !h_y) return fail(ASP_ERR_INVALID_ARG, "NULL argument");
+    const size_t es = plans[0]->val_is_f64 ? 8 : 4;
+    const size_t xb = plans[0]->n_cols * es, yb = plans[0]->n_rows * es;
+    const size_t half = ASP_STATIC_STAGE_BYTES / 2;
+    if (xb > half || yb > half)
+        return fail(ASP_ERR_INVALID_ARG, "matrix too large for the static staging area: x and y must each fit in " + std::to_string(half) + " bytes");
+    unsigned char *stage = nullptr;
+    asp_status st = static_stage_address(ctx, &stage);
+    if (st != ASP_OK) return st;
+    unsigned char *sx = stage, *sy = stage + half;
+    ASP_CUDA(cudaMemcpyAsync(sx, h_x, xb, cudaMemcpyHostToDevice, ctx->stream));
+    st = asp_spmv(ctx, plans, n_plans, sx, sy, 1); // zero_y = 1: the y half still holds the previous call's result
+    if (st != ASP_OK) return st;
+    ASP_CUDA(cudaMemcpyAsync(h_y, sy, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    ASP_CUDA(cudaStreamSynchronize(ctx->stream));
+    return ASP_OK;
+}
+
+uint64_t asp_static_stage_bytes(void) { return ASP_STATIC_STAGE_BYTES; }
+
 asp_status asp_time(asp_ctx *ctx, asp_plan *const *plans, int n_plans, int warmup, int reps, int zero_y,
                     double gflops_up_bound, float *ms_per_spmv, float *gflops)
 {

@@ -177,6 +177,16 @@ asp_status asp_spmv(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const voi
  * reference's a.out run (host arrays in, host y out) without the text files. */
 asp_status asp_spmv_host(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *h_x, void *h_y);
 
+/* No counterpart in the reference. asp_spmv_host for callers that must not trigger a device
+ * allocation (a solver whose own pool owns all device memory; a loop that cannot afford the
+ * device-wide synchronisation of cudaMalloc / cudaFree): x and y are staged in a fixed device
+ * array of asp_static_stage_bytes() bytes (half for x, half for y) that every GPU loading the
+ * library holds until exit. Fails with ASP_ERR_INVALID_ARG when n_cols or n_rows times the
+ * value size exceeds half of it. The first call for a device looks up the array's address and
+ * should be made before any stream capture; calls that overlap on one GPU race on the array. */
+asp_status asp_spmv_host_static(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *h_x, void *h_y);
+uint64_t asp_static_stage_bytes(void);
+
 /* replaces execute_binary + perf_result parsing (executor.cc:6-59): CUDA-event timing of
  * `reps` SpMVs after `warmup`, x and y internal (x = 100 everywhere, as the generated main()
  * does). gflops = 2*sum(true_nnz)*1e-6/ms. Returns ASP_ERR_IMPLAUSIBLE when gflops exceeds
