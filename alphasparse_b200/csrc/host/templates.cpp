@@ -401,6 +401,396 @@ bool init_k6(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::st
     add_nnz_arrays(t, b, col, val, b.pad_col.size());
     return true;
 }
+// read_index[6] / staggered_padding_val_arr: inside every WLB the TLBs are taken in groups of 32 and
+// element k of lane l of group g moves to g*32*S + k*32 + l (op_manager.cc:3569-3589). Identity
+// when every TLB holds one non-zero.
+void staggered_arrays(const CompressedBlock &b, std::vector<uint8_t> &col, std::vector<uint8_t> &val)
+{
+    const u64 n_pad = b.pad_col.size();
+    const int cb = dtype_bytes(b.col_dt), es = b.val.es;
+    col.assign(n_pad * cb, 0);
+    val.assign(n_pad * es, 0);
+    const Level &B = b.blb, &W = b.wlb;
+    const u64 nb = B.block_num;
+#pragma omp parallel for schedule(dynamic, 64)
+    for (u64 i = 0; i < nb; i++)
+        for (u64 w = B.index.v[i]; w < B.index.v[i + 1]; w++)
+        {
+            const u64 S = b.tlb.coo_size.v[w];
+            const u64 base = B.coo_begin.v[i] + W.coo_begin.v[w];
+            const u64 groups = (W.index.v[w + 1] - W.index.v[w]) / 32;
+            for (u64 g = 0; g < groups; g++)
+            {
+                const u64 o = base + g * 32 * S;
+                interleave_cols(col.data() + o * cb, b.col_dt, b.pad_col.data() + o, 32, S);
+                interleave_vals(val.data() + o * es, es, b.pad_val.b.data() + o * es, 32, S);
+            }
+        }
+}
+
+std::vector<u64> first_n(const std::vector<u64> &v, u64 n) { return std::vector<u64>(v.begin(), v.begin() + n); }
+
+// ---- DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE (direct_atom_total_warp_reduce_op.cc) ------------
+bool init_k4(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::string &err)
+{
+    common_head(m, b, ASP_DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE, t);
+    const Level &B = b.blb, &W = b.wlb;
+    std::vector<u64> rows(W.block_num), nz(W.block_num + 1);
+    for (u64 i = 0; i < B.block_num; i++)
+        for (u64 w = B.index.v[i]; w < B.index.v[i + 1]; w++)
+        {
+            if (W.row_num.v[w] != 1)
+            {
+                err = "warp-per-row template needs one row per WLB";
+                return false;
+            }
+            rows[w] = B.first_row.v[i] + W.first_row.v[w];
+            nz[w] = B.coo_begin.v[i] + W.coo_begin.v[w];
+            if (w >= 1 && rows[w] == rows[w - 1]) t.is_atom_add = true;
+        }
+    nz[W.block_num] = b.pad_col.size();
+    t.effective_num = effective_and_permute(m, b, rows);
+    u64 mx = 0;
+    for (u64 r : rows) mx = std::max(mx, r);
+    TemplateArray &rm = add_meta(t, ASP_ARR_GLOBAL_ROW_INDEX_OF_WARP_LEVEL_BLOCK, rows, suitable_dtype(mx));
+    try_linear_then_cycle_increase(rm, rows);
+    TemplateArray &no = add_meta(t, ASP_ARR_GLOBAL_WARP_NZ_BEGIN_OFFSET, nz, suitable_dtype(b.pad_col.size() + 1));
+    detect_linear(nz, no.comp);
+    add_perm(m, t);
+    std::vector<uint8_t> col, val;
+    staggered_arrays(b, col, val);
+    add_nnz_arrays(t, b, col, val, b.pad_col.size());
+    return true;
+}
+
+// ---- SHARED_MEMORY_LONG_ROW_TEMPLATE (shared_memory_long_row_op.cc) ---------------------------
+bool init_k7(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::string &err)
+{
+    common_head(m, b, ASP_SHARED_MEMORY_LONG_ROW_TEMPLATE, t);
+    const Level &B = b.blb;
+    for (u64 i = 0; i < B.block_num; i++)
+    {
+        if (B.row_num.v[i] != 1)
+        {
+            err = "long-row template needs one row per BLB";
+            return false;
+        }
+        if (i + 1 < B.block_num && B.first_row.v[i] == B.first_row.v[i + 1]) t.is_atom_add = true;
+    }
+    for (u64 s : b.tlb.coo_size.v)
+        if (s != 1)
+        {
+            err = "long-row template needs TLB size 1";
+            return false;
+        }
+    std::vector<u64> rows(B.first_row.v);
+    if (m.is_sorted)
+        for (u64 &r : rows) r = m.perm[r + b.min_row];
+    u64 mx = 0;
+    for (u64 r : rows) mx = std::max(mx, r);
+    TemplateArray &rm = add_meta(t, ASP_ARR_ROW_INDEX_OF_BLOCK_LEVEL_BLOCK, rows, suitable_dtype(mx));
+    try_linear_then_cycle_increase(rm, rows);
+    TemplateArray &bn = add_meta(t, ASP_ARR_BLOCK_NZ_BEGIN_OFFSET, B.coo_begin.v, B.coo_begin.dt);
+    detect_linear(B.coo_begin.v, bn.comp);
+    add_perm(m, t);
+    std::vector<uint8_t> col, val;
+    staggered_arrays(b, col, val);
+    add_nnz_arrays(t, b, col, val, b.pad_col.size());
+    return true;
+}
+
+bool blbs_overlap_in_rows(const Level &B)
+{
+    u64 gmax = B.first_row.v[0] + B.row_num.v[0] - 1;
+    for (u64 i = 1; i < B.block_num; i++)
+    {
+        if (B.first_row.v[i] <= gmax) return true;
+        gmax = std::max(gmax, B.first_row.v[i] + B.row_num.v[i] - 1);
+    }
+    return false;
+}
+
+// ---- SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE (shared_memory_total_warp_reduce_op.cc) ---------
+bool init_k8(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::string &err)
+{
+    common_head(m, b, ASP_SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE, t);
+    const Level &B = b.blb, &W = b.wlb;
+    if (blbs_overlap_in_rows(B)) t.is_atom_add = true;
+    t.effective_num = b.max_row - b.min_row + 1;
+    std::vector<u64> roff(b.n_rows + 1, 0), nz(W.block_num + 1);
+    for (u64 i = 0; i < B.block_num; i++)
+        for (u64 w = B.index.v[i]; w < B.index.v[i + 1]; w++)
+        {
+            if (W.row_num.v[w] != 1)
+            {
+                err = "warp-reduce shared-memory template needs one row per WLB";
+                return false;
+            }
+            roff[B.first_row.v[i] + W.first_row.v[w] + 1]++;
+            nz[w] = B.coo_begin.v[i] + W.coo_begin.v[w];
+        }
+    nz[W.block_num] = b.pad_col.size();
+    for (u64 r = 0; r < b.n_rows; r++) roff[r + 1] += roff[r];
+    TemplateArray &ro = add_meta(t, ASP_ARR_ROW_OFFSET_IN_WARP_TMP_RESULT, roff, suitable_dtype(roff.back()));
+    std::vector<u64> brow(B.first_row.v);
+    brow.push_back(b.n_rows);
+    TemplateArray &br = add_meta(t, ASP_ARR_BLOCK_FIRST_ROW_INDEX, brow, suitable_dtype(b.n_rows));
+    TemplateArray &bw = add_meta(t, ASP_ARR_BLOCK_BEGIN_WARP_INDEX_OFFSET, B.index.v, B.index.dt);
+    TemplateArray &fn = add_meta(t, ASP_ARR_GLOBAL_WARP_BLOCK_FIRST_NZ, nz, suitable_dtype(nz.back()));
+    detect_linear(B.index.v, bw.comp);
+    detect_linear(roff, ro.comp);
+    detect_linear(brow, br.comp);
+    detect_linear(nz, fn.comp);
+    add_perm(m, t);
+    std::vector<uint8_t> col, val;
+    staggered_arrays(b, col, val);
+    add_nnz_arrays(t, b, col, val, b.pad_col.size());
+    return true;
+}
+
+// closed form of warp_nz_begin_offset in the 3-level templates: cycle-linear with the cycle taken
+// from the linear form of block_begin_warp_index_offset (direct_atom_op.cc:1828-1890)
+void try_cycle_linear_warp_nz(TemplateArray &wn, const std::vector<u64> &v, const TemplateArray &bw, const std::vector<u64> &bwv)
+{
+    u64 cycle = 0;
+    if (bw.comp.kind == ASP_COMPRESS_LINEAR) cycle = bw.comp.coef;
+    else
+    {
+        ClosedForm f;
+        if (!detect_linear(bwv, f)) return;
+        cycle = f.coef;
+    }
+    detect_cycle_linear(v, cycle, wn.comp);
+}
+
+// ---- DIRECT_ATOM_TEMPLATE (direct_atom_op.cc) --------------------------------------------------
+bool init_k1(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::string &err)
+{
+    common_head(m, b, ASP_DIRECT_ATOM_TEMPLATE, t);
+    const Level &B = b.blb, &W = b.wlb;
+    bool adj = false;
+    std::vector<u64> rows = tlb_global_rows(b, adj);
+    if (adj) t.is_atom_add = true;
+    if (m.is_sorted)
+        for (u64 &r : rows) r = m.perm[r + b.min_row]; // every TLB, padded rows included, as the reference does
+    u64 mx = 0;
+    for (u64 r : rows) mx = std::max(mx, r);
+    TemplateArray &rm = add_meta(t, ASP_ARR_GLOBAL_ROW_INDEX_OF_THREAD_LEVEL_BLOCK, rows, suitable_dtype(mx));
+    TemplateArray &bw = add_meta(t, ASP_ARR_BLOCK_BEGIN_WARP_INDEX_OFFSET, B.index.v, B.index.dt);
+    TemplateArray &wt = add_meta(t, ASP_ARR_WARP_BEGIN_THREAD_INDEX_OFFSET, W.index.v, W.index.dt);
+    TemplateArray &ts = add_meta(t, ASP_ARR_THREAD_BLOCK_SIZE_IN_WARP, b.tlb.coo_size.v, b.tlb.coo_size.dt);
+    std::vector<u64> bnz = first_n(B.coo_begin.v, B.block_num);
+    TemplateArray &bn = add_meta(t, ASP_ARR_BLOCK_NZ_BEGIN_OFFSET, bnz, B.coo_begin.dt);
+    TemplateArray &wn = add_meta(t, ASP_ARR_WARP_NZ_BEGIN_OFFSET, W.coo_begin.v, W.coo_begin.dt);
+    try_linear_then_cycle_increase(rm, rows);
+    detect_linear(B.index.v, bw.comp);
+    detect_linear(W.index.v, wt.comp);
+    if (!detect_constant(b.tlb.coo_size.v, ts.comp)) detect_branch(b.tlb.coo_size.v, ts.comp);
+    detect_linear(bnz, bn.comp);
+    try_cycle_linear_warp_nz(wn, W.coo_begin.v, bw, B.index.v);
+    add_perm(m, t);
+    std::vector<uint8_t> col, val;
+    staggered_arrays(b, col, val);
+    add_nnz_arrays(t, b, col, val, b.pad_col.size());
+    (void)err;
+    return true;
+}
+
+// ---- SHARED_MEMORY_TEMPLATE (shared_memory_op.cc) ----------------------------------------------
+bool init_k5(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::string &err)
+{
+    common_head(m, b, ASP_SHARED_MEMORY_TEMPLATE, t);
+    const Level &B = b.blb, &W = b.wlb;
+    if (blbs_overlap_in_rows(B)) t.is_atom_add = true;
+    bool adj = false;
+    std::vector<u64> rows = tlb_global_rows(b, adj);
+    std::vector<u64> roff(b.n_rows + 1, 0);
+    for (u64 r : rows) roff[r + 1]++;
+    for (u64 r = 0; r < b.n_rows; r++) roff[r + 1] += roff[r];
+    // values / columns interleaved per WLB: element k of local TLB i at base + i + k*n_w
+    const u64 n_pad = b.pad_col.size();
+    const int cb = dtype_bytes(b.col_dt), es = b.val.es;
+    std::vector<uint8_t> col(n_pad * cb), val(n_pad * es);
+    for (u64 i = 0; i < B.block_num; i++)
+        for (u64 w = B.index.v[i]; w < B.index.v[i + 1]; w++)
+        {
+            const u64 base = B.coo_begin.v[i] + W.coo_begin.v[w], n = W.index.v[w + 1] - W.index.v[w], S = b.tlb.coo_size.v[w];
+            interleave_cols(col.data() + base * cb, b.col_dt, b.pad_col.data() + base, n, S);
+            interleave_vals(val.data() + base * es, es, b.pad_val.b.data() + base * es, n, S);
+        }
+    TemplateArray &ro = add_meta(t, ASP_ARR_ROW_OFFSET_IN_THREAD_TMP_RESULT, roff, suitable_dtype(roff.back()));
+    std::vector<u64> brow(B.first_row.v);
+    brow.push_back(b.n_rows);
+    TemplateArray &br = add_meta(t, ASP_ARR_BLOCK_FIRST_ROW_INDEX, brow, suitable_dtype(b.n_rows));
+    TemplateArray &bw = add_meta(t, ASP_ARR_BLOCK_BEGIN_WARP_INDEX_OFFSET, B.index.v, B.index.dt);
+    TemplateArray &wt = add_meta(t, ASP_ARR_WARP_BEGIN_THREAD_INDEX_OFFSET, W.index.v, W.index.dt);
+    TemplateArray &ts = add_meta(t, ASP_ARR_THREAD_BLOCK_SIZE_IN_WARP, b.tlb.coo_size.v, b.tlb.coo_size.dt);
+    std::vector<u64> bnz = first_n(B.coo_begin.v, B.block_num);
+    TemplateArray &bn = add_meta(t, ASP_ARR_BLOCK_NZ_BEGIN_OFFSET, bnz, B.coo_begin.dt);
+    TemplateArray &wn = add_meta(t, ASP_ARR_WARP_NZ_BEGIN_OFFSET, W.coo_begin.v, W.coo_begin.dt);
+    detect_linear(B.index.v, bw.comp);
+    detect_linear(W.index.v, wt.comp);
+    if (!detect_constant(b.tlb.coo_size.v, ts.comp)) detect_branch(b.tlb.coo_size.v, ts.comp);
+    detect_linear(bnz, bn.comp);
+    try_cycle_linear_warp_nz(wn, W.coo_begin.v, bw, B.index.v);
+    detect_linear(brow, br.comp);
+    detect_linear(roff, ro.comp);
+    add_perm(m, t);
+    add_nnz_arrays(t, b, col, val, n_pad);
+    (void)err;
+    return true;
+}
+
+int bit_count(u64 v)
+{
+    int n = 0;
+    while (v)
+    {
+        v >>= 1;
+        n++;
+    }
+    return n;
+}
+
+// ---- UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE[_WITH_WARP_REDUCE] ---------------------------
+// (unaligned_warp_reduce_same_TLB_size_op.cc:5-297, helpers :434-512 and :1332-1645)
+bool init_k9(const Matrix &m, const CompressedBlock &b, bool with_warp_reduce, TemplateData &t, std::string &err)
+{
+    common_head(m, b, with_warp_reduce ? ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE : ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE, t);
+    if (!b.tlb_is_nnz_div)
+    {
+        err = "CSR5-like templates need the TLB level built by the nnz division";
+        return false;
+    }
+    const u64 S = b.tlb.coo_size.v[0];
+    // rows without non-zeros become one zero at column 0; the tail is padded to whole warps by
+    // repeating the last (row, column) with value 0
+    std::vector<u64> row;
+    std::vector<u32> col;
+    row.reserve(b.col.size() + b.n_rows);
+    col.reserve(b.col.size() + b.n_rows);
+    std::vector<u64> src; // source position of every element, ~0 for filler
+    src.reserve(b.col.size() + b.n_rows);
+    u64 last_row_with_nz = 0;
+    for (u64 r = 0; r < b.n_rows; r++)
+        if (b.rowptr[r + 1] > b.rowptr[r]) last_row_with_nz = r;
+    for (u64 r = 0; r <= last_row_with_nz; r++)
+    {
+        if (b.rowptr[r + 1] == b.rowptr[r])
+        {
+            row.push_back(r);
+            col.push_back(0);
+            src.push_back(~0ull);
+            continue;
+        }
+        for (u64 k = b.rowptr[r]; k < b.rowptr[r + 1]; k++)
+        {
+            row.push_back(r);
+            col.push_back(b.col[k]);
+            src.push_back(k);
+        }
+    }
+    const u64 wn = 32 * S;
+    const u64 target = (row.size() + wn - 1) / wn * wn;
+    while (row.size() < target)
+    {
+        row.push_back(row.back());
+        col.push_back(col.back());
+        src.push_back(~0ull);
+    }
+    const u64 n = row.size(), T = n / S, Wn = T / 32;
+    // row-start flags (the first non-zero of every warp always starts a sum), first rows per warp
+    std::vector<uint8_t> flag(n);
+    for (u64 i = 0; i < n; i++) flag[i] = (i % wn == 0) ? 1 : (row[i] != row[i - 1]);
+    std::vector<u64> wfirst(Wn);
+    for (u64 w = 0; w < Wn; w++) wfirst[w] = row[w * wn];
+    // per TLB: does it hold a row start, count of following start-free TLBs, first row started (relative)
+    std::vector<uint8_t> has(T, 0);
+    for (u64 tl = 0; tl < T; tl++)
+        for (u64 k = 0; k < S; k++) has[tl] |= flag[tl * S + k];
+    std::vector<u64> roff(T, 0), frow(T, 0);
+    u64 max_roff = 0, max_frow = 0, last_head = 0, run = 0;
+    for (u64 tl = 1; tl < T; tl++)
+    {
+        if (!has[tl]) run++;
+        else
+        {
+            max_roff = std::max(max_roff, run);
+            roff[last_head] = run;
+            run = 0;
+            last_head = tl;
+        }
+    }
+    max_roff = std::max(max_roff, run);
+    roff[last_head] = run;
+    for (u64 tl = 0; tl < T; tl++)
+    {
+        if (has[tl])
+        {
+            for (u64 k = 0; k < S; k++)
+                if (flag[tl * S + k])
+                {
+                    frow[tl] = row[tl * S + k] - wfirst[tl / 32];
+                    break;
+                }
+        }
+        else
+            frow[tl] = frow[tl - 1];
+        max_frow = std::max(max_frow, frow[tl]);
+    }
+    int bits_row = bit_count(max_frow), bits_off = bit_count(max_roff);
+    if (bits_row == 0) bits_row = 1;
+    if (bits_off == 0) bits_off = 1;
+    const int total_bits = (int)S + bits_row + bits_off;
+    if (total_bits > 64)
+    {
+        err = "CSR5-like: row-start flags + offsets do not fit in 64 bits";
+        return false;
+    }
+    const int word = total_bits <= 8 ? 8 : total_bits <= 16 ? 16 : total_bits <= 32 ? 32 : 64;
+    const int meta_dt = word == 8 ? ASP_U8 : word == 16 ? ASP_U16 : word == 32 ? ASP_U32 : ASP_U64;
+    std::vector<u64> meta(T);
+    for (u64 tl = 0; tl < T; tl++)
+    {
+        u64 f = 0;
+        for (u64 k = 0; k < S; k++)
+            if (flag[tl * S + k]) f |= 1ull << (S - 1 - k);
+        u64 v = f << (word - (int)S - bits_off - bits_row + bits_off);
+        v |= roff[tl];
+        v <<= bits_row;
+        v |= frow[tl];
+        meta[tl] = v;
+    }
+    t.tlb_size = S;
+    t.bits_word = word;
+    t.bits_flag = (int)S;
+    t.bits_row = bits_row;
+    t.bits_off = bits_off;
+    t.n_tlb = (b.col.size() + S - 1) / S;
+    if (with_warp_reduce) wfirst.push_back(row.back() + 1);
+    TemplateArray &fr = add_meta(t, ASP_ARR_GLOBAL_FIRST_ROW_INDEX_OF_WARP_LEVEL_BLOCK, wfirst, b.row_dt);
+    try_linear_then_cycle_increase(fr, wfirst);
+    add_meta(t, ASP_ARR_COMBINE_META_OF_THREAD_LEVEL_BLOCK, meta, meta_dt);
+    add_perm(m, t);
+    // values / columns: element k of lane l of warp w at w*32*S + k*32 + l
+    const int cb = dtype_bytes(b.col_dt), es = b.val.es;
+    std::vector<uint8_t> ocol(n * cb, 0), oval(n * es, 0);
+    for (u64 i = 0; i < n; i++)
+    {
+        const u64 tl = i / S, k = i % S, w = tl / 32, lane = tl % 32;
+        const u64 d = w * wn + k * 32 + lane;
+        switch (cb)
+        {
+        case 1: ocol[d] = (uint8_t)col[i]; break;
+        case 2: ((uint16_t *)ocol.data())[d] = (uint16_t)col[i]; break;
+        case 4: ((uint32_t *)ocol.data())[d] = col[i]; break;
+        default: ((uint64_t *)ocol.data())[d] = col[i]; break;
+        }
+        if (src[i] != ~0ull) memcpy(&oval[d * es], &b.val.b[src[i] * es], es);
+    }
+    add_nnz_arrays(t, b, ocol, oval, n);
+    return true;
+}
 } // namespace
 
 bool init_template(const Matrix &m, size_t sub, int type, TemplateData &out, std::string &err)
@@ -411,6 +801,12 @@ bool init_template(const Matrix &m, size_t sub, int type, TemplateData &out, std
         return false;
     }
     const CompressedBlock &b = m.blocks[sub];
+    const bool csr5 = type == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || type == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE;
+    if (!csr5 && b.tlb_is_nnz_div)
+    {
+        err = "this template needs an ELL-style TLB level";
+        return false;
+    }
     if (!(b.blb.built && b.wlb.built && b.tlb.built))
     {
         err = "sub-matrix is not tiled at all three levels";
@@ -421,6 +817,13 @@ bool init_template(const Matrix &m, size_t sub, int type, TemplateData &out, std
     case ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS: return init_k3(m, b, out, err);
     case ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS: return init_k2(m, b, out, err);
     case ASP_SHARED_MEMORY_TEMPLATE_WARP_COMPRESS: return init_k6(m, b, out, err);
+    case ASP_DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE: return init_k4(m, b, out, err);
+    case ASP_SHARED_MEMORY_LONG_ROW_TEMPLATE: return init_k7(m, b, out, err);
+    case ASP_SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE: return init_k8(m, b, out, err);
+    case ASP_DIRECT_ATOM_TEMPLATE: return init_k1(m, b, out, err);
+    case ASP_SHARED_MEMORY_TEMPLATE: return init_k5(m, b, out, err);
+    case ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE: return init_k9(m, b, false, out, err);
+    case ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE: return init_k9(m, b, true, out, err);
     default: err = "template not implemented by the host lowering"; return false;
     }
 }
