@@ -2,6 +2,7 @@
 // execution from a textual spec, access to the lowered templates.
 #include <string.h>
 
+#include <algorithm>
 #include <map>
 #include <new>
 #include <sstream>
@@ -126,6 +127,31 @@ bool apply_sub_node(CompressedBlock &b, const std::vector<std::string> &tok, std
         return err = "unknown compressed-view node " + op, false;
     return true;
 }
+
+bool apply_dense_node(Matrix &m, const std::vector<std::string> &tok, bool &compressed, std::string &err)
+{
+    if (tok[0] == "sort")
+    {
+        const u64 step = tok.size() > 1 ? strtoull(tok[1].c_str(), nullptr, 10) : 1;
+        if (step == 0 || m.is_sorted || m.is_blocked) return err = "bad dense sort", false;
+        dense_row_coarse_sort(m, step);
+    }
+    else if (tok[0] == "rowdiv_exp")
+    {
+        if (tok.size() < 4 || m.is_blocked) return err = "bad dense rowdiv_exp", false;
+        const u64 lo = strtoull(tok[1].c_str(), nullptr, 10), hi = strtoull(tok[2].c_str(), nullptr, 10), rate = strtoull(tok[3].c_str(), nullptr, 10);
+        if (lo == 0 || hi < lo || rate < 2) return err = "bad dense rowdiv_exp parameters", false;
+        dense_row_div(m, row_div_position_exponential(m, lo, hi, rate));
+    }
+    else if (tok[0] == "compress")
+    {
+        compress_dense_view(m);
+        compressed = true;
+    }
+    else
+        return err = "unknown dense-view node " + tok[0], false;
+    return true;
+}
 } // namespace
 
 extern "C" {
@@ -193,6 +219,65 @@ uint64_t asp_matrix_rows(const asp_matrix *m) { return m ? m->m->n_rows : 0; }
 uint64_t asp_matrix_cols(const asp_matrix *m) { return m ? m->m->n_cols : 0; }
 uint64_t asp_matrix_nnz(const asp_matrix *m) { return m ? m->m->nnz : 0; }
 
+asp_status asp_dense_execute(const asp_matrix *in, const char *spec, asp_matrix **out)
+{
+    if (!in || !spec || !out) return hfail(ASP_ERR_INVALID_ARG, "NULL argument");
+    *out = nullptr;
+    if (in->m->is_compressed) return hfail(ASP_ERR_INVALID_ARG, "matrix is already compressed");
+    try
+    {
+        std::unique_ptr<asp_matrix> h(new asp_matrix());
+        h->m.reset(new Matrix(*in->m));
+        Matrix &m = *h->m;
+        bool compressed = false;
+        std::istringstream f(spec);
+        std::string line;
+        while (std::getline(f, line))
+        {
+            const size_t hash = line.find('#');
+            if (hash != std::string::npos) line = line.substr(0, hash);
+            std::istringstream is(line);
+            std::vector<std::string> tok;
+            std::string w;
+            while (is >> w) tok.push_back(w);
+            if (tok.empty()) continue;
+            if (tok[0] != "dense" || tok.size() < 2) return hfail(ASP_ERR_INVALID_ARG, "only dense-view nodes are allowed here: " + line);
+            if (compressed) return hfail(ASP_ERR_INVALID_ARG, "dense-view node after compress");
+            std::string err;
+            if (!apply_dense_node(m, std::vector<std::string>(tok.begin() + 1, tok.end()), compressed, err)) return hfail(ASP_ERR_INVALID_ARG, err);
+        }
+        if (!compressed) compress_dense_view(m);
+        std::vector<u32>().swap(m.col);
+        std::vector<uint8_t>().swap(m.val.b);
+        *out = h.release();
+    }
+    catch (const std::bad_alloc &)
+    {
+        return hfail(ASP_ERR_ALLOC, "host allocation failed");
+    }
+    return ASP_OK;
+}
+
+int asp_matrix_num_subs(const asp_matrix *m) { return (m && m->m->is_compressed) ? (int)m->m->blocks.size() : 0; }
+
+asp_status asp_matrix_sub_rows(const asp_matrix *m, int sub, uint64_t *n_rows, uint64_t *nnz, uint64_t *min_row_nnz, uint64_t *max_row_nnz)
+{
+    if (!m || !m->m->is_compressed || sub < 0 || sub >= (int)m->m->blocks.size()) return hfail(ASP_ERR_INVALID_ARG, "bad sub-matrix id");
+    const CompressedBlock &b = m->m->blocks[sub];
+    u64 mn = ~0ull, mx = 0;
+    for (u64 r = 0; r < b.n_rows; r++)
+    {
+        const u64 l = b.rowptr[r + 1] - b.rowptr[r];
+        mn = std::min(mn, l);
+        mx = std::max(mx, l);
+    }
+    if (n_rows) *n_rows = b.n_rows;
+    if (nnz) *nnz = b.col.size();
+    if (min_row_nnz) *min_row_nnz = mn;
+    if (max_row_nnz) *max_row_nnz = mx;
+    return ASP_OK;
+}
+
 asp_status asp_graph_execute(const asp_matrix *in, const char *spec, asp_format **out)
 {
     if (!in || !spec || !out) return hfail(ASP_ERR_INVALID_ARG, "NULL argument");
@@ -235,45 +320,74 @@ asp_status asp_graph_execute(const asp_matrix *in, const char *spec, asp_format 
     try
     {
         std::unique_ptr<asp_format> F(new asp_format());
-        F->m.reset(new Matrix(*in->m));
-        Matrix &m = *F->m;
-        bool compressed = false;
-        for (const std::vector<std::string> &tok : dense_ops)
+        auto sub_spec_of = [&](size_t i) -> const SubSpec * {
+            if (subs.count((long)i)) return &subs[(long)i];
+            if (subs.count(-1)) return &subs[-1];
+            return nullptr;
+        };
+        if (in->m->is_compressed)
         {
-            if (compressed) return hfail(ASP_ERR_INVALID_ARG, "dense-view node after compress");
-            if (tok[0] == "sort")
+            // the dense view has been executed already (asp_dense_execute): copy only the blocks
+            // this graph lowers, the way the reference value-copies the compressed matrix per trial
+            if (!dense_ops.empty()) return hfail(ASP_ERR_INVALID_ARG, "dense-view node on a matrix that is already compressed");
+            const Matrix &src = *in->m;
+            F->m.reset(new Matrix());
+            Matrix &m = *F->m;
+            m.n_rows = src.n_rows;
+            m.n_cols = src.n_cols;
+            m.nnz = src.nnz;
+            m.val_dt = src.val_dt;
+            m.is_sorted = src.is_sorted;
+            m.sorted_row_index = src.sorted_row_index;
+            m.perm_dt = src.perm_dt;
+            m.perm = src.perm;
+            m.is_blocked = src.is_blocked;
+            m.is_compressed = true;
+            m.ranges = src.ranges;
+            m.blocks.resize(src.blocks.size());
+            for (size_t i = 0; i < src.blocks.size(); i++)
             {
-                const u64 step = tok.size() > 1 ? strtoull(tok[1].c_str(), nullptr, 10) : 1;
-                if (step == 0 || m.is_sorted || m.is_blocked) return hfail(ASP_ERR_INVALID_ARG, "bad dense sort");
-                dense_row_coarse_sort(m, step);
+                const SubSpec *sp = sub_spec_of(i);
+                if (!sp) return hfail(ASP_ERR_INVALID_ARG, "no spec for sub-matrix " + std::to_string(i));
+                if (template_of_name(sp->templ) == ASP_EMPTY_TEMPLATE)
+                {
+                    CompressedBlock &b = m.blocks[i];
+                    const CompressedBlock &o = src.blocks[i];
+                    b.min_row = o.min_row, b.max_row = o.max_row, b.min_col = o.min_col, b.max_col = o.max_col;
+                    b.begin_coo = o.begin_coo, b.end_coo = o.end_coo;
+                }
+                else
+                    m.blocks[i] = src.blocks[i];
             }
-            else if (tok[0] == "rowdiv_exp")
-            {
-                if (tok.size() < 4 || m.is_blocked) return hfail(ASP_ERR_INVALID_ARG, "bad dense rowdiv_exp");
-                const u64 lo = strtoull(tok[1].c_str(), nullptr, 10), hi = strtoull(tok[2].c_str(), nullptr, 10), rate = strtoull(tok[3].c_str(), nullptr, 10);
-                if (lo == 0 || hi < lo || rate < 2) return hfail(ASP_ERR_INVALID_ARG, "bad dense rowdiv_exp parameters");
-                dense_row_div(m, row_div_position_exponential(m, lo, hi, rate));
-            }
-            else if (tok[0] == "compress")
-            {
-                compress_dense_view(m);
-                compressed = true;
-            }
-            else
-                return hfail(ASP_ERR_INVALID_ARG, "unknown dense-view node " + tok[0]);
         }
-        if (!compressed) compress_dense_view(m);
-        // the dense view is no longer needed once every block holds its slice
-        std::vector<u32>().swap(m.col);
-        std::vector<uint8_t>().swap(m.val.b);
+        else
+        {
+            F->m.reset(new Matrix(*in->m));
+            Matrix &m = *F->m;
+            bool compressed = false;
+            for (const std::vector<std::string> &tok : dense_ops)
+            {
+                if (compressed) return hfail(ASP_ERR_INVALID_ARG, "dense-view node after compress");
+                std::string err;
+                if (!apply_dense_node(m, tok, compressed, err)) return hfail(ASP_ERR_INVALID_ARG, err);
+            }
+            if (!compressed) compress_dense_view(m);
+            // the dense view is no longer needed once every block holds its slice
+            std::vector<u32>().swap(m.col);
+            std::vector<uint8_t>().swap(m.val.b);
+        }
+        Matrix &m = *F->m;
         const size_t nsub = m.blocks.size();
         F->subs.resize(nsub);
         for (size_t i = 0; i < nsub; i++)
         {
-            const SubSpec *s = nullptr;
-            if (subs.count((long)i)) s = &subs[(long)i];
-            else if (subs.count(-1)) s = &subs[-1];
-            else return hfail(ASP_ERR_INVALID_ARG, "no spec for sub-matrix " + std::to_string(i));
+            const SubSpec *s = sub_spec_of(i);
+            if (!s) return hfail(ASP_ERR_INVALID_ARG, "no spec for sub-matrix " + std::to_string(i));
+            if (template_of_name(s->templ) == ASP_EMPTY_TEMPLATE)
+            {
+                F->subs[i] = TemplateData();
+                continue;
+            }
             CompressedBlock &b = m.blocks[i];
             std::string err;
             for (const std::vector<std::string> &tok : s->nodes)

@@ -22,6 +22,7 @@ HOST_EXPORTS = [
     "asp_matrix_from_csr", "asp_matrix_from_coo_file", "asp_matrix_destroy", "asp_matrix_rows", "asp_matrix_cols",
     "asp_matrix_nnz", "asp_graph_execute", "asp_format_destroy", "asp_format_num_subs", "asp_format_global_perm",
     "asp_format_sub_info", "asp_format_plan_descs", "asp_format_padding_rate", "asp_host_last_error",
+    "asp_dense_execute", "asp_matrix_num_subs", "asp_matrix_sub_rows",
 ]
 
 _bound = False
@@ -42,6 +43,12 @@ def _lib():
             fn.restype = C.c_uint64
         L.asp_graph_execute.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]
         L.asp_graph_execute.restype = C.c_int
+        L.asp_dense_execute.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p)]
+        L.asp_dense_execute.restype = C.c_int
+        L.asp_matrix_num_subs.argtypes = [C.c_void_p]
+        L.asp_matrix_num_subs.restype = C.c_int
+        L.asp_matrix_sub_rows.argtypes = [C.c_void_p, C.c_int] + [C.POINTER(C.c_uint64)] * 4
+        L.asp_matrix_sub_rows.restype = C.c_int
         L.asp_format_destroy.argtypes = [C.c_void_p]
         L.asp_format_destroy.restype = None
         L.asp_format_num_subs.argtypes = [C.c_void_p]
@@ -101,6 +108,23 @@ class Matrix:
     @property
     def nnz(self):
         return int(_lib().asp_matrix_nnz(self._h))
+
+    def dense(self, dense_spec: str = "dense compress") -> "Matrix":
+        """Run only the dense-view nodes (sort / row division / compress); the result can be lowered
+        repeatedly with execute() on `sub ...` lines."""
+        h = C.c_void_p()
+        _check(_lib().asp_dense_execute(self._h, dense_spec.encode(), C.byref(h)))
+        return Matrix(h)
+
+    @property
+    def n_subs(self) -> int:
+        return int(_lib().asp_matrix_num_subs(self._h))
+
+    def sub_rows(self, i: int):
+        """(rows, nnz, min row nnz, max row nnz) of sub-matrix i of a compressed matrix."""
+        v = [C.c_uint64() for _ in range(4)]
+        _check(_lib().asp_matrix_sub_rows(self._h, i, *[C.byref(x) for x in v]))
+        return tuple(int(x.value) for x in v)
 
     def execute(self, spec: str) -> "Format":
         """Run an Operator Graph (see include/asp_b200_host.h for the spec grammar)."""

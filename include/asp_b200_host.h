@@ -48,6 +48,19 @@ uint64_t asp_matrix_nnz(const asp_matrix *m);
  * (execute_default_div_to_complete_each_level_blocking, default_auto_tuner.cc:384).
  */
 asp_status asp_graph_execute(const asp_matrix *m, const char *spec, asp_format **out);
+
+/* Dense-view part of a graph on its own (`dense ...` lines only; compress is implied): returns a
+ * compressed matrix whose sub-matrices can then be lowered again and again with
+ * asp_graph_execute(`sub ...` lines only). This is how the reference's tuner works: the dense
+ * view is executed once per dense strategy (execute_dense_matrix_exe_graph_with_param_strategy,
+ * default_auto_tuner.cc:2073) and value-copied for every compressed-view trial
+ * (val_copy_from_old_matrix_struct, struct.cc:392). Sub-matrices whose spec names the template
+ * EMPTY are neither copied nor lowered (EMPTY_TEMPLATE of the reference, empty_op.cc). */
+asp_status asp_dense_execute(const asp_matrix *m, const char *dense_spec, asp_matrix **out);
+/* number of sub-matrices of a compressed matrix (0 before compress) */
+int asp_matrix_num_subs(const asp_matrix *m);
+/* row statistics of one sub-matrix: what the tuner's rule gates look at (matrix_info.cc:122-190) */
+asp_status asp_matrix_sub_rows(const asp_matrix *m, int sub, uint64_t *n_rows, uint64_t *nnz, uint64_t *min_row_nnz, uint64_t *max_row_nnz);
 void asp_format_destroy(asp_format *f);
 
 int asp_format_num_subs(const asp_format *f);

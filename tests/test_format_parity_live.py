@@ -1,0 +1,68 @@
+"""CPU suite, part 4: native operators against the reference host code, run live.
+
+Needs oracle/_ref/ref_dump (built from the reference tree by oracle/Makefile); skipped where
+it is absent. Sweeps node parameters the committed fixtures do not cover."""
+import numpy as np
+import pytest
+
+import refdump
+from alphasparse_b200 import matrices as M
+from alphasparse_b200.graph import Matrix
+from test_format_parity import compare_with_manifest
+
+pytestmark = pytest.mark.skipif(not refdump.have_ref_dump(), reason="reference format oracle not built")
+
+
+def _uniform():
+    return M.uniform_random(768, 12, seed=11)[0]
+
+
+def _long_rows():
+    rng = np.random.default_rng(5)
+    return M.from_row_lengths(rng.integers(40, 300, size=512), 4096, seed=6, dtype=np.float64)[0]
+
+
+def _mixed():
+    rng = np.random.default_rng(7)
+    lengths = np.concatenate([rng.integers(520, 900, size=16), rng.integers(130, 500, size=120), rng.integers(33, 127, size=400),
+                              np.minimum(rng.zipf(2.0, size=3000), 31)])
+    rng.shuffle(lengths)
+    return M.from_row_lengths(lengths, 8192, seed=8)[0]
+
+
+CASES = [
+    ("uniform", _uniform, "dense compress\nsub all row_padding 192 1\nsub all blb_row_evenly 192\nsub all tlb_row\nsub all template K2"),
+    ("uniform", _uniform, "dense compress\nsub all row_padding 64 1\nsub all blb_row_evenly 64\nsub all tlb_col_fixed 7\nsub all template K6"),
+    ("uniform", _uniform, "dense compress\nsub all row_padding 32 1\nsub all blb_row_evenly 32\nsub all tlb_col_fixed 1\nsub all template K6"),
+    ("uniform", _uniform, "dense compress\nsub all blb_row_nnz 128\nsub all tlb_col_fixed 2\nsub all template K6"),
+    ("uniform", _uniform, "dense compress\nsub all tlb_nnz 2\nsub all template K9"),
+    ("uniform", _uniform, "dense compress\nsub all tlb_nnz 7\nsub all template K10"),
+    ("uniform", _uniform, "dense compress\nsub all tlb_nnz 16\nsub all template K9"),
+    ("uniform", _uniform, "dense compress\nsub all blb_row_evenly 96\nsub all wlb_row_evenly 32\nsub all tlb_col_fixed 3\nsub all template K1"),
+    ("uniform", _uniform, "dense compress\nsub all blb_row_evenly 128\nsub all wlb_row_evenly 8\nsub all tlb_row\nsub all template K5"),
+    ("long", _long_rows, "dense compress\nsub all wlb_col_fixed 64\nsub all template K4"),
+    ("long", _long_rows, "dense compress\nsub all wlb_col_fixed 96\nsub all template K4"),
+    ("long", _long_rows, "dense compress\nsub all row_padding 2 1\nsub all blb_row_evenly 2\nsub all wlb_col_fixed 64\nsub all template K8"),
+    ("long", _long_rows, "dense compress\nsub all blb_row_nnz 896\nsub all wlb_col_fixed 128\nsub all template K8"),
+    ("long", _long_rows, "dense compress\nsub all blb_col_fixed 64\nsub all template K7"),
+    ("long", _long_rows, "dense compress\nsub all blb_col_fixed 256\nsub all template K7"),
+    ("long", _long_rows, "dense compress\nsub all row_padding 32 1\nsub all tlb_row\nsub all template K3"),
+    ("mixed", _mixed, "dense sort 1\ndense compress\nsub all row_padding 64 1\nsub all blb_row_evenly 64\nsub all tlb_col_fixed 4\nsub all template K6"),
+    ("mixed", _mixed, "dense sort 1\ndense compress\nsub all blb_col_fixed 128\nsub all template K7"),
+    ("mixed", _mixed, "dense sort 1\ndense compress\nsub all wlb_col_fixed 32\nsub all template K4"),
+    ("mixed", _mixed, "dense sort 1\ndense compress\nsub all blb_row_nnz 4096\nsub all wlb_col_fixed 32\nsub all template K8"),
+    ("mixed", _mixed, "dense sort 1\ndense rowdiv_exp 128 4096 8\ndense compress\nsub all row_padding 32 1\nsub all blb_row_evenly 32\nsub all tlb_col_fixed 4\nsub all template K6"),
+    ("mixed", _mixed, "dense sort 1\ndense rowdiv_exp 512 4096 16\ndense compress\nsub all blb_row_nnz 4096\nsub all wlb_col_fixed 64\nsub all template K8"),
+]
+_cache = {}
+
+
+@pytest.mark.parametrize("idx", range(len(CASES)))
+def test_native_equals_reference_live(idx):
+    name, gen, spec = CASES[idx]
+    if name not in _cache:
+        _cache[name] = gen()
+    m = _cache[name]
+    man = refdump.run_ref_dump(m, spec)
+    fmt = Matrix.from_csr(m).execute(spec)
+    compare_with_manifest(fmt, man, f"{name}: {spec!r}")

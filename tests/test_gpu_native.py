@@ -1,0 +1,103 @@
+"""GPU suite, native path end to end: seeded matrix -> native Operator Graph -> C-ABI upload ->
+CUDA kernel -> y against the CPU oracle. Sizes are chosen so the oracle finishes in well under a
+second; the full-size configurations are checked the same way inside bench.py."""
+import numpy as np
+import pytest
+
+import refdump
+import specs
+from alphasparse_b200 import capi, matrices as M, tuner
+from alphasparse_b200.graph import Matrix
+
+pytestmark = pytest.mark.gpu
+
+
+def run(ctx, m, x, spec, what):
+    fmt = Matrix.from_csr(m).execute(spec)
+    g = fmt.upload(ctx)
+    y = g.spmv_host(x)
+    y_ref, scale = refdump.csr_ref(m, x)
+    refdump.assert_y(y, y_ref, scale, m.values.dtype, what)
+    g.close()
+    fmt.close()
+
+
+@pytest.fixture(scope="module")
+def mats():
+    rng = np.random.default_rng(3)
+    lengths = np.concatenate([rng.integers(600, 5000, size=24), rng.integers(130, 500, size=300), rng.integers(33, 127, size=2000),
+                              np.minimum(rng.zipf(2.1, size=30000), 31)])
+    rng.shuffle(lengths)
+    return {
+        "uniform_f32": M.uniform_random(20000, 16, seed=0),
+        "laplace_f64": M.laplacian_2d(160, seed=1),
+        "fem_f64": M.block_fem(4096, 27, 256, seed=3),
+        "mixed_f32": M.from_row_lengths(lengths, 40000, seed=2),
+        "rmat_f32": M.rmat(13, 16, seed=4),
+    }
+
+
+@pytest.mark.parametrize("mat", ["uniform_f32", "laplace_f64"])
+@pytest.mark.parametrize("spec", sorted(specs.COMPRESSED_SPECS))
+def test_every_strategy_on_short_row_matrices(asp_ctx, mats, mat, spec):
+    m, x = mats[mat]
+    run(asp_ctx, m, x, specs.full_spec(spec), f"{mat} {spec}")
+
+
+@pytest.mark.parametrize("spec", ["S5_K3", "S1_K2", "S4_K4", "S6_K8", "S7_K8", "S8_K7", "S2_K6", "S9_K9", "S9_K10"])
+def test_block_fem_fp64(asp_ctx, mats, spec):
+    m, x = mats["fem_f64"]
+    run(asp_ctx, m, x, specs.full_spec(spec), f"fem {spec}")
+
+
+@pytest.mark.parametrize("dense", ["dense sort 1\ndense compress", "dense compress"])
+@pytest.mark.parametrize("spec", ["S8_K7", "S4_K4", "S7_K8", "S3_K6", "S2_K6", "X_K1", "X_K5"])
+def test_power_law_rows_sorted_and_unsorted(asp_ctx, mats, dense, spec):
+    m, x = mats["mixed_f32"]
+    run(asp_ctx, m, x, specs.full_spec(spec, dense), f"mixed {dense!r} {spec}")
+
+
+@pytest.mark.parametrize("dense", ["dense sort 1\ndense rowdiv_exp 32 4096 4\ndense compress", "dense sort 1\ndense rowdiv_exp 128 4096 8\ndense compress"])
+@pytest.mark.parametrize("pick", [0, -1])
+def test_sorted_row_division_with_a_template_per_strip(asp_ctx, mats, dense, pick):
+    """Dense-view strategy 3 of the tuner: every strip gets the first / last whitelist strategy its
+    row statistics allow."""
+    m, x = mats["mixed_f32"]
+    hm = Matrix.from_csr(m)
+    cm = hm.dense(dense)
+    assert cm.n_subs >= 3
+    lines = []
+    for i in range(cm.n_subs):
+        rows, nnz, mn, mx = cm.sub_rows(i)
+        cands = tuner.compressed_candidates(mn, mx, nnz / rows, True, quick=True)
+        assert cands, (i, mn, mx)
+        lines.append(cands[pick].lines(i))
+    fmt = cm.execute("\n".join(lines))
+    g = fmt.upload(asp_ctx)
+    y = g.spmv_host(x)
+    y_ref, scale = refdump.csr_ref(m, x)
+    refdump.assert_y(y, y_ref, scale, m.values.dtype, f"{dense!r} pick {pick}: {lines}")
+    g.close()
+    fmt.close()
+
+
+@pytest.mark.parametrize("spec", ["S8_K7", "S9_K9", "S9_K10", "S3_K6", "S7_K8"])
+def test_rows_without_nonzeros(asp_ctx, mats, spec):
+    """R-MAT adjacency has empty rows (the reference's front door rejects them, main.cc:604-621);
+    their y must be exactly 0."""
+    m, x = mats["rmat_f32"]
+    assert (m.row_lengths() == 0).any()
+    run(asp_ctx, m, x, specs.full_spec(spec), f"rmat {spec}")
+    run(asp_ctx, m, x, specs.full_spec(spec, "dense sort 1\ndense compress") if spec not in ("S9_K9", "S9_K10") else specs.full_spec(spec), f"rmat sorted {spec}")
+
+
+@pytest.mark.parametrize("mat", ["uniform_f32", "mixed_f32", "fem_f64"])
+def test_tuner_search_returns_a_correct_plan(asp_ctx, mats, mat):
+    m, x = mats[mat]
+    fmt, group, trials, desc = tuner.search(asp_ctx, m, quick=True, warmup=1, reps=3)
+    assert len(trials) > 0 and desc["subs"]
+    y = group.spmv_host(x)
+    y_ref, scale = refdump.csr_ref(m, x)
+    refdump.assert_y(y, y_ref, scale, m.values.dtype, f"tuner {mat}: {desc}")
+    group.close()
+    fmt.close()
