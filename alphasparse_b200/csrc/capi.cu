@@ -106,6 +106,11 @@ struct asp_ctx
     int device = 0;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    // side streams: the sub-matrix kernels of one SpMV run concurrently (the reference gives every
+    // sub-matrix kernel its own stream, code_builder.cc:1515-1518)
+    static const int kAux = 3;
+    cudaStream_t aux[kAux] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_fork = nullptr, ev_join[kAux] = {nullptr, nullptr, nullptr};
     int sm_count = 0;
     int max_smem_optin = 0;
     // scratch x / y used by asp_time and asp_spmv_host; grown on demand
@@ -127,6 +132,7 @@ struct asp_plan
     uint64_t fmt_bytes = 0;
     uint64_t smem_elems = 0; // partial results per CTA (shared-memory family)
     uint64_t units_for_grid = 0;
+    uint64_t warp_tasks = 0; // SELL-like with equal strips: warp-sized work items
     bool needs_zero = false;
 };
 
@@ -216,6 +222,18 @@ asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threa
         static const char *cap = getenv("ASP_ELL_MAX_GRID");
         if (cap && atoll(cap) > 0 && tblock > atoll(cap)) tblock = atoll(cap);
     }
+    if (t == ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS && threads > 256)
+    {
+        // the SELL-like kernel is compiled for at most 256 threads per CTA (register budget); its
+        // strip loop is CTA-stride, so a narrower CTA only changes how a strip is walked
+        threads = 256;
+    }
+    if (t == ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS && p->warp_tasks > 0)
+    {
+        threads = (threads + 31) / 32 * 32;
+        const int64_t needed = (int64_t)((p->warp_tasks + (uint64_t)(threads / 32) - 1) / (uint64_t)(threads / 32));
+        if (tblock > needed) tblock = needed > 0 ? needed : 1;
+    }
     p->grid = (unsigned)tblock;
     p->block = (unsigned)threads;
     return ASP_OK;
@@ -287,6 +305,12 @@ asp_status asp_ctx_create(int device, asp_ctx **out)
     cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreate(&c->ev0);
     if (e == cudaSuccess) e = cudaEventCreate(&c->ev1);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming);
+    for (int i = 0; i < asp_ctx::kAux && e == cudaSuccess; i++)
+    {
+        e = cudaStreamCreateWithFlags(&c->aux[i], cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_join[i], cudaEventDisableTiming);
+    }
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, device);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
     if (e != cudaSuccess)
@@ -307,6 +331,12 @@ void asp_ctx_destroy(asp_ctx *c)
     if (c->y) cudaFree(c->y);
     if (c->ev0) cudaEventDestroy(c->ev0);
     if (c->ev1) cudaEventDestroy(c->ev1);
+    if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+    for (int i = 0; i < asp_ctx::kAux; i++)
+    {
+        if (c->ev_join[i]) cudaEventDestroy(c->ev_join[i]);
+        if (c->aux[i]) cudaStreamDestroy(c->aux[i]);
+    }
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
@@ -526,6 +556,11 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
             }
             p->vec = p->val_is_f64 ? 2 : 4;
             p->units_for_grid = B;
+            {
+                // equal strips: the kernel walks warp tasks of 32 * vec TLBs (see k_sell)
+                const HostMeta &bt = hm[asp::MS_BLK_THR];
+                if (bt.kind == ASP_COMPRESS_LINEAR && bt.coef > 0 && bt.coef % (32ull * p->vec) == 0) p->warp_tasks = B * (bt.coef / (32ull * p->vec));
+            }
             break;
         }
         case ASP_DIRECT_ATOM_TEMPLATE:
@@ -695,16 +730,40 @@ asp_status asp_spmv(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const voi
     if (zero_y == 2)
         for (int i = 0; i < n_plans; i++) clear = clear || (plans[i]->templ != ASP_EMPTY_TEMPLATE && plans[i]->needs_zero);
     if (clear) ASP_CUDA(cudaMemsetAsync(d_y, 0, first->n_rows * (first->val_is_f64 ? 8 : 4), ctx->stream));
+    int active = 0;
+    for (int i = 0; i < n_plans; i++) active += plans[i]->templ != ASP_EMPTY_TEMPLATE;
+    const bool fork = active > 1;
+    if (fork) ASP_CUDA(cudaEventRecord(ctx->ev_fork, ctx->stream));
+    bool used[asp_ctx::kAux] = {false, false, false};
+    int k = 0;
     for (int i = 0; i < n_plans; i++)
     {
         asp_plan *p = plans[i];
         if (p->templ == ASP_EMPTY_TEMPLATE) continue;
         if (p->val_is_f64 != first->val_is_f64 || p->n_rows != first->n_rows || p->n_cols != first->n_cols)
             return fail(ASP_ERR_INVALID_ARG, "plans of different matrices in one call");
+        cudaStream_t st = ctx->stream;
+        if (fork && k > 0)
+        {
+            const int j = (k - 1) % asp_ctx::kAux;
+            st = ctx->aux[j];
+            if (!used[j])
+            {
+                ASP_CUDA(cudaStreamWaitEvent(st, ctx->ev_fork, 0));
+                used[j] = true;
+            }
+        }
+        k++;
         p->args.x = d_x;
         p->args.y = d_y;
-        ASP_CUDA(asp::launch_template(p->templ, p->val_is_f64, p->col_width, p->args, p->grid, p->block, p->smem, ctx->stream, p->vec));
+        ASP_CUDA(asp::launch_template(p->templ, p->val_is_f64, p->col_width, p->args, p->grid, p->block, p->smem, st, p->vec));
     }
+    for (int j = 0; j < asp_ctx::kAux; j++)
+        if (used[j])
+        {
+            ASP_CUDA(cudaEventRecord(ctx->ev_join[j], ctx->aux[j]));
+            ASP_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_join[j], 0));
+        }
     return ASP_OK;
 }
 

@@ -258,22 +258,99 @@ __global__ void __launch_bounds__(512) k_ell(const KArgs a)
 }
 
 // ---------------------------------------------------------------------------------------------
-// DIRECT_ATOM_TEMPLATE_WARP_COMPRESS (SELL-like): CTA <-> BLB (row strip); inside the strip
-// element k of local TLB i sits at nz0 + i + k*n, n = TLBs of the strip.
+// DIRECT_ATOM_TEMPLATE_WARP_COMPRESS (SELL-like): inside BLB b (a row strip of n TLBs) element k
+// of local TLB i sits at nz0 + i + k*n.
+//
+// Strips of equal size (block_begin_thread_index_offset is linear, as ROW_PADDING + even row
+// division gives) are cut into warp tasks of 32*V TLBs that a persistent grid of warps walks, so
+// thousands of tiny strips cost no CTA launches; otherwise one CTA takes one strip at a time.
 // ---------------------------------------------------------------------------------------------
 template <class VT, class CT, int V>
-__global__ void __launch_bounds__(1024) k_sell(const KArgs a)
+__device__ __forceinline__ void sell_group(const KArgs &a, const VT *__restrict__ val, const CT *__restrict__ col, const VT *__restrict__ x,
+                                           VT *__restrict__ y, u64 nz, u64 n, u32 S, u64 t0, u64 radd)
+{
+    VT acc[V];
+#pragma unroll
+    for (int j = 0; j < V; j++) acc[j] = 0;
+    const VT *vp = val + nz;
+    const CT *cp = col + nz;
+    constexpr int U = 4;
+    for (u32 k0 = 0; k0 < S; k0 += U)
+    {
+        VT v[U][V];
+        CT c[U][V];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (k0 + u < S)
+            {
+                ld_stream_n<VT, V>(vp + (u64)(k0 + u) * n, v[u]);
+                ld_stream_n<CT, V>(cp + (u64)(k0 + u) * n, c[u]);
+            }
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (k0 + u < S)
+            {
+#pragma unroll
+                for (int j = 0; j < V; j++) acc[j] += v[u][j] * __ldg(x + c[u][j]);
+            }
+    }
+    const Meta &rm = a.m[MS_ROW_OF_TLB];
+    if (V == 4 && rm.kind == MK_ARRAY && rm.width == 4 && (t0 & 3) == 0 && t0 + V <= a.effective)
+    {
+        const uint4 r = __ldg(reinterpret_cast<const uint4 *>((const unsigned int *)rm.p + t0));
+        out_add(y, (u64)r.x + radd, acc[0], a.atomic != 0);
+        out_add(y, (u64)r.y + radd, acc[1 % V], a.atomic != 0);
+        out_add(y, (u64)r.z + radd, acc[2 % V], a.atomic != 0);
+        out_add(y, (u64)r.w + radd, acc[3 % V], a.atomic != 0);
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < V; j++)
+    {
+        const u64 t = t0 + j;
+        if (t < a.effective) out_add(y, mget(rm, t) + radd, acc[j], a.atomic != 0);
+    }
+}
+
+template <class VT, class CT, int V>
+__global__ void __launch_bounds__(256) k_sell(const KArgs a)
 {
     const VT *__restrict__ val = (const VT *)a.val;
     const CT *__restrict__ col = (const CT *)a.col;
     const VT *__restrict__ x = (const VT *)a.x + a.first_col;
     VT *__restrict__ y = (VT *)a.y;
     const u64 radd = a.row_add ? a.first_row : 0;
+    const Meta &bt = a.m[MS_BLK_THR];
+    if (V > 1 && bt.kind == MK_LINEAR && bt.coef > 0 && (bt.coef % (32 * V)) == 0)
+    {
+        const u64 n = bt.coef;
+        const u64 tasks_per_blb = n / (32 * V);
+        const u64 total = a.n_units * tasks_per_blb;
+        const u32 lane = threadIdx.x & 31;
+        const u64 wstride = ((u64)gridDim.x * blockDim.x) >> 5;
+        for (u64 task = ((u64)blockIdx.x * blockDim.x + threadIdx.x) >> 5; task < total; task += wstride)
+        {
+            const u64 b = task / tasks_per_blb;
+            const u64 i = (task - b * tasks_per_blb) * (32 * V) + (u64)lane * V;
+            const u64 t0 = bt.icpt + b * n + i;
+            if (t0 >= a.effective) continue;
+            const u64 nz0 = mget(a.m[MS_BLK_NZ], b);
+            const u32 S = (u32)mget(a.m[MS_TLB_SIZE], b);
+            if ((nz0 % V) == 0)
+                sell_group<VT, CT, V>(a, val, col, x, y, nz0 + i, n, S, t0, radd);
+            else
+            {
+#pragma unroll
+                for (int j = 0; j < V; j++) sell_group<VT, CT, 1>(a, val, col, x, y, nz0 + i + j, n, S, t0 + j, radd);
+            }
+        }
+        return;
+    }
     for (u64 b = blockIdx.x; b < a.n_units; b += gridDim.x)
     {
         const u64 nz0 = mget(a.m[MS_BLK_NZ], b);
-        const u64 t0 = mget(a.m[MS_BLK_THR], b);
-        const u64 t1 = mget(a.m[MS_BLK_THR], b + 1);
+        const u64 t0 = mget(bt, b);
+        const u64 t1 = mget(bt, b + 1);
         const u32 S = (u32)mget(a.m[MS_TLB_SIZE], b);
         const u64 n = t1 - t0;
         if (t0 >= a.effective) continue;
@@ -282,48 +359,15 @@ __global__ void __launch_bounds__(1024) k_sell(const KArgs a)
             for (u64 i = (u64)threadIdx.x * V; i < n; i += (u64)blockDim.x * V)
             {
                 if (t0 + i >= a.effective) break;
-                VT acc[V];
-#pragma unroll
-                for (int j = 0; j < V; j++) acc[j] = 0;
-                const VT *vp = val + nz0 + i;
-                const CT *cp = col + nz0 + i;
-#pragma unroll 4
-                for (u32 k = 0; k < S; k++)
-                {
-                    VT v[V];
-                    CT c[V];
-                    ld_stream_n<VT, V>(vp, v);
-                    ld_stream_n<CT, V>(cp, c);
-#pragma unroll
-                    for (int j = 0; j < V; j++) acc[j] += v[j] * __ldg(x + c[j]);
-                    vp += n;
-                    cp += n;
-                }
-#pragma unroll
-                for (int j = 0; j < V; j++)
-                {
-                    const u64 t = t0 + i + j;
-                    if (t < a.effective) out_add(y, mget(a.m[MS_ROW_OF_TLB], t) + radd, acc[j], a.atomic != 0);
-                }
+                sell_group<VT, CT, V>(a, val, col, x, y, nz0 + i, n, S, t0 + i, radd);
             }
         }
         else
         {
             for (u64 i = threadIdx.x; i < n; i += blockDim.x)
             {
-                const u64 t = t0 + i;
-                if (t >= a.effective) break;
-                VT acc = 0;
-                const VT *vp = val + nz0 + i;
-                const CT *cp = col + nz0 + i;
-#pragma unroll 4
-                for (u32 k = 0; k < S; k++)
-                {
-                    acc += __ldcs(vp) * __ldg(x + __ldcs(cp));
-                    vp += n;
-                    cp += n;
-                }
-                out_add(y, mget(a.m[MS_ROW_OF_TLB], t) + radd, acc, a.atomic != 0);
+                if (t0 + i >= a.effective) break;
+                sell_group<VT, CT, 1>(a, val, col, x, y, nz0 + i, n, S, t0 + i, radd);
             }
         }
     }

@@ -72,13 +72,13 @@ def compressed_candidates(mn: int, mx: int, avg: float, is_sorted: bool, quick: 
         while c <= min(4096, _ceil32(mx)):
             cs.append(c)
             c *= 2
-        for c in ((cs[len(cs) // 2:][:2] or cs) if quick else cs):
-            out.append(Candidate(f"S8_K7_c{c}", [f"blb_col_fixed {c}"], "K7", [(t, 1) for t in sorted({min(1024, max(32, c // 4)), min(1024, max(64, c // 2))})]))
+        for c in (cs[-2:] if quick else cs):
+            out.append(Candidate(f"S8_K7_c{c}", [f"blb_col_fixed {c}"], "K7", [(t, 1) for t in sorted({min(1024, max(32, c // 16)), min(1024, max(64, c // 8)), min(1024, max(64, c // 4))})]))
     if mx <= 512:
         out.append(Candidate("S5_K3", ["row_padding 32 1", "tlb_row"], "K3", [(t, 1) for t in T3]))
         for mm in ([128, 256] if quick else [64, 128, 192, 256]):
             out.append(Candidate(f"S1_K2_m{mm}", [f"row_padding {mm} 1", f"blb_row_evenly {mm}", "tlb_row"], "K2",
-                                 [(t, 1) for t in sorted({max(32, mm // 4), max(32, mm // 2)})]))
+                                 [(t, 1) for t in (128, 256)]))
         if not is_sorted:
             # strategy 9: TLB_NNZ_DIV(s) -> CSR5-like templates, s = 2 .. min(avg, 32)
             hi = int(max(2, min(avg, 32)))
@@ -231,5 +231,22 @@ def search(ctx: capi.Context, m: CsrMatrix, quick: bool = True, warmup: int = 2,
     if winner is None:
         raise RuntimeError("no graph could be built and timed for this matrix")
     ms, dense, picks, fmt, group = winner
-    desc = {"dense": dense.replace("\n", " | "), "subs": [{"graph": c.name, "threads": l[0], "row_reduce": l[1]} for c, l, _ in picks]}
+    desc = {"dense": dense.replace("\n", " | "),
+            "subs": [{"graph": c.name, "nodes": c.nodes, "template": c.template, "threads": l[0], "row_reduce": l[1]} for c, l, _ in picks]}
     return fmt, group, trials, desc
+
+
+def build(ctx: capi.Context, m: CsrMatrix, desc: dict):
+    """Lower and upload exactly the graph a previous search() described (no timing)."""
+    hm = Matrix.from_csr(m)
+    cm = hm.dense(desc["dense"].replace(" | ", "\n"))
+    if cm.n_subs != len(desc["subs"]):
+        raise ValueError(f"graph describes {len(desc['subs'])} sub-matrices, the dense view gives {cm.n_subs}")
+    spec = "\n".join(Candidate(s["graph"], s["nodes"], s["template"], []).lines(i) for i, s in enumerate(desc["subs"]))
+    fmt = cm.execute(spec)
+    group = fmt.upload(ctx)
+    for i, s in enumerate(desc["subs"]):
+        set_launch(fmt, group, i, s["threads"], s["row_reduce"])
+    cm.close()
+    hm.close()
+    return fmt, group

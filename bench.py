@@ -146,6 +146,7 @@ def main():
     ap.add_argument("--dense", default="dense compress", help="with --spec: dense-view nodes, '|'-separated")
     ap.add_argument("--spec", default=None, help="run exactly this compressed-view graph (name from the candidate list)")
     ap.add_argument("--threads", type=int, default=0, help="with --spec: thread_num_in_block")
+    ap.add_argument("--graph", default=None, help="skip the search: a bench JSON line file (its config.graph is used) or the graph JSON itself")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
@@ -207,6 +208,10 @@ def main():
         graph_desc = {"dense": args.dense, "subs": [{"graph": cand[0].name, "threads": th, "row_reduce": red}]}
         cm.close()
         hm.close()
+    elif args.graph:
+        graph_desc = json.load(open(args.graph))["config"]["graph"] if os.path.exists(args.graph) else json.loads(args.graph)
+        fmt, group = tuner.build(ctx, m, graph_desc)
+        trials = []
     else:
         fmt, group, trials, graph_desc = tuner.search(ctx, m, quick=not args.full_search, log=log)
     search_s = time.perf_counter() - t_s
