@@ -214,6 +214,25 @@ asp_status asp_matrix_from_coo_file(const char *path, int val_dtype, asp_matrix 
     return ASP_OK;
 }
 
+asp_status asp_partition_rows_by_nnz(uint64_t n_rows, const int64_t *indptr, int parts, uint64_t *bounds)
+{
+    if (!indptr || !bounds || parts <= 0 || n_rows == 0) return hfail(ASP_ERR_INVALID_ARG, "NULL argument or parts <= 0");
+    const int64_t nnz = indptr[n_rows];
+    bounds[0] = 0;
+    for (int p = 1; p < parts; p++)
+    {
+        // first row whose offset reaches p/parts of the non-zeros; rows are never split
+        const int64_t target = (int64_t)(((__int128)nnz * p) / parts);
+        const int64_t *it = std::lower_bound(indptr, indptr + n_rows + 1, target);
+        uint64_t r = (uint64_t)(it - indptr);
+        if (r > n_rows) r = n_rows;
+        if (r < bounds[p - 1]) r = bounds[p - 1];
+        bounds[p] = r;
+    }
+    bounds[parts] = n_rows;
+    return ASP_OK;
+}
+
 void asp_matrix_destroy(asp_matrix *m) { delete m; }
 uint64_t asp_matrix_rows(const asp_matrix *m) { return m ? m->m->n_rows : 0; }
 uint64_t asp_matrix_cols(const asp_matrix *m) { return m ? m->m->n_cols : 0; }

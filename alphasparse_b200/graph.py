@@ -22,7 +22,7 @@ HOST_EXPORTS = [
     "asp_matrix_from_csr", "asp_matrix_from_coo_file", "asp_matrix_destroy", "asp_matrix_rows", "asp_matrix_cols",
     "asp_matrix_nnz", "asp_graph_execute", "asp_format_destroy", "asp_format_num_subs", "asp_format_global_perm",
     "asp_format_sub_info", "asp_format_plan_descs", "asp_format_padding_rate", "asp_host_last_error",
-    "asp_dense_execute", "asp_matrix_num_subs", "asp_matrix_sub_rows",
+    "asp_dense_execute", "asp_matrix_num_subs", "asp_matrix_sub_rows", "asp_partition_rows_by_nnz",
 ]
 
 _bound = False
@@ -49,6 +49,8 @@ def _lib():
         L.asp_matrix_num_subs.restype = C.c_int
         L.asp_matrix_sub_rows.argtypes = [C.c_void_p, C.c_int] + [C.POINTER(C.c_uint64)] * 4
         L.asp_matrix_sub_rows.restype = C.c_int
+        L.asp_partition_rows_by_nnz.argtypes = [C.c_uint64, C.c_void_p, C.c_int, C.c_void_p]
+        L.asp_partition_rows_by_nnz.restype = C.c_int
         L.asp_format_destroy.argtypes = [C.c_void_p]
         L.asp_format_destroy.restype = None
         L.asp_format_num_subs.argtypes = [C.c_void_p]
@@ -76,6 +78,14 @@ def _check(status: int):
 _NP_OF_DT = {capi.U8: np.uint8, capi.U16: np.uint16, capi.U32: np.uint32, capi.U64: np.uint64, capi.F32: np.float32, capi.F64: np.float64}
 _ROLE_NAME = {v: k for k, v in capi.ROLE.items()}
 _KIND_NAME = {v: k for k, v in capi.COMPRESS.items()}
+
+
+def partition_rows_by_nnz(indptr: np.ndarray, parts: int) -> np.ndarray:
+    """Row bounds (parts + 1 entries) of contiguous row blocks with about nnz / parts non-zeros each."""
+    ip = np.ascontiguousarray(indptr, dtype=np.int64)
+    out = np.zeros(parts + 1, dtype=np.uint64)
+    _check(_lib().asp_partition_rows_by_nnz(ip.shape[0] - 1, ip.ctypes.data, parts, out.ctypes.data))
+    return out.astype(np.int64)
 
 
 class Matrix:

@@ -82,6 +82,12 @@ asp_status asp_format_plan_descs(const asp_format *f, asp_plan_desc *descs);
 /* per-point padding rate the tuner gates on (PADDING_RATE_UP_BOUND): padded nnz / true nnz */
 double asp_format_padding_rate(const asp_format *f, int sub);
 
+/* No counterpart in the reference (it is single-GPU, code_builder.cc:1483-1489): contiguous row
+ * blocks with about nnz / parts non-zeros each, for sharding a matrix over `parts` GPUs with x
+ * replicated. bounds gets parts + 1 entries, bounds[p] .. bounds[p + 1] is the row range of
+ * part p; a row is never split. */
+asp_status asp_partition_rows_by_nnz(uint64_t n_rows, const int64_t *indptr, int parts, uint64_t *bounds);
+
 /* text of the last error a host-side entry point reported on this thread */
 const char *asp_host_last_error(void);
 

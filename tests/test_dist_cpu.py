@@ -1,0 +1,85 @@
+"""CPU suite, part 5: the multi-GPU plumbing with gloo ranks on the host.
+
+The product's local SpMV needs a GPU; here each rank's slice is computed by the CPU oracle (test
+infrastructure) so that partitioning, the uneven all-gather and the repeated-SpMV loop are checked
+against the single-rank result."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import refdump
+from alphasparse_b200 import matrices as M
+from alphasparse_b200.dist import ShardedSpmv, balanced_bounds_from_degrees
+from alphasparse_b200.graph import partition_rows_by_nnz
+
+
+def test_partition_balances_nnz_and_covers_all_rows():
+    m, _ = M.power_law(50000, 2.1, 3000, seed=2)
+    for parts in (1, 2, 3, 4, 8):
+        b = partition_rows_by_nnz(m.indptr, parts)
+        assert b[0] == 0 and b[-1] == m.n_rows and np.all(np.diff(b) >= 0)
+        per = np.diff(m.indptr[b])
+        assert per.sum() == m.nnz
+        assert per.max() - per.min() <= 2 * m.row_lengths().max()  # each cut is off by at most one row
+    deg = m.row_lengths()
+    assert np.array_equal(balanced_bounds_from_degrees(deg, 4), partition_rows_by_nnz(m.indptr, 4))
+
+
+def test_partition_with_more_parts_than_rows_with_nonzeros():
+    m, _ = M.rmat(6, 2, seed=1)
+    b = partition_rows_by_nnz(m.indptr, 8)
+    assert b[0] == 0 and b[-1] == m.n_rows and np.all(np.diff(b) >= 0)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, iters, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    m, x = M.rmat(10, 8, seed=4)  # has empty rows; values in (0, 1]
+    m.values *= 0.05  # keep x <- A x from overflowing in a few iterations
+    bounds = partition_rows_by_nnz(m.indptr, world)
+    blk = m.row_slice(int(bounds[rank]), int(bounds[rank + 1]))
+
+    def local_spmv(xt, yt):
+        y = refdump.csr_native(blk, xt.numpy())
+        yt[: blk.n_rows] = torch.from_numpy(y)
+
+    sh = ShardedSpmv(local_spmv, bounds, rank, world, torch.float32, "cpu")
+    xt = torch.from_numpy(x.copy())
+    y_slice = sh.spmv_slice(xt).clone()
+    xf = sh.iterate(xt, iters)
+    np.save(os.path.join(out_dir, f"slice_{rank}.npy"), y_slice.numpy())
+    np.save(os.path.join(out_dir, f"final_{rank}.npy"), xf.numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_repeated_spmv_matches_single_rank(world, tmp_path):
+    iters = 4
+    mp.spawn(_worker, args=(world, _free_port(), iters, str(tmp_path)), nprocs=world, join=True)
+    m, x = M.rmat(10, 8, seed=4)
+    m.values *= 0.05
+    ref = x.copy()
+    first = refdump.csr_native(m, ref)
+    for _ in range(iters):
+        ref = refdump.csr_native(m, ref)
+    bounds = partition_rows_by_nnz(m.indptr, world)
+    for r in range(world):
+        sl = np.load(tmp_path / f"slice_{r}.npy")
+        assert np.array_equal(sl, first[bounds[r] : bounds[r + 1]])
+        assert np.array_equal(np.load(tmp_path / f"final_{r}.npy"), ref)
