@@ -1,0 +1,113 @@
+"""The sharded graph workload of bench.py: R-MAT adjacency, nnz-balanced row blocks over the ranks,
+x replicated, `iters` repeated SpMVs with an all-gather of y into the next x (strong scaling: the
+matrix is the same at every N). Returns the fields bench.py prints."""
+from __future__ import annotations
+
+import time
+
+import numpy as np
+import torch
+
+from . import capi, matrices_gpu, tuner
+from .dist import ShardedSpmv, balanced_bounds_from_degrees
+
+
+def run(args, rank: int, world: int, local_rank: int, dist, log):
+    dev = torch.device("cuda", local_rank)
+    scale, ef, seed, iters = args.scale, 16, 4, args.iters
+    n = 1 << scale
+    t0 = time.perf_counter()
+    # pass 1: per-row edge counts (every rank takes a share of the chunks), summed over ranks
+    total = n * ef
+    n_chunks = (total + matrices_gpu.CHUNK - 1) // matrices_gpu.CHUNK
+    deg = matrices_gpu.rmat_row_degrees(scale, ef, seed, dev, chunk_ids=range(rank, n_chunks, world))
+    if dist:
+        dist.all_reduce(deg)
+    bounds = balanced_bounds_from_degrees(deg.cpu().numpy(), world)
+    del deg
+    r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+    # pass 2: this rank's row block (global columns), duplicates merged
+    indptr, cols, vals = matrices_gpu.rmat_block(scale, ef, seed, r0, r1, dev)
+    nnz_local = int(indptr[-1].item())
+    m = matrices_gpu.to_host_csr(indptr, cols, vals, n)
+    del indptr, cols, vals
+    torch.cuda.empty_cache()
+    gen_s = time.perf_counter() - t0
+    if log:
+        log(f"rows [{r0}, {r1}) nnz {nnz_local} generated in {gen_s:.1f} s")
+
+    ctx = capi.Context(local_rank)
+    t0 = time.perf_counter()
+    if args.graph:
+        import json
+        import os
+
+        desc = json.load(open(args.graph))["config"]["graph"] if os.path.exists(args.graph) else json.loads(args.graph)
+        fmt, group = tuner.build(ctx, m, desc)
+        trials = []
+    else:
+        fmt, group, trials, desc = tuner.search(ctx, m, quick=not args.full_search, log=log, warmup=1, reps=5)
+    search_s = time.perf_counter() - t0
+    stream = torch.cuda.ExternalStream(ctx.stream)
+    x0 = matrices_gpu.rmat_x(scale, seed, dev)
+
+    def local_spmv(xt, yt):
+        group.spmv(xt.data_ptr(), yt.data_ptr(), True)  # empty rows are never stored by a kernel: clear y
+
+    with torch.cuda.stream(stream):
+        sh = ShardedSpmv(local_spmv, bounds, rank, world, torch.float32, dev)
+        xa = x0.clone()
+        xb = torch.empty_like(x0)
+        # parity of the first SpMV of this rank's slice against the CPU oracle (bounded sizes only)
+        parity = None
+        y1 = sh.spmv_slice(x0).clone()
+        torch.cuda.synchronize()
+        if m.nnz <= 300_000_000:
+            import os
+            import sys
+
+            sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tests"))
+            import refdump
+
+            y_ref, scl = refdump.csr_ref(m, x0.cpu().numpy())
+            parity = refdump.rel_err(y1.cpu().numpy(), y_ref, scl)
+        W, K = max(args.warmup, 3), max(args.steps, 1)
+        for _ in range(W):
+            sh.local_spmv(xa, sh.y_local)
+            sh.gather_into(xb)
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        c0 = torch.cuda.Event(enable_timing=True)
+        c1 = torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(K):
+            xa.copy_(x0)
+            sh.iterate(xa, iters, xb)
+        e1.record(stream)
+        e1.synchronize()
+        ms_total = e0.elapsed_time(e1)
+        # compute-only time of the same number of local SpMVs (no exchange), for the breakdown
+        c0.record(stream)
+        for _ in range(iters):
+            sh.local_spmv(x0, sh.y_local)
+        c1.record(stream)
+        c1.synchronize()
+        ms_compute = c0.elapsed_time(c1) / iters
+    nnz_total = torch.tensor([nnz_local], dtype=torch.int64, device=dev)
+    t = torch.tensor([ms_total, ms_compute], device=dev)
+    if dist:
+        dist.all_reduce(nnz_total)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t[0].item()) / K  # one step = `iters` repeated SpMVs
+    nnz_all = int(nnz_total.item())
+    out = {
+        "ms_per_step": ms_step, "ms_per_spmv": ms_step / iters, "ms_compute_per_spmv_max": float(t[1].item()),
+        "gflops": 2.0 * nnz_all * iters / (ms_step * 1e-3) * 1e-9, "nnz": nnz_all, "rows": n, "iters": iters, "graph": desc,
+        "search_s": search_s, "gen_s": gen_s, "parity": parity, "rows_local": r1 - r0, "nnz_local": nnz_local,
+        "format_bytes": int(group.format_bytes()), "launches_per_spmv": group.launches(), "m_local": m, "group": group, "ctx": ctx, "x0": x0, "sharded": sh, "fmt": fmt,
+    }
+    return out

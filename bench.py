@@ -135,12 +135,77 @@ def run_reference(args, rank, world):
     print(json.dumps(line))
 
 
+def run_c5(args, rank, world, local_rank, dist):
+    """Sharded R-MAT, repeated SpMV (see alphasparse_b200/bench_rmat.py). One step = `iters` SpMVs."""
+    import torch
+
+    from alphasparse_b200 import bench_rmat
+
+    log = (lambda s: print(f"[rank {rank}] {s}", file=sys.stderr)) if args.verbose else None
+    if args.steps == 200:
+        args.steps = 3  # a step is 100 SpMVs of a ~1e9-nnz matrix
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    r = bench_rmat.run(args, rank, world, local_rank, dist, log)
+    sampler.stop_flag.set()
+    n, nnz, iters = r["rows"], r["nnz"], r["iters"]
+    b_alg = nnz * 8 + 4 * (n + 1) + 4 * (n + n)
+    achieved = b_alg * iters / (r["ms_per_step"] * 1e-3) * 1e-9
+    peak, peak_kind = measured_peak_gbs()
+    if rank == 0:
+        line = {
+            "metric": "SpMV GFLOP/s", "value": r["gflops"], "unit": "GFLOP/s", "n_gpus": world, "steps": max(args.steps, 1), "warmup": max(args.warmup, 3),
+            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "c5", "description": f"R-MAT scale {args.scale}, edge factor 16, a/b/c/d .57/.19/.19/.05, seed 4, {iters} repeated SpMVs per step",
+                       "rows": n, "nnz": nnz, "rows_rank0": r["rows_local"], "nnz_rank0": r["nnz_local"], "graph_rank0": r["graph"],
+                       "l2": "inputs larger than L2", "search_s": round(r["search_s"], 1), "generate_s": round(r["gen_s"], 1),
+                       "ms_per_spmv": r["ms_per_spmv"], "ms_compute_per_spmv_max_over_ranks": r["ms_compute_per_spmv_max"]},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world), "traffic": None,
+                         "peak_kind": peak_kind, "algorithmic_bytes": b_alg, "note": "x gathers are random over 2^scale columns: DRAM traffic exceeds the algorithmic bytes"},
+            "gpu_launches": int(max(args.steps, 1) * iters * r["launches_per_spmv"]),
+            "clocks": sampler.summary(), "parity_max_rel_err": r["parity"],
+        }
+    # end to end (all ranks take part): x0 from pinned host memory in, final x out
+    hx = r["x0"].cpu().pin_memory()
+    hy = torch.empty_like(hx).pin_memory()
+    dev_x = torch.empty_like(r["x0"])
+    scratch = torch.empty_like(r["x0"])
+    stream = torch.cuda.ExternalStream(r["ctx"].stream)
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    t0 = time.perf_counter()
+    with torch.cuda.stream(stream):
+        dev_x.copy_(hx, non_blocking=True)
+        xf = r["sharded"].iterate(dev_x, iters, scratch)
+        hy.copy_(xf, non_blocking=True)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if dist:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    if rank == 0:
+        line["e2e"] = {"value": 2.0 * nnz * iters / e2e_s * 1e-9, "unit": "GFLOP/s", "h2d_bytes_per_step": int(4 * n), "d2h_bytes_per_step": int(4 * n), "ms_per_step": e2e_s * 1e3}
+        if not args.no_cpu_baseline and r["m_local"].nnz <= 300_000_000:
+            gf, threads, passes, med = cpu_baseline(r["m_local"], r["x0"].cpu().numpy(), budget_s=10.0)
+            line["cpu_baseline"] = {"value": gf, "unit": "GFLOP/s", "cores": threads, "kind": "port",
+                                    "sample": f"{passes} SpMV passes over rank 0's row block ({r['nnz_local']} nnz, median {med * 1e3:.1f} ms), OpenMP row-parallel CSR loop"}
+        print(json.dumps(line))
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"])
+    ap.add_argument("--scale", type=int, default=26, help="c5: R-MAT scale (2^scale rows)")
+    ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x by all-gather)")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--full-search", action="store_true", help="sweep the full node-parameter and launch grids (slow)")
     ap.add_argument("--dense", default="dense compress", help="with --spec: dense-view nodes, '|'-separated")
@@ -172,6 +237,9 @@ def main():
         dist = dist_
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
+    if args.workload == "c5":
+        run_c5(args, rank, world, local_rank, dist)
+        return
     W, K = max(args.warmup, 3), max(args.steps, 1)
     desc, gen = WORKLOADS[args.workload]
     if args.workload == "c2" and world > 1:
