@@ -10,6 +10,11 @@ import torch
 
 from . import capi, matrices_gpu, tuner
 from .dist import ShardedSpmv, balanced_bounds_from_degrees
+from .graph import partition_rows_by_nnz
+
+# One CSR5-like kernel over the unsorted block: no row sort, so y is written in row order and a row
+# chunk of the block is a contiguous slice of the next x.
+DEFAULT_GRAPH = {"dense": "dense compress", "subs": [{"graph": "S9_K10_s16", "nodes": ["tlb_nnz 16"], "template": "K10", "threads": 128, "row_reduce": 1}]}
 
 
 def run(args, rank: int, world: int, local_rank: int, dist, log):
@@ -38,24 +43,47 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
 
     ctx = capi.Context(local_rank)
     t0 = time.perf_counter()
+    # row chunks of this rank's block (nnz-balanced), one plan group each: chunk c is exchanged
+    # while chunk c+1 is computed
+    n_chunks = max(1, args.chunks if args.chunks > 0 else (4 if world > 1 else 1))
+    cuts = partition_rows_by_nnz(m.indptr, n_chunks)
     if args.graph:
         import json
         import os
 
-        desc = json.load(open(args.graph))["config"]["graph"] if os.path.exists(args.graph) else json.loads(args.graph)
-        fmt, group = tuner.build(ctx, m, desc)
-        trials = []
+        if os.path.exists(args.graph):
+            cfg = json.load(open(args.graph))["config"]
+            desc = cfg.get("graph", cfg.get("graph_rank0"))
+        else:
+            desc = json.loads(args.graph)
+    elif args.full_search or args.search:
+        # search on the chunk in the middle of the block, reuse its graph for the others
+        mid = n_chunks // 2
+        mc = m.row_slice(int(cuts[mid]), int(cuts[mid + 1]))
+        fmt_, group_, _, desc = tuner.search(ctx, mc, quick=not args.full_search, log=log, warmup=1, reps=5)
+        group_.close()
+        del fmt_, group_, mc
     else:
-        fmt, group, trials, desc = tuner.search(ctx, m, quick=not args.full_search, log=log, warmup=1, reps=5)
+        desc = DEFAULT_GRAPH
+    fmts, groups, chunks = [], [], []
+    for c in range(n_chunks):
+        lo, hi = int(cuts[c]), int(cuts[c + 1])
+        mc = m.row_slice(lo, hi) if n_chunks > 1 else m
+        f, g = tuner.build(ctx, mc, desc)
+        fmts.append(f)
+        groups.append(g)
+
+        def fn(xt, yt, g=g):
+            g.spmv(xt.data_ptr(), yt.data_ptr(), True)  # empty rows are never stored by a kernel: clear y
+
+        chunks.append((fn, lo, hi))
+        del mc
     search_s = time.perf_counter() - t0
     stream = torch.cuda.ExternalStream(ctx.stream)
     x0 = matrices_gpu.rmat_x(scale, seed, dev)
 
-    def local_spmv(xt, yt):
-        group.spmv(xt.data_ptr(), yt.data_ptr(), True)  # empty rows are never stored by a kernel: clear y
-
     with torch.cuda.stream(stream):
-        sh = ShardedSpmv(local_spmv, bounds, rank, world, torch.float32, dev)
+        sh = ShardedSpmv(None, bounds, rank, world, torch.float32, dev, chunks=chunks)
         xa = x0.clone()
         xb = torch.empty_like(x0)
         # parity of the first SpMV of this rank's slice against the CPU oracle (bounded sizes only)
@@ -73,8 +101,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
             parity = refdump.rel_err(y1.cpu().numpy(), y_ref, scl)
         W, K = max(args.warmup, 3), max(args.steps, 1)
         for _ in range(W):
-            sh.local_spmv(xa, sh.y_local)
-            sh.gather_into(xb)
+            sh.step_into(xa, xb)
         torch.cuda.synchronize()
         if dist:
             dist.barrier()
@@ -93,7 +120,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
         # compute-only time of the same number of local SpMVs (no exchange), for the breakdown
         c0.record(stream)
         for _ in range(iters):
-            sh.local_spmv(x0, sh.y_local)
+            sh.spmv_slice(x0)
         c1.record(stream)
         c1.synchronize()
         ms_compute = c0.elapsed_time(c1) / iters
@@ -108,6 +135,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
         "ms_per_step": ms_step, "ms_per_spmv": ms_step / iters, "ms_compute_per_spmv_max": float(t[1].item()),
         "gflops": 2.0 * nnz_all * iters / (ms_step * 1e-3) * 1e-9, "nnz": nnz_all, "rows": n, "iters": iters, "graph": desc,
         "search_s": search_s, "gen_s": gen_s, "parity": parity, "rows_local": r1 - r0, "nnz_local": nnz_local,
-        "format_bytes": int(group.format_bytes()), "launches_per_spmv": group.launches(), "m_local": m, "group": group, "ctx": ctx, "x0": x0, "sharded": sh, "fmt": fmt,
+        "format_bytes": int(sum(g.format_bytes() for g in groups)), "launches_per_spmv": int(sum(g.launches() for g in groups)), "chunks": n_chunks,
+        "m_local": m, "group": groups, "ctx": ctx, "x0": x0, "sharded": sh, "fmt": fmts,
     }
     return out

@@ -222,6 +222,13 @@ asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threa
         static const char *cap = getenv("ASP_ELL_MAX_GRID");
         if (cap && atoll(cap) > 0 && tblock > atoll(cap)) tblock = atoll(cap);
     }
+    if ((t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE) && threads > 256)
+    {
+        // compiled for at most 256 threads per CTA; the warp loop is grid-stride, so more CTAs
+        // of 256 threads walk the same warps
+        tblock = std::min<int64_t>(tblock * ((threads + 255) / 256), 2147483647LL);
+        threads = 256;
+    }
     if (t == ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS && threads > 256)
     {
         // the SELL-like kernel is compiled for at most 256 threads per CTA (register budget); its
@@ -554,8 +561,17 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
                     if (t1 < t0 || t1 > T || hm[asp::MS_BLK_NZ].get(b) + (t1 - t0) * hm[asp::MS_TLB_SIZE].get(b) > nnz_pad) st = ASP_ERR_BOUNDS, why = "SELL-like: a BLB reaches outside val_arr";
                 }
             }
-            p->vec = p->val_is_f64 ? 2 : 4;
+            {
+                // 32 bytes of values per lane and k-step keep enough bytes in flight per warp; fp64
+                // strips that are not a multiple of 128 TLBs fall back to 16-byte lanes
+                const HostMeta &bt = hm[asp::MS_BLK_THR];
+                const bool eq128 = bt.kind == ASP_COMPRESS_LINEAR && bt.coef > 0 && bt.coef % 128 == 0;
+                p->vec = (p->val_is_f64 && !eq128) ? 2 : 4;
+            }
+            if (const char *e = getenv("ASP_SELL_VEC")) p->vec = atoi(e) > 0 ? atoi(e) : p->vec; // tuning knob
+            if (const char *e = getenv("ASP_SELL_PATH")) a.path = atoi(e);                      // tuning knob
             p->units_for_grid = B;
+            if ((a.path & 1) == 0)
             {
                 // equal strips: the kernel walks warp tasks of 32 * vec TLBs (see k_sell)
                 const HostMeta &bt = hm[asp::MS_BLK_THR];

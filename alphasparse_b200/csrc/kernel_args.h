@@ -73,6 +73,7 @@ struct KArgs
     int row_reduce; // thread_num_of_row_reduce
     int bits_word, bits_flag, bits_row, bits_off;
     int warps_first_row_len; // length of the WLB first-row array (K10 has a +1 sentinel)
+    int path;                // kernel-specific walk: SELL-like 0 = warp tasks when strips are equal, 1 = one CTA per strip
 };
 
 } // namespace asp

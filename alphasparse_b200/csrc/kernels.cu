@@ -274,25 +274,27 @@ __device__ __forceinline__ void sell_group(const KArgs &a, const VT *__restrict_
     for (int j = 0; j < V; j++) acc[j] = 0;
     const VT *vp = val + nz;
     const CT *cp = col + nz;
-    constexpr int U = 4;
-    for (u32 k0 = 0; k0 < S; k0 += U)
     {
-        VT v[U][V];
-        CT c[U][V];
+        constexpr int U = 4;
+        for (u32 k0 = 0; k0 < S; k0 += U)
+        {
+            VT v[U][V];
+            CT c[U][V];
 #pragma unroll
-        for (int u = 0; u < U; u++)
-            if (k0 + u < S)
-            {
-                ld_stream_n<VT, V>(vp + (u64)(k0 + u) * n, v[u]);
-                ld_stream_n<CT, V>(cp + (u64)(k0 + u) * n, c[u]);
-            }
+            for (int u = 0; u < U; u++)
+                if (k0 + u < S)
+                {
+                    ld_stream_n<VT, V>(vp + (u64)(k0 + u) * n, v[u]);
+                    ld_stream_n<CT, V>(cp + (u64)(k0 + u) * n, c[u]);
+                }
 #pragma unroll
-        for (int u = 0; u < U; u++)
-            if (k0 + u < S)
-            {
+            for (int u = 0; u < U; u++)
+                if (k0 + u < S)
+                {
 #pragma unroll
-                for (int j = 0; j < V; j++) acc[j] += v[u][j] * __ldg(x + c[u][j]);
-            }
+                    for (int j = 0; j < V; j++) acc[j] += v[u][j] * __ldg(x + c[u][j]);
+                }
+        }
     }
     const Meta &rm = a.m[MS_ROW_OF_TLB];
     if (V == 4 && rm.kind == MK_ARRAY && rm.width == 4 && (t0 & 3) == 0 && t0 + V <= a.effective)
@@ -321,7 +323,7 @@ __global__ void __launch_bounds__(256) k_sell(const KArgs a)
     VT *__restrict__ y = (VT *)a.y;
     const u64 radd = a.row_add ? a.first_row : 0;
     const Meta &bt = a.m[MS_BLK_THR];
-    if (V > 1 && bt.kind == MK_LINEAR && bt.coef > 0 && (bt.coef % (32 * V)) == 0)
+    if ((a.path & 1) == 0 && V > 1 && bt.kind == MK_LINEAR && bt.coef > 0 && (bt.coef % (32 * V)) == 0)
     {
         const u64 n = bt.coef;
         const u64 tasks_per_blb = n / (32 * V);
@@ -647,7 +649,7 @@ __global__ void __launch_bounds__(1024) k_smem_wlb(const KArgs a)
 // emitted code writes the per-thread partial instead of the total for rows that span threads.
 // ---------------------------------------------------------------------------------------------
 template <class VT, class CT, bool WARP_FAST>
-__global__ void __launch_bounds__(1024) k_csr5(const KArgs a)
+__global__ void __launch_bounds__(256) k_csr5(const KArgs a)
 {
     const VT *__restrict__ val = (const VT *)a.val;
     const CT *__restrict__ col = (const CT *)a.col;
@@ -667,7 +669,22 @@ __global__ void __launch_bounds__(1024) k_csr5(const KArgs a)
             if (R0 == R1)
             {
                 VT s = 0;
-                for (u32 k = 0; k < S; k++, nz += 32) s += __ldcs(val + nz) * __ldg(x + __ldcs(col + nz));
+                constexpr u32 UF = 8;
+                for (u32 k0 = 0; k0 < S; k0 += UF, nz += 32 * UF)
+                {
+                    VT v[UF];
+                    CT c[UF];
+#pragma unroll
+                    for (u32 u = 0; u < UF; u++)
+                        if (k0 + u < S)
+                        {
+                            c[u] = __ldcs(col + nz + 32 * u);
+                            v[u] = __ldcs(val + nz + 32 * u);
+                        }
+#pragma unroll
+                    for (u32 u = 0; u < UF; u++)
+                        if (k0 + u < S) s += v[u] * __ldg(x + c[u]);
+                }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
                 if (lane == 0) atomicAdd(y + row_on_device(a, R0), s);
@@ -680,25 +697,45 @@ __global__ void __launch_bounds__(1024) k_csr5(const KArgs a)
         u32 yo = frow;
         bool seen = false;
         VT sum = 0, tail = 0;
-        for (u32 k = 0; k < S; k++, nz += 32)
+        // products of U elements are fetched together (independent gathers in flight) before the
+        // sequential walk over the row-start flags
+        constexpr u32 U = 8;
+        for (u32 k0 = 0; k0 < S; k0 += U, nz += 32 * U)
         {
-            const bool flag = (meta >> (a.bits_word - 1 - k)) & 1ull;
-            if (flag)
-            {
-                if (seen)
+            VT v[U];
+            CT c[U];
+#pragma unroll
+            for (u32 u = 0; u < U; u++)
+                if (k0 + u < S)
                 {
-                    // a row that starts and ends inside this thread; only the warp's very first
-                    // row can also receive contributions from the previous warp
-                    const bool at = a.atomic || (lane == 0 && yo == frow);
-                    out_add(y, row_on_device(a, R0 + yo), sum, at);
-                    yo++;
+                    c[u] = __ldcs(col + nz + 32 * u);
+                    v[u] = __ldcs(val + nz + 32 * u);
                 }
-                else
-                    tail = sum;
-                seen = true;
-                sum = 0;
-            }
-            sum += __ldcs(val + nz) * __ldg(x + __ldcs(col + nz));
+#pragma unroll
+            for (u32 u = 0; u < U; u++)
+                if (k0 + u < S) v[u] *= __ldg(x + c[u]);
+#pragma unroll
+            for (u32 u = 0; u < U; u++)
+                if (k0 + u < S)
+                {
+                    const bool flag = (meta >> (a.bits_word - 1 - (k0 + u))) & 1ull;
+                    if (flag)
+                    {
+                        if (seen)
+                        {
+                            // a row that starts and ends inside this thread; only the warp's very
+                            // first row can also receive contributions from the previous warp
+                            const bool at = a.atomic || (lane == 0 && yo == frow);
+                            out_add(y, row_on_device(a, R0 + yo), sum, at);
+                            yo++;
+                        }
+                        else
+                            tail = sum;
+                        seen = true;
+                        sum = 0;
+                    }
+                    sum += v[u];
+                }
         }
         if (!seen) tail = sum;
         // suffix scan of the tails, segmented at threads that start a row: after the scan

@@ -2,10 +2,14 @@
 
 Rank p owns the contiguous rows [bounds[p], bounds[p+1]) (nnz-balanced, asp_partition_rows_by_nnz),
 builds its own format on that block with global column indices and runs the single-GPU path. A
-single SpMV needs no communication. In repeated-SpMV mode (x <- A x) every iteration ends with an
-all-gather of the ranks' y slices into the next x: the slices differ in length, so they are gathered
-into a buffer of `world * max_rows` elements and compacted with one copy per rank. Kernels only ever
-read local memory; NCCL moves remote data into it first.
+single SpMV needs no communication. In repeated-SpMV mode (x <- A x) every rank's new slice has to
+reach every other rank before the next iteration. The slices differ in length (nnz-balanced blocks of
+a skewed matrix differ several-fold in rows), so they are exchanged unpadded: each rank sends its
+slice straight into the peers' next-x buffers at the slice's own offset (NCCL grouped send/recv,
+i.e. `all_to_all` on tensor lists), and the kernels write their slice of the next x in place, so
+there is no staging copy either. To hide the exchange a rank's block is cut into row chunks, each
+with its own plan group: chunk c travels on a second stream while chunk c+1 is computed. Kernels
+only ever read local memory; NCCL moves remote data into it first.
 
 The reference is single-GPU (code_builder.cc:1483-1489); this module has no counterpart there.
 """
@@ -17,41 +21,93 @@ import torch.distributed as dist
 
 
 class ShardedSpmv:
-    """`local_spmv(x, y_local)` computes this rank's slice: x is the full replicated vector
-    (torch tensor, length n_cols), y_local a tensor of at least bounds[rank+1]-bounds[rank] elements.
-    On a GPU it is `PlanGroup.spmv` on the tensors' pointers; the CPU tests pass a host function."""
+    """`local_spmv(x, y_rows)` computes this rank's slice: x is the full replicated vector (torch
+    tensor, length n_cols), y_rows a tensor view of exactly the rows to produce. On a GPU it is
+    `PlanGroup.spmv` on the tensors' pointers; the CPU tests pass a host function.
 
-    def __init__(self, local_spmv, bounds, rank: int, world: int, dtype, device, group=None):
-        self.local_spmv = local_spmv
+    `chunks`, if given, replaces `local_spmv` by a list of `(fn, lo, hi)`: fn(x, y_rows) produces the
+    local rows [lo, hi) (relative to bounds[rank]); the ranges must tile the rank's block in order.
+    """
+
+    def __init__(self, local_spmv, bounds, rank: int, world: int, dtype, device, group=None, chunks=None):
         self.bounds = [int(b) for b in bounds]
         self.rank, self.world, self.group = rank, world, group
         self.rows = [self.bounds[p + 1] - self.bounds[p] for p in range(world)]
-        self.max_rows = max(self.rows)
         self.n = self.bounds[-1]
-        self.y_local = torch.zeros(self.max_rows, dtype=dtype, device=device)
-        self.gathered = torch.zeros(world * self.max_rows, dtype=dtype, device=device) if world > 1 else None
+        self.device = torch.device(device)
+        my_rows = self.rows[rank]
+        self.chunks = list(chunks) if chunks is not None else [(local_spmv, 0, my_rows)]
+        assert self.chunks[0][1] == 0 and self.chunks[-1][2] == my_rows
+        assert all(self.chunks[i][2] == self.chunks[i + 1][1] for i in range(len(self.chunks) - 1))
+        self.y_local = torch.zeros(max(1, my_rows), dtype=dtype, device=device)
+        # every rank's chunk cuts in global rows: cuts[p][c] .. cuts[p][c+1]
+        C = len(self.chunks)
+        mine = torch.tensor([self.bounds[rank] + c[1] for c in self.chunks] + [self.bounds[rank + 1]], dtype=torch.int64)
+        if world > 1:
+            counts = [torch.zeros(1, dtype=torch.int64, device=device) for _ in range(world)]
+            dist.all_gather(counts, torch.tensor([C], dtype=torch.int64, device=device), group=group)
+            if any(int(c.item()) != C for c in counts):
+                raise ValueError("all ranks must cut their block into the same number of chunks")
+            allc = [torch.zeros(C + 1, dtype=torch.int64, device=device) for _ in range(world)]
+            dist.all_gather(allc, mine.to(device), group=group)
+            self.cuts = [[int(v) for v in t.cpu().tolist()] for t in allc]
+        else:
+            self.cuts = [[int(v) for v in mine.tolist()]]
+        self.on_gpu = self.device.type == "cuda"
+        self._comm = torch.cuda.Stream(device=self.device) if (self.on_gpu and world > 1) else None
+        self._ev = [torch.cuda.Event() for _ in range(C)] if self._comm is not None else None
+        self._done = torch.cuda.Event() if self._comm is not None else None
+        self._empty = torch.empty(0, dtype=dtype, device=device)
+        self._use_a2a = world > 1 and dist.get_backend(group) == "nccl"
 
+    # -- one SpMV of this rank's block, no communication -------------------------------------
     def spmv_slice(self, x: torch.Tensor) -> torch.Tensor:
-        """y[bounds[rank]:bounds[rank+1]] for the replicated x (no communication)."""
-        self.local_spmv(x, self.y_local)
+        """y[bounds[rank]:bounds[rank+1]] for the replicated x."""
+        for fn, lo, hi in self.chunks:
+            if hi > lo:
+                fn(x, self.y_local[lo:hi])
         return self.y_local[: self.rows[self.rank]]
 
-    def gather_into(self, x_next: torch.Tensor) -> None:
-        """All ranks' current y slices -> x_next (full length), in row order."""
-        if self.world == 1:
-            x_next[: self.rows[0]].copy_(self.y_local[: self.rows[0]])
-            return
-        dist.all_gather_into_tensor(self.gathered, self.y_local, group=self.group)
-        for p in range(self.world):
-            x_next[self.bounds[p] : self.bounds[p + 1]].copy_(self.gathered[p * self.max_rows : p * self.max_rows + self.rows[p]])
+    # -- exchange of chunk c: my rows cuts[rank][c:c+2] go to every peer, theirs come here ---
+    def _exchange(self, c: int, x_next: torch.Tensor) -> None:
+        me = self.rank
+        src = x_next[self.cuts[me][c] : self.cuts[me][c + 1]]
+        if self._use_a2a:
+            outs = [self._empty if p == me else x_next[self.cuts[p][c] : self.cuts[p][c + 1]] for p in range(self.world)]
+            ins = [self._empty if p == me else src for p in range(self.world)]
+            dist.all_to_all(outs, ins, group=self.group)
+        else:  # backends without all_to_all (gloo on the host): one broadcast per owner
+            for p in range(self.world):
+                seg = x_next[self.cuts[p][c] : self.cuts[p][c + 1]]
+                if seg.numel():
+                    dist.broadcast(seg, src=p if self.group is None else dist.get_global_rank(self.group, p), group=self.group)
+
+    def step_into(self, x: torch.Tensor, x_next: torch.Tensor) -> None:
+        """x_next <- A x on every rank (replicated result)."""
+        base = self.bounds[self.rank]
+        cur = torch.cuda.current_stream(self.device) if self._comm is not None else None
+        for c, (fn, lo, hi) in enumerate(self.chunks):
+            if hi > lo:
+                fn(x, x_next[base + lo : base + hi])
+            if self.world == 1:
+                continue
+            if self._comm is not None:
+                self._ev[c].record(cur)
+                self._comm.wait_event(self._ev[c])
+                with torch.cuda.stream(self._comm):
+                    self._exchange(c, x_next)
+            else:
+                self._exchange(c, x_next)
+        if self._comm is not None:
+            self._done.record(self._comm)
+            cur.wait_event(self._done)
 
     def iterate(self, x0: torch.Tensor, iters: int, scratch: torch.Tensor | None = None) -> torch.Tensor:
         """x <- A x, `iters` times (square matrices); returns the final replicated x."""
         a = x0
         b = scratch if scratch is not None else torch.empty_like(x0)
         for _ in range(iters):
-            self.local_spmv(a, self.y_local)
-            self.gather_into(b)
+            self.step_into(a, b)
             a, b = b, a
         return a
 

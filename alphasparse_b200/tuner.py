@@ -79,13 +79,17 @@ def compressed_candidates(mn: int, mx: int, avg: float, is_sorted: bool, quick: 
         for mm in ([128, 256] if quick else [64, 128, 192, 256]):
             out.append(Candidate(f"S1_K2_m{mm}", [f"row_padding {mm} 1", f"blb_row_evenly {mm}", "tlb_row"], "K2",
                                  [(t, 1) for t in (128, 256)]))
-        if not is_sorted:
-            # strategy 9: TLB_NNZ_DIV(s) -> CSR5-like templates, s = 2 .. min(avg, 32)
-            hi = int(max(2, min(avg, 32)))
-            ss = sorted({2, max(2, hi // 2), hi}) if quick else sorted(set(integer_range(2, hi, max(1, (hi - 2) // 3 or 1))))
-            for s in ss:
-                out.append(Candidate(f"S9_K9_s{s}", [f"tlb_nnz {s}"], "K9", [(t, 1) for t in (128, 256)]))
-                out.append(Candidate(f"S9_K10_s{s}", [f"tlb_nnz {s}"], "K10", [(t, 1) for t in (128, 256)]))
+    if not is_sorted:
+        # strategy 9: TLB_NNZ_DIV(s) -> CSR5-like templates, s = 2 .. min(avg, 32). Rows of any
+        # length qualify (a long row simply spans many warps), so a skewed matrix can run as ONE
+        # kernel with no row sort: y is then written in row order instead of scattered.
+        hi = int(max(2, min(avg, 32)))
+        ss = sorted({2, max(2, hi // 2), hi}) if quick else sorted(set(integer_range(2, hi, max(1, (hi - 2) // 3 or 1))))
+        if mx > 512:
+            ss = sorted(set(ss) | {8, 16})
+        for s in ss:
+            out.append(Candidate(f"S9_K9_s{s}", [f"tlb_nnz {s}"], "K9", [(t, 1) for t in (128, 256)]))
+            out.append(Candidate(f"S9_K10_s{s}", [f"tlb_nnz {s}"], "K10", [(t, 1) for t in (128, 256)]))
     if mn >= 30 and mx <= 512:
         # strategy 4: WLB_COL_DIV(c) -> warp per row chunk; c from 32 up past the longest row
         step = max(32, _ceil32(max(1, (mx - mn) // 3)))

@@ -160,7 +160,8 @@ def run_c5(args, rank, world, local_rank, dist):
             "config": {"workload": "c5", "description": f"R-MAT scale {args.scale}, edge factor 16, a/b/c/d .57/.19/.19/.05, seed 4, {iters} repeated SpMVs per step",
                        "rows": n, "nnz": nnz, "rows_rank0": r["rows_local"], "nnz_rank0": r["nnz_local"], "graph_rank0": r["graph"],
                        "l2": "inputs larger than L2", "search_s": round(r["search_s"], 1), "generate_s": round(r["gen_s"], 1),
-                       "ms_per_spmv": r["ms_per_spmv"], "ms_compute_per_spmv_max_over_ranks": r["ms_compute_per_spmv_max"]},
+                       "ms_per_spmv": r["ms_per_spmv"], "ms_compute_per_spmv_max_over_ranks": r["ms_compute_per_spmv_max"], "row_chunks_per_rank": r["chunks"],
+                       "exchange": "none (1 GPU)" if world == 1 else "unpadded NCCL send/recv of each row chunk on a second stream, overlapped with the next chunk's kernel"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world), "traffic": None,
                          "peak_kind": peak_kind, "algorithmic_bytes": b_alg, "note": "x gathers are random over 2^scale columns: DRAM traffic exceeds the algorithmic bytes"},
             "gpu_launches": int(max(args.steps, 1) * iters * r["launches_per_spmv"]),
@@ -182,17 +183,36 @@ def run_c5(args, rank, world, local_rank, dist):
         hy.copy_(xf, non_blocking=True)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    replicas_agree = None
     if dist:
         t = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
+        # every rank must hold the same final x, bit for bit
+        chk = torch.stack([xf.double().sum(), xf.double().abs().max()])
+        lo, hi = chk.clone(), chk.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        replicas_agree = bool(torch.equal(lo, hi))
     if rank == 0:
         line["e2e"] = {"value": 2.0 * nnz * iters / e2e_s * 1e-9, "unit": "GFLOP/s", "h2d_bytes_per_step": int(4 * n), "d2h_bytes_per_step": int(4 * n), "ms_per_step": e2e_s * 1e3}
+        line["replicas_agree"] = replicas_agree
         if not args.no_cpu_baseline and r["m_local"].nnz <= 300_000_000:
             gf, threads, passes, med = cpu_baseline(r["m_local"], r["x0"].cpu().numpy(), budget_s=10.0)
             line["cpu_baseline"] = {"value": gf, "unit": "GFLOP/s", "cores": threads, "kind": "port",
                                     "sample": f"{passes} SpMV passes over rank 0's row block ({r['nnz_local']} nnz, median {med * 1e3:.1f} ms), OpenMP row-parallel CSR loop"}
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    # Tear down in dependency order: torch frees pinned blocks by recording an event on the stream
+    # they were last used on, and that stream belongs to the context object.
+    torch.cuda.synchronize()
+    del hx, hy, dev_x, scratch, xf, stream
+    for k in ("sharded", "x0", "group", "fmt", "m_local"):
+        r.pop(k, None)
+    import gc
+
+    gc.collect()
+    torch.cuda.synchronize()
+    r.pop("ctx", None)
     if dist:
         dist.barrier()
         dist.destroy_process_group()
@@ -205,7 +225,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"])
     ap.add_argument("--scale", type=int, default=26, help="c5: R-MAT scale (2^scale rows)")
-    ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x by all-gather)")
+    ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x by an unpadded exchange of the ranks' slices)")
+    ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank whose exchange overlaps the next chunk's kernels (0: 4 when sharded, else 1)")
+    ap.add_argument("--search", action="store_true", help="c5: run the quick search instead of the default one-kernel graph")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--full-search", action="store_true", help="sweep the full node-parameter and launch grids (slow)")
     ap.add_argument("--dense", default="dense compress", help="with --spec: dense-view nodes, '|'-separated")
@@ -339,10 +361,17 @@ def main():
     for _ in range(Ke):
         capi.check(capi.lib().asp_spmv_host(ctx.handle, plans, group.n, C.c_void_p(hx.data_ptr()), C.c_void_p(hy.data_ptr())))
     e2e_s = (time.perf_counter() - t0) / Ke
+    replicas_agree = None
     if dist:
         t = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
+        # every rank must hold the same final x, bit for bit
+        chk = torch.stack([xf.double().sum(), xf.double().abs().max()])
+        lo, hi = chk.clone(), chk.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        replicas_agree = bool(torch.equal(lo, hi))
     sampler.stop_flag.set()
 
     # parity of what was just timed, against the CPU oracle on rank 0 (bounded: c2-sized matrices take ~0.1 s)

@@ -45,7 +45,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, iters, out_dir):
+def _worker(rank, world, port, iters, out_dir, n_chunks=1):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -54,11 +54,19 @@ def _worker(rank, world, port, iters, out_dir):
     bounds = partition_rows_by_nnz(m.indptr, world)
     blk = m.row_slice(int(bounds[rank]), int(bounds[rank + 1]))
 
-    def local_spmv(xt, yt):
-        y = refdump.csr_native(blk, xt.numpy())
-        yt[: blk.n_rows] = torch.from_numpy(y)
+    def make(sub):
+        def fn(xt, yt):
+            assert yt.shape[0] == sub.n_rows
+            yt.copy_(torch.from_numpy(refdump.csr_native(sub, xt.numpy())))
 
-    sh = ShardedSpmv(local_spmv, bounds, rank, world, torch.float32, "cpu")
+        return fn
+
+    if n_chunks == 1:
+        sh = ShardedSpmv(make(blk), bounds, rank, world, torch.float32, "cpu")
+    else:
+        cuts = partition_rows_by_nnz(blk.indptr, n_chunks)
+        chunks = [(make(blk.row_slice(int(cuts[c]), int(cuts[c + 1]))), int(cuts[c]), int(cuts[c + 1])) for c in range(n_chunks)]
+        sh = ShardedSpmv(None, bounds, rank, world, torch.float32, "cpu", chunks=chunks)
     xt = torch.from_numpy(x.copy())
     y_slice = sh.spmv_slice(xt).clone()
     xf = sh.iterate(xt, iters)
@@ -68,10 +76,10 @@ def _worker(rank, world, port, iters, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_sharded_repeated_spmv_matches_single_rank(world, tmp_path):
+@pytest.mark.parametrize("world,n_chunks", [(2, 1), (3, 1), (2, 3)])
+def test_sharded_repeated_spmv_matches_single_rank(world, n_chunks, tmp_path):
     iters = 4
-    mp.spawn(_worker, args=(world, _free_port(), iters, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), iters, str(tmp_path), n_chunks), nprocs=world, join=True)
     m, x = M.rmat(10, 8, seed=4)
     m.values *= 0.05
     ref = x.copy()
