@@ -14,7 +14,7 @@ from .graph import partition_rows_by_nnz
 
 # One CSR5-like kernel over the unsorted block: no row sort, so y is written in row order and a row
 # chunk of the block is a contiguous slice of the next x.
-DEFAULT_GRAPH = {"dense": "dense compress", "subs": [{"graph": "S9_K10_s16", "nodes": ["tlb_nnz 16"], "template": "K10", "threads": 128, "row_reduce": 1}]}
+DEFAULT_GRAPH = {"dense": "dense compress", "subs": [{"graph": "S9_K9_s32", "nodes": ["tlb_nnz 32"], "template": "K9", "threads": 128, "row_reduce": 1}]}
 
 
 def run(args, rank: int, world: int, local_rank: int, dist, log):

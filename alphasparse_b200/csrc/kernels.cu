@@ -104,6 +104,92 @@ __device__ __forceinline__ Vec<T, V> ld_stream(const T *p)
     u.r = __ldcs(reinterpret_cast<const R *>(p));
     return u.v;
 }
+// The same loads as volatile PTX: the compiler keeps volatile asm statements in program order, so a
+// batch of loads written before its uses is issued as a batch (it otherwise interleaves loads and
+// uses to save registers, which serialises the memory latency).
+template <int BYTES>
+__device__ __forceinline__ void ld_cs_raw(const void *p, unsigned int (&r)[(BYTES + 3) / 4])
+{
+    if constexpr (BYTES == 16)
+        asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "l"(p));
+    else if constexpr (BYTES == 8)
+        asm volatile("ld.global.cs.v2.u32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "l"(p));
+    else if constexpr (BYTES == 4)
+        asm volatile("ld.global.cs.u32 %0, [%1];" : "=r"(r[0]) : "l"(p));
+    else if constexpr (BYTES == 2)
+    {
+        unsigned short t;
+        asm volatile("ld.global.cs.u16 %0, [%1];" : "=h"(t) : "l"(p));
+        r[0] = t;
+    }
+    else
+    {
+        unsigned int t;
+        asm volatile("ld.global.cs.u8 %0, [%1];" : "=r"(t) : "l"(p));
+        r[0] = t;
+    }
+}
+
+template <class T, int V>
+__device__ __forceinline__ void ld_stream_pinned(const T *p, T (&out)[V])
+{
+    constexpr int BYTES = sizeof(T) * V;
+    if constexpr (BYTES <= 16)
+    {
+        unsigned int r[(BYTES + 3) / 4];
+        ld_cs_raw<BYTES>(p, r);
+        if constexpr (sizeof(T) == 8)
+        {
+#pragma unroll
+            for (int j = 0; j < V; j++)
+            {
+                const unsigned long long w = ((unsigned long long)r[2 * j + 1] << 32) | r[2 * j];
+                out[j] = *reinterpret_cast<const T *>(&w);
+            }
+        }
+        else if constexpr (sizeof(T) == 4)
+        {
+#pragma unroll
+            for (int j = 0; j < V; j++) out[j] = *reinterpret_cast<const T *>(&r[j]);
+        }
+        else if constexpr (sizeof(T) == 2)
+        {
+#pragma unroll
+            for (int j = 0; j < V; j++) out[j] = (T)((r[j / 2] >> (16 * (j & 1))) & 0xffffu);
+        }
+        else
+        {
+#pragma unroll
+            for (int j = 0; j < V; j++) out[j] = (T)((r[j / 4] >> (8 * (j & 3))) & 0xffu);
+        }
+    }
+    else
+    {
+        constexpr int H = 16 / sizeof(T);
+#pragma unroll
+        for (int h = 0; h < V / H; h++)
+        {
+            T half[H];
+            ld_stream_pinned<T, H>(p + h * H, half);
+#pragma unroll
+            for (int j = 0; j < H; j++) out[h * H + j] = half[j];
+        }
+    }
+}
+
+__device__ __forceinline__ float ld_x_pinned(const float *p)
+{
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ double ld_x_pinned(const double *p)
+{
+    double v;
+    asm volatile("ld.global.nc.f64 %0, [%1];" : "=d"(v) : "l"(p));
+    return v;
+}
+
 // 32-byte groups (8 x f32 / 4 x f64) are fetched as two 16-byte halves
 template <class T, int V>
 __device__ __forceinline__ void ld_stream_n(const T *p, T (&out)[V])
@@ -223,24 +309,33 @@ __global__ void __launch_bounds__(512) k_ell(const KArgs a)
         else
         {
             constexpr int U = 4;
-            for (u32 k0 = 0; k0 < S; k0 += U)
+            u32 k = 0;
+            for (; k + U <= S; k += U)
             {
                 VT v[U][V];
                 CT c[U][V];
 #pragma unroll
-                for (int u = 0; u < U; u++)
-                    if (k0 + u < S)
-                    {
-                        ld_stream_n<VT, V>(vp + (u64)(k0 + u) * P, v[u]);
-                        ld_stream_n<CT, V>(cp + (u64)(k0 + u) * P, c[u]);
-                    }
+                for (int u = 0; u < U; u++) ld_stream_pinned<CT, V>(cp + (u64)(k + u) * P, c[u]);
+#pragma unroll
+                for (int u = 0; u < U; u++) ld_stream_pinned<VT, V>(vp + (u64)(k + u) * P, v[u]);
+                VT xv[U][V];
 #pragma unroll
                 for (int u = 0; u < U; u++)
-                    if (k0 + u < S)
-                    {
 #pragma unroll
-                        for (int j = 0; j < V; j++) acc[j] += v[u][j] * __ldg(x + c[u][j]);
-                    }
+                    for (int j = 0; j < V; j++) xv[u][j] = ld_x_pinned(x + c[u][j]);
+#pragma unroll
+                for (int u = 0; u < U; u++)
+#pragma unroll
+                    for (int j = 0; j < V; j++) acc[j] += v[u][j] * xv[u][j];
+            }
+            for (; k < S; k++)
+            {
+                VT v[V];
+                CT c[V];
+                ld_stream_n<VT, V>(vp + (u64)k * P, v);
+                ld_stream_n<CT, V>(cp + (u64)k * P, c);
+#pragma unroll
+                for (int j = 0; j < V; j++) acc[j] += v[j] * __ldg(x + c[j]);
             }
         }
         if (unit_rows && t0 + V <= a.effective)
@@ -265,38 +360,15 @@ __global__ void __launch_bounds__(512) k_ell(const KArgs a)
 // division gives) are cut into warp tasks of 32*V TLBs that a persistent grid of warps walks, so
 // thousands of tiny strips cost no CTA launches; otherwise one CTA takes one strip at a time.
 // ---------------------------------------------------------------------------------------------
-template <class VT, class CT, int V>
-__device__ __forceinline__ void sell_group(const KArgs &a, const VT *__restrict__ val, const CT *__restrict__ col, const VT *__restrict__ x,
-                                           VT *__restrict__ y, u64 nz, u64 n, u32 S, u64 t0, u64 radd)
+template <class VT, int V>
+__device__ __forceinline__ void sell_store(const KArgs &a, VT *__restrict__ y, const VT (&acc)[V], u64 t0, u64 radd)
 {
-    VT acc[V];
-#pragma unroll
-    for (int j = 0; j < V; j++) acc[j] = 0;
-    const VT *vp = val + nz;
-    const CT *cp = col + nz;
-    {
-        constexpr int U = 4;
-        for (u32 k0 = 0; k0 < S; k0 += U)
-        {
-            VT v[U][V];
-            CT c[U][V];
-#pragma unroll
-            for (int u = 0; u < U; u++)
-                if (k0 + u < S)
-                {
-                    ld_stream_n<VT, V>(vp + (u64)(k0 + u) * n, v[u]);
-                    ld_stream_n<CT, V>(cp + (u64)(k0 + u) * n, c[u]);
-                }
-#pragma unroll
-            for (int u = 0; u < U; u++)
-                if (k0 + u < S)
-                {
-#pragma unroll
-                    for (int j = 0; j < V; j++) acc[j] += v[u][j] * __ldg(x + c[u][j]);
-                }
-        }
-    }
     const Meta &rm = a.m[MS_ROW_OF_TLB];
+    if (V > 1 && rm.kind == MK_LINEAR && rm.coef == 1 && !a.atomic && t0 + V <= a.effective && ((t0 + rm.icpt + radd) % V) == 0)
+    {
+        store_rows<VT, V>(y, t0 + rm.icpt + radd, acc);
+        return;
+    }
     if (V == 4 && rm.kind == MK_ARRAY && rm.width == 4 && (t0 & 3) == 0 && t0 + V <= a.effective)
     {
         const uint4 r = __ldg(reinterpret_cast<const uint4 *>((const unsigned int *)rm.p + t0));
@@ -312,6 +384,52 @@ __device__ __forceinline__ void sell_group(const KArgs &a, const VT *__restrict_
         const u64 t = t0 + j;
         if (t < a.effective) out_add(y, mget(rm, t) + radd, acc[j], a.atomic != 0);
     }
+}
+
+template <class VT, class CT, int V>
+__device__ __forceinline__ void sell_group(const KArgs &a, const VT *__restrict__ val, const CT *__restrict__ col, const VT *__restrict__ x,
+                                           VT *__restrict__ y, u64 nz, u64 n, u32 S, u64 t0, u64 radd)
+{
+    VT acc[V];
+#pragma unroll
+    for (int j = 0; j < V; j++) acc[j] = 0;
+    const VT *vp = val + nz;
+    const CT *cp = col + nz;
+    constexpr int U = 4;
+    u32 k = 0;
+    // full batches: U value and U index vectors in flight, then U*V gathers, then the FMAs
+    for (; k + U <= S; k += U)
+    {
+        VT v[U][V];
+        CT c[U][V];
+#pragma unroll
+        for (int u = 0; u < U; u++) ld_stream_pinned<CT, V>(cp + (u64)u * n, c[u]);
+#pragma unroll
+        for (int u = 0; u < U; u++) ld_stream_pinned<VT, V>(vp + (u64)u * n, v[u]);
+        VT xv[U][V];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int j = 0; j < V; j++) xv[u][j] = ld_x_pinned(x + c[u][j]);
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int j = 0; j < V; j++) acc[j] += v[u][j] * xv[u][j];
+        vp += (u64)U * n;
+        cp += (u64)U * n;
+    }
+    for (; k < S; k++)
+    {
+        VT v[V];
+        CT c[V];
+        ld_stream_n<VT, V>(vp, v);
+        ld_stream_n<CT, V>(cp, c);
+#pragma unroll
+        for (int j = 0; j < V; j++) acc[j] += v[j] * __ldg(x + c[j]);
+        vp += n;
+        cp += n;
+    }
+    sell_store<VT, V>(a, y, acc, t0, radd);
 }
 
 template <class VT, class CT, int V>
@@ -477,7 +595,28 @@ __global__ void __launch_bounds__(1024) k_long_row(const KArgs a)
         VT acc = 0;
         if (((beg | end) & (V - 1)) == 0)
         {
-            for (u64 i = beg + (u64)threadIdx.x * V; i < end; i += (u64)blockDim.x * V)
+            const u64 step = (u64)blockDim.x * V;
+            u64 i = beg + (u64)threadIdx.x * V;
+            // two CTA-strides per trip: both index vectors, both value vectors, then 2V gathers
+            for (; i + step < end; i += 2 * step)
+            {
+                VT v[2][V];
+                CT c[2][V];
+                ld_stream_pinned<CT, V>(col + i, c[0]);
+                ld_stream_pinned<CT, V>(col + i + step, c[1]);
+                ld_stream_pinned<VT, V>(val + i, v[0]);
+                ld_stream_pinned<VT, V>(val + i + step, v[1]);
+                VT xv[2][V];
+#pragma unroll
+                for (int u = 0; u < 2; u++)
+#pragma unroll
+                    for (int j = 0; j < V; j++) xv[u][j] = ld_x_pinned(x + c[u][j]);
+#pragma unroll
+                for (int u = 0; u < 2; u++)
+#pragma unroll
+                    for (int j = 0; j < V; j++) acc += v[u][j] * xv[u][j];
+            }
+            for (; i < end; i += step)
             {
                 VT v[V];
                 CT c[V];
@@ -648,6 +787,32 @@ __global__ void __launch_bounds__(1024) k_smem_wlb(const KArgs a)
 // sums), and the thread that holds a row's start writes the row's total. The reference's
 // emitted code writes the per-thread partial instead of the total for rows that span threads.
 // ---------------------------------------------------------------------------------------------
+// products val[nz + 32u] * x[col[nz + 32u]], u < cnt <= U. A full batch issues its U index loads,
+// U value loads and U gathers in that order (volatile PTX keeps the order), so U gathers are in flight.
+template <class VT, class CT, int U>
+__device__ __forceinline__ void strided_products(const VT *__restrict__ val, const CT *__restrict__ col, const VT *__restrict__ x, u64 nz, u32 cnt, VT (&p)[U])
+{
+    if (cnt >= (u32)U)
+    {
+        CT c[U][1];
+        VT v[U][1];
+#pragma unroll
+        for (int u = 0; u < U; u++) ld_stream_pinned<CT, 1>(col + nz + 32 * u, c[u]);
+#pragma unroll
+        for (int u = 0; u < U; u++) ld_stream_pinned<VT, 1>(val + nz + 32 * u, v[u]);
+        VT xv[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) xv[u] = ld_x_pinned(x + c[u][0]);
+#pragma unroll
+        for (int u = 0; u < U; u++) p[u] = v[u][0] * xv[u];
+    }
+    else
+    {
+#pragma unroll
+        for (int u = 0; u < U; u++) p[u] = (u32)u < cnt ? __ldcs(val + nz + 32 * u) * __ldg(x + __ldcs(col + nz + 32 * u)) : VT(0);
+    }
+}
+
 template <class VT, class CT, bool WARP_FAST>
 __global__ void __launch_bounds__(256) k_csr5(const KArgs a)
 {
@@ -669,21 +834,13 @@ __global__ void __launch_bounds__(256) k_csr5(const KArgs a)
             if (R0 == R1)
             {
                 VT s = 0;
-                constexpr u32 UF = 8;
+                constexpr int UF = 8;
                 for (u32 k0 = 0; k0 < S; k0 += UF, nz += 32 * UF)
                 {
-                    VT v[UF];
-                    CT c[UF];
+                    VT pr[UF];
+                    strided_products<VT, CT, UF>(val, col, x, nz, S - k0, pr);
 #pragma unroll
-                    for (u32 u = 0; u < UF; u++)
-                        if (k0 + u < S)
-                        {
-                            c[u] = __ldcs(col + nz + 32 * u);
-                            v[u] = __ldcs(val + nz + 32 * u);
-                        }
-#pragma unroll
-                    for (u32 u = 0; u < UF; u++)
-                        if (k0 + u < S) s += v[u] * __ldg(x + c[u]);
+                    for (int u = 0; u < UF; u++) s += pr[u];
                 }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -703,17 +860,7 @@ __global__ void __launch_bounds__(256) k_csr5(const KArgs a)
         for (u32 k0 = 0; k0 < S; k0 += U, nz += 32 * U)
         {
             VT v[U];
-            CT c[U];
-#pragma unroll
-            for (u32 u = 0; u < U; u++)
-                if (k0 + u < S)
-                {
-                    c[u] = __ldcs(col + nz + 32 * u);
-                    v[u] = __ldcs(val + nz + 32 * u);
-                }
-#pragma unroll
-            for (u32 u = 0; u < U; u++)
-                if (k0 + u < S) v[u] *= __ldg(x + c[u]);
+            strided_products<VT, CT, (int)U>(val, col, x, nz, S - k0, v);
 #pragma unroll
             for (u32 u = 0; u < U; u++)
                 if (k0 + u < S)
