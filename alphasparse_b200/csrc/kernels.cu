@@ -328,14 +328,24 @@ __global__ void __launch_bounds__(512) k_ell(const KArgs a)
 #pragma unroll
                     for (int j = 0; j < V; j++) acc[j] += v[u][j] * xv[u][j];
             }
-            for (; k < S; k++)
+            if (k < S)
             {
-                VT v[V];
-                CT c[V];
-                ld_stream_n<VT, V>(vp + (u64)k * P, v);
-                ld_stream_n<CT, V>(cp + (u64)k * P, c);
+                VT v[U - 1][V];
+                CT c[U - 1][V];
 #pragma unroll
-                for (int j = 0; j < V; j++) acc[j] += v[j] * __ldg(x + c[j]);
+                for (int u = 0; u < U - 1; u++)
+                    if (k + u < S)
+                    {
+                        ld_stream_n<VT, V>(vp + (u64)(k + u) * P, v[u]);
+                        ld_stream_n<CT, V>(cp + (u64)(k + u) * P, c[u]);
+                    }
+#pragma unroll
+                for (int u = 0; u < U - 1; u++)
+                    if (k + u < S)
+                    {
+#pragma unroll
+                        for (int j = 0; j < V; j++) acc[j] += v[u][j] * __ldg(x + c[u][j]);
+                    }
             }
         }
         if (unit_rows && t0 + V <= a.effective)
@@ -418,16 +428,25 @@ __device__ __forceinline__ void sell_group(const KArgs &a, const VT *__restrict_
         vp += (u64)U * n;
         cp += (u64)U * n;
     }
-    for (; k < S; k++)
+    if (k < S)
     {
-        VT v[V];
-        CT c[V];
-        ld_stream_n<VT, V>(vp, v);
-        ld_stream_n<CT, V>(cp, c);
+        // the last S % U steps (all of a short TLB) as one predicated batch
+        VT v[U - 1][V];
+        CT c[U - 1][V];
 #pragma unroll
-        for (int j = 0; j < V; j++) acc[j] += v[j] * __ldg(x + c[j]);
-        vp += n;
-        cp += n;
+        for (int u = 0; u < U - 1; u++)
+            if (k + u < S)
+            {
+                ld_stream_n<VT, V>(vp + (u64)u * n, v[u]);
+                ld_stream_n<CT, V>(cp + (u64)u * n, c[u]);
+            }
+#pragma unroll
+        for (int u = 0; u < U - 1; u++)
+            if (k + u < S)
+            {
+#pragma unroll
+                for (int j = 0; j < V; j++) acc[j] += v[u][j] * __ldg(x + c[u][j]);
+            }
     }
     sell_store<VT, V>(a, y, acc, t0, radd);
 }

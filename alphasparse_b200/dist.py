@@ -26,7 +26,9 @@ class ShardedSpmv:
     `PlanGroup.spmv` on the tensors' pointers; the CPU tests pass a host function.
 
     `chunks`, if given, replaces `local_spmv` by a list of `(fn, lo, hi)`: fn(x, y_rows) produces the
-    local rows [lo, hi) (relative to bounds[rank]); the ranges must tile the rank's block in order.
+    local rows [lo, hi) (relative to bounds[rank]); the ranges must tile the rank's block. They are
+    computed and exchanged in list order, and only the last exchange is not hidden behind a kernel,
+    so the chunk with the fewest rows belongs last.
     """
 
     def __init__(self, local_spmv, bounds, rank: int, world: int, dtype, device, group=None, chunks=None):
@@ -37,22 +39,23 @@ class ShardedSpmv:
         self.device = torch.device(device)
         my_rows = self.rows[rank]
         self.chunks = list(chunks) if chunks is not None else [(local_spmv, 0, my_rows)]
-        assert self.chunks[0][1] == 0 and self.chunks[-1][2] == my_rows
-        assert all(self.chunks[i][2] == self.chunks[i + 1][1] for i in range(len(self.chunks) - 1))
+        tiled = sorted((lo, hi) for _, lo, hi in self.chunks)
+        assert tiled[0][0] == 0 and tiled[-1][1] == my_rows and all(tiled[i][1] == tiled[i + 1][0] for i in range(len(tiled) - 1))
         self.y_local = torch.zeros(max(1, my_rows), dtype=dtype, device=device)
-        # every rank's chunk cuts in global rows: cuts[p][c] .. cuts[p][c+1]
+        # every rank's chunks in global rows, in the order they are computed and exchanged:
+        # span[p][c] = (first row, end row) of the c-th chunk of rank p
         C = len(self.chunks)
-        mine = torch.tensor([self.bounds[rank] + c[1] for c in self.chunks] + [self.bounds[rank + 1]], dtype=torch.int64)
+        mine = torch.tensor([[self.bounds[rank] + lo, self.bounds[rank] + hi] for _, lo, hi in self.chunks], dtype=torch.int64).reshape(-1)
         if world > 1:
             counts = [torch.zeros(1, dtype=torch.int64, device=device) for _ in range(world)]
             dist.all_gather(counts, torch.tensor([C], dtype=torch.int64, device=device), group=group)
             if any(int(c.item()) != C for c in counts):
                 raise ValueError("all ranks must cut their block into the same number of chunks")
-            allc = [torch.zeros(C + 1, dtype=torch.int64, device=device) for _ in range(world)]
+            allc = [torch.zeros(2 * C, dtype=torch.int64, device=device) for _ in range(world)]
             dist.all_gather(allc, mine.to(device), group=group)
-            self.cuts = [[int(v) for v in t.cpu().tolist()] for t in allc]
+            self.span = [[(int(t[2 * c]), int(t[2 * c + 1])) for c in range(C)] for t in (u.cpu() for u in allc)]
         else:
-            self.cuts = [[int(v) for v in mine.tolist()]]
+            self.span = [[(int(mine[2 * c]), int(mine[2 * c + 1])) for c in range(C)]]
         self.on_gpu = self.device.type == "cuda"
         self._comm = torch.cuda.Stream(device=self.device) if (self.on_gpu and world > 1) else None
         self._ev = [torch.cuda.Event() for _ in range(C)] if self._comm is not None else None
@@ -68,17 +71,17 @@ class ShardedSpmv:
                 fn(x, self.y_local[lo:hi])
         return self.y_local[: self.rows[self.rank]]
 
-    # -- exchange of chunk c: my rows cuts[rank][c:c+2] go to every peer, theirs come here ---
+    # -- exchange of chunk c: my rows span[rank][c] go to every peer, theirs come here -------
     def _exchange(self, c: int, x_next: torch.Tensor) -> None:
         me = self.rank
-        src = x_next[self.cuts[me][c] : self.cuts[me][c + 1]]
+        src = x_next[self.span[me][c][0] : self.span[me][c][1]]
         if self._use_a2a:
-            outs = [self._empty if p == me else x_next[self.cuts[p][c] : self.cuts[p][c + 1]] for p in range(self.world)]
+            outs = [self._empty if p == me else x_next[self.span[p][c][0] : self.span[p][c][1]] for p in range(self.world)]
             ins = [self._empty if p == me else src for p in range(self.world)]
             dist.all_to_all(outs, ins, group=self.group)
         else:  # backends without all_to_all (gloo on the host): one broadcast per owner
             for p in range(self.world):
-                seg = x_next[self.cuts[p][c] : self.cuts[p][c + 1]]
+                seg = x_next[self.span[p][c][0] : self.span[p][c][1]]
                 if seg.numel():
                     dist.broadcast(seg, src=p if self.group is None else dist.get_global_rank(self.group, p), group=self.group)
 

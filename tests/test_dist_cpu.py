@@ -65,7 +65,8 @@ def _worker(rank, world, port, iters, out_dir, n_chunks=1):
         sh = ShardedSpmv(make(blk), bounds, rank, world, torch.float32, "cpu")
     else:
         cuts = partition_rows_by_nnz(blk.indptr, n_chunks)
-        chunks = [(make(blk.row_slice(int(cuts[c]), int(cuts[c + 1]))), int(cuts[c]), int(cuts[c + 1])) for c in range(n_chunks)]
+        order = sorted(range(n_chunks), key=lambda c: -(int(cuts[c + 1]) - int(cuts[c])))  # most rows first
+        chunks = [(make(blk.row_slice(int(cuts[c]), int(cuts[c + 1]))), int(cuts[c]), int(cuts[c + 1])) for c in order]
         sh = ShardedSpmv(None, bounds, rank, world, torch.float32, "cpu", chunks=chunks)
     xt = torch.from_numpy(x.copy())
     y_slice = sh.spmv_slice(xt).clone()
