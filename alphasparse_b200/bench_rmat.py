@@ -28,7 +28,9 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
     deg = matrices_gpu.rmat_row_degrees(scale, ef, seed, dev, chunk_ids=range(rank, n_chunks, world))
     if dist:
         dist.all_reduce(deg)
-    bounds = balanced_bounds_from_degrees(deg.cpu().numpy(), world)
+    # "nnz": equal non-zeros per rank; "bytes": equal algorithmic bytes, i.e. a row weighs as much
+    # as one non-zero (4 B of y + 4 B of row structure against 4 B value + 4 B index)
+    bounds = balanced_bounds_from_degrees((deg + (1 if args.balance == "bytes" else 0)).cpu().numpy(), world)
     del deg
     r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
     # pass 2: this rank's row block (global columns), duplicates merged
@@ -41,11 +43,11 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
     if log:
         log(f"rows [{r0}, {r1}) nnz {nnz_local} generated in {gen_s:.1f} s")
 
+    n_chunks = max(1, args.chunks if args.chunks > 0 else (4 if world > 1 else 1))
     ctx = capi.Context(local_rank)
     t0 = time.perf_counter()
     # row chunks of this rank's block (nnz-balanced), one plan group each: chunk c is exchanged
     # while chunk c+1 is computed
-    n_chunks = max(1, args.chunks if args.chunks > 0 else (4 if world > 1 else 1))
     cuts = partition_rows_by_nnz(m.indptr, n_chunks)
     if args.graph:
         import json
@@ -84,7 +86,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
     x0 = matrices_gpu.rmat_x(scale, seed, dev)
 
     with torch.cuda.stream(stream):
-        sh = ShardedSpmv(None, bounds, rank, world, torch.float32, dev, chunks=chunks)
+        sh = ShardedSpmv(None, bounds, rank, world, torch.float32, dev, chunks=chunks, exchange=args.exchange)
         xa = x0.clone()
         xb = torch.empty_like(x0)
         # parity of the first SpMV of this rank's slice against the CPU oracle (bounded sizes only)

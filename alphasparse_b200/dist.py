@@ -31,14 +31,14 @@ class ShardedSpmv:
     so the chunk with the fewest rows belongs last.
     """
 
-    def __init__(self, local_spmv, bounds, rank: int, world: int, dtype, device, group=None, chunks=None):
+    def __init__(self, local_spmv, bounds, rank: int, world: int, dtype, device, group=None, chunks=None, exchange: str = "allgather"):
         self.bounds = [int(b) for b in bounds]
         self.rank, self.world, self.group = rank, world, group
         self.rows = [self.bounds[p + 1] - self.bounds[p] for p in range(world)]
         self.n = self.bounds[-1]
         self.device = torch.device(device)
         my_rows = self.rows[rank]
-        self.chunks = list(chunks) if chunks is not None else [(local_spmv, 0, my_rows)]
+        self.chunks = [tuple(c) for c in chunks] if chunks is not None else [(local_spmv, 0, my_rows)]
         tiled = sorted((lo, hi) for _, lo, hi in self.chunks)
         assert tiled[0][0] == 0 and tiled[-1][1] == my_rows and all(tiled[i][1] == tiled[i + 1][0] for i in range(len(tiled) - 1))
         self.y_local = torch.zeros(max(1, my_rows), dtype=dtype, device=device)
@@ -61,7 +61,12 @@ class ShardedSpmv:
         self._ev = [torch.cuda.Event() for _ in range(C)] if self._comm is not None else None
         self._done = torch.cuda.Event() if self._comm is not None else None
         self._empty = torch.empty(0, dtype=dtype, device=device)
-        self._use_a2a = world > 1 and dist.get_backend(group) == "nccl"
+        # NCCL: "allgather" = all_gather on unequal views (one broadcast per owner, grouped into one
+        # launch; the owner's slice leaves its GPU once), "a2a" = grouped send/recv pairs (the slice
+        # leaves the owner once per peer). gloo has neither for unequal sizes: broadcasts in a loop.
+        self._mode = exchange if (world > 1 and dist.get_backend(group) == "nccl") else "bcast_loop"
+        if self._mode not in ("allgather", "a2a", "bcast_loop"):
+            raise ValueError(f"unknown exchange mode {exchange}")
 
     # -- one SpMV of this rank's block, no communication -------------------------------------
     def spmv_slice(self, x: torch.Tensor) -> torch.Tensor:
@@ -75,11 +80,14 @@ class ShardedSpmv:
     def _exchange(self, c: int, x_next: torch.Tensor) -> None:
         me = self.rank
         src = x_next[self.span[me][c][0] : self.span[me][c][1]]
-        if self._use_a2a:
+        if self._mode == "a2a":
             outs = [self._empty if p == me else x_next[self.span[p][c][0] : self.span[p][c][1]] for p in range(self.world)]
             ins = [self._empty if p == me else src for p in range(self.world)]
             dist.all_to_all(outs, ins, group=self.group)
-        else:  # backends without all_to_all (gloo on the host): one broadcast per owner
+        elif self._mode == "allgather":
+            outs = [x_next[self.span[p][c][0] : self.span[p][c][1]] for p in range(self.world)]
+            dist.all_gather(outs, src, group=self.group)
+        else:
             for p in range(self.world):
                 seg = x_next[self.span[p][c][0] : self.span[p][c][1]]
                 if seg.numel():
@@ -87,6 +95,8 @@ class ShardedSpmv:
 
     def step_into(self, x: torch.Tensor, x_next: torch.Tensor) -> None:
         """x_next <- A x on every rank (replicated result)."""
+        # (Running the chunks' kernels concurrently on prioritised streams was measured and lost:
+        # the chunks then finish together and no exchange is hidden.)
         base = self.bounds[self.rank]
         cur = torch.cuda.current_stream(self.device) if self._comm is not None else None
         for c, (fn, lo, hi) in enumerate(self.chunks):

@@ -160,8 +160,8 @@ def run_c5(args, rank, world, local_rank, dist):
             "config": {"workload": "c5", "description": f"R-MAT scale {args.scale}, edge factor 16, a/b/c/d .57/.19/.19/.05, seed 4, {iters} repeated SpMVs per step",
                        "rows": n, "nnz": nnz, "rows_rank0": r["rows_local"], "nnz_rank0": r["nnz_local"], "graph_rank0": r["graph"],
                        "l2": "inputs larger than L2", "search_s": round(r["search_s"], 1), "generate_s": round(r["gen_s"], 1),
-                       "ms_per_spmv": r["ms_per_spmv"], "ms_compute_per_spmv_max_over_ranks": r["ms_compute_per_spmv_max"], "row_chunks_per_rank": r["chunks"],
-                       "exchange": "none (1 GPU)" if world == 1 else "unpadded NCCL send/recv of each row chunk on a second stream, overlapped with the next chunk's kernel"},
+                       "ms_per_spmv": r["ms_per_spmv"], "ms_compute_per_spmv_max_over_ranks": r["ms_compute_per_spmv_max"], "row_chunks_per_rank": r["chunks"], "balance": args.balance,
+                       "exchange": "none (1 GPU)" if world == 1 else f"unpadded NCCL {args.exchange} of each row chunk on a second stream, overlapped with the next chunk's kernel"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world), "traffic": None,
                          "peak_kind": peak_kind, "algorithmic_bytes": b_alg, "note": "x gathers are random over 2^scale columns: DRAM traffic exceeds the algorithmic bytes"},
             "gpu_launches": int(max(args.steps, 1) * iters * r["launches_per_spmv"]),
@@ -229,6 +229,8 @@ def main():
     ap.add_argument("--scale", type=int, default=26, help="c5: R-MAT scale (2^scale rows)")
     ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x by an unpadded exchange of the ranks' slices)")
     ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank whose exchange overlaps the next chunk's kernels (0: 4 when sharded, else 1)")
+    ap.add_argument("--exchange", default="allgather", choices=["allgather", "a2a"], help="c5: NCCL form of the unpadded slice exchange")
+    ap.add_argument("--balance", default="nnz", choices=["nnz", "bytes"], help="c5: what the row blocks of the ranks have equal amounts of")
     ap.add_argument("--search", action="store_true", help="c5: run the quick search instead of the default one-kernel graph")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--full-search", action="store_true", help="sweep the full node-parameter and launch grids (slow)")
@@ -259,7 +261,8 @@ def main():
         import torch.distributed as dist_
 
         dist = dist_
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)  # the exchange must not queue behind SpMV kernels
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), pg_options=opts)
 
     if args.workload == "c5":
         run_c5(args, rank, world, local_rank, dist)
