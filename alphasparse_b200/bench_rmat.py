@@ -87,8 +87,9 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
 
     with torch.cuda.stream(stream):
         sh = ShardedSpmv(None, bounds, rank, world, torch.float32, dev, chunks=chunks, exchange=args.exchange)
-        xa = x0.clone()
-        xb = torch.empty_like(x0)
+        xa = sh.new_vector()
+        xb = sh.new_vector()
+        xa.copy_(x0)
         # parity of the first SpMV of this rank's slice against the CPU oracle (bounded sizes only)
         parity = None
         y1 = sh.spmv_slice(x0).clone()
@@ -138,7 +139,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
         "ms_per_step": ms_step, "ms_per_spmv": ms_step / iters, "ms_compute_per_spmv_max": float(t[1].item()),
         "gflops": 2.0 * nnz_all * iters / (ms_step * 1e-3) * 1e-9, "nnz": nnz_all, "rows": n, "iters": iters, "graph": desc,
         "search_s": search_s, "gen_s": gen_s, "parity": parity, "rows_local": r1 - r0, "nnz_local": nnz_local,
-        "format_bytes": int(sum(g.format_bytes() for g in groups)), "launches_per_spmv": int(sum(g.launches() for g in groups)), "chunks": n_chunks,
+        "format_bytes": int(sum(g.format_bytes() for g in groups)), "launches_per_spmv": int(sum(g.launches() for g in groups)), "chunks": n_chunks, "exchange_used": sh._mode,
         "m_local": m, "group": groups, "ctx": ctx, "x0": x0, "sharded": sh, "fmt": fmts,
     }
     return out

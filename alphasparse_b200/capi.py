@@ -56,7 +56,7 @@ class PlanDesc(C.Structure):
 
 
 EXPORTS = [
-    "asp_ctx_create", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_destroy",
+    "asp_ctx_create", "asp_multicast_store", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_destroy",
     "asp_plan_set_launch", "asp_plan_format_bytes", "asp_plan_launches", "asp_spmv", "asp_spmv_host", "asp_time",
     "asp_synchronize", "asp_status_str", "asp_last_error", "asp_built_for_sm100a", "asp_spmv_host_static",
     "asp_static_stage_bytes",
@@ -81,6 +81,8 @@ def lib() -> C.CDLL:
     L = C.CDLL(LIB_PATH)
     L.asp_ctx_create.argtypes = [C.c_int, C.POINTER(C.c_void_p)]
     L.asp_ctx_create.restype = C.c_int
+    L.asp_multicast_store.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int]
+    L.asp_multicast_store.restype = C.c_int
     L.asp_ctx_destroy.argtypes = [C.c_void_p]
     L.asp_ctx_destroy.restype = None
     L.asp_ctx_stream.argtypes = [C.c_void_p]
@@ -122,6 +124,11 @@ def check(status: int) -> None:
     if status != 0:
         L = lib()
         raise AspError(status, f"{L.asp_status_str(status).decode()}: {L.asp_last_error().decode()}")
+
+
+def multicast_store(src_ptr: int, multicast_ptr: int, nbytes: int, stream: int, ctas: int = 0) -> None:
+    """asp_multicast_store: one-to-all store of a slice through an NVLink multicast address."""
+    check(lib().asp_multicast_store(src_ptr, multicast_ptr, nbytes, stream, ctas))
 
 
 class Context:

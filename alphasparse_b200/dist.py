@@ -64,9 +64,45 @@ class ShardedSpmv:
         # NCCL: "allgather" = all_gather on unequal views (one broadcast per owner, grouped into one
         # launch; the owner's slice leaves its GPU once), "a2a" = grouped send/recv pairs (the slice
         # leaves the owner once per peer). gloo has neither for unequal sizes: broadcasts in a loop.
+        #   "multicast" = the owner stores its slice once through an NVLink multicast address and
+        # NVSwitch replicates it into every rank's buffer (asp_multicast_store); x and x_next must
+        # then come from new_vector(), which maps them symmetrically on all ranks. A one-element
+        # all-reduce after the last chunk orders the stores of all ranks before the next SpMV.
         self._mode = exchange if (world > 1 and dist.get_backend(group) == "nccl") else "bcast_loop"
-        if self._mode not in ("allgather", "a2a", "bcast_loop"):
+        if self._mode not in ("allgather", "a2a", "bcast_loop", "multicast"):
             raise ValueError(f"unknown exchange mode {exchange}")
+        self._dtype = dtype
+        self._mc = {}  # data_ptr of a symmetric vector -> its multicast address
+        self._symm_keep = []
+        self._flag = torch.zeros(1, dtype=torch.float32, device=device) if self._mode == "multicast" else None
+
+    def new_vector(self) -> torch.Tensor:
+        """A length-n vector usable as x / x_next. In multicast mode it is symmetric memory mapped
+        on every rank and bound to a multicast object; falls back to the unequal all_gather when
+        the platform offers no multicast (then an ordinary tensor is returned)."""
+        if self._mode == "multicast":
+            try:
+                import torch.distributed._symmetric_memory as symm
+
+                gname = (self.group or dist.group.WORLD).group_name
+                try:
+                    symm.enable_symm_mem_for_group(gname)
+                except Exception:
+                    pass
+                t = symm.empty(self.n, dtype=self._dtype, device=self.device)
+                hdl = symm.rendezvous(t, gname)
+                mc = int(hdl.multicast_ptr)
+                ok = torch.tensor([1 if mc else 0], device=self.device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+                if int(ok.item()) == 0:
+                    raise RuntimeError("no multicast address for symmetric memory")
+                self._mc[t.data_ptr()] = mc
+                self._symm_keep.append((t, hdl))
+                return t
+            except Exception as e:  # every rank takes the same branch: the check above is collective
+                self._mode = "allgather"
+                self.fallback_reason = repr(e)[:200]
+        return torch.empty(self.n, dtype=self._dtype, device=self.device)
 
     # -- one SpMV of this rank's block, no communication -------------------------------------
     def spmv_slice(self, x: torch.Tensor) -> torch.Tensor:
@@ -84,6 +120,17 @@ class ShardedSpmv:
             outs = [self._empty if p == me else x_next[self.span[p][c][0] : self.span[p][c][1]] for p in range(self.world)]
             ins = [self._empty if p == me else src for p in range(self.world)]
             dist.all_to_all(outs, ins, group=self.group)
+        elif self._mode == "multicast":
+            from . import capi
+
+            mc = self._mc.get(x_next.data_ptr())
+            if mc is None:
+                raise ValueError("multicast exchange needs vectors from new_vector()")
+            if src.numel():
+                off = self.span[me][c][0] * src.element_size()
+                capi.multicast_store(src.data_ptr(), mc + off, src.numel() * src.element_size(), torch.cuda.current_stream(self.device).cuda_stream, 0)
+            if c == len(self.chunks) - 1:
+                dist.all_reduce(self._flag, group=self.group)  # every rank's stores are done past this point
         elif self._mode == "allgather":
             outs = [x_next[self.span[p][c][0] : self.span[p][c][1]] for p in range(self.world)]
             dist.all_gather(outs, src, group=self.group)

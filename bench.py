@@ -161,7 +161,7 @@ def run_c5(args, rank, world, local_rank, dist):
                        "rows": n, "nnz": nnz, "rows_rank0": r["rows_local"], "nnz_rank0": r["nnz_local"], "graph_rank0": r["graph"],
                        "l2": "inputs larger than L2", "search_s": round(r["search_s"], 1), "generate_s": round(r["gen_s"], 1),
                        "ms_per_spmv": r["ms_per_spmv"], "ms_compute_per_spmv_max_over_ranks": r["ms_compute_per_spmv_max"], "row_chunks_per_rank": r["chunks"], "balance": args.balance,
-                       "exchange": "none (1 GPU)" if world == 1 else f"unpadded NCCL {args.exchange} of each row chunk on a second stream, overlapped with the next chunk's kernel"},
+                       "exchange": "none (1 GPU)" if world == 1 else f"{r['exchange_used']} of each row chunk on a second stream, overlapped with the next chunk's kernel"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world), "traffic": None,
                          "peak_kind": peak_kind, "algorithmic_bytes": b_alg, "note": "x gathers are random over 2^scale columns: DRAM traffic exceeds the algorithmic bytes"},
             "gpu_launches": int(max(args.steps, 1) * iters * r["launches_per_spmv"]),
@@ -170,8 +170,8 @@ def run_c5(args, rank, world, local_rank, dist):
     # end to end (all ranks take part): x0 from pinned host memory in, final x out
     hx = r["x0"].cpu().pin_memory()
     hy = torch.empty_like(hx).pin_memory()
-    dev_x = torch.empty_like(r["x0"])
-    scratch = torch.empty_like(r["x0"])
+    dev_x = r["sharded"].new_vector()
+    scratch = r["sharded"].new_vector()
     stream = torch.cuda.ExternalStream(r["ctx"].stream)
     torch.cuda.synchronize()
     if dist:
@@ -229,7 +229,7 @@ def main():
     ap.add_argument("--scale", type=int, default=26, help="c5: R-MAT scale (2^scale rows)")
     ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x by an unpadded exchange of the ranks' slices)")
     ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank whose exchange overlaps the next chunk's kernels (0: 4 when sharded, else 1)")
-    ap.add_argument("--exchange", default="allgather", choices=["allgather", "a2a"], help="c5: NCCL form of the unpadded slice exchange")
+    ap.add_argument("--exchange", default="allgather", choices=["multicast", "allgather", "a2a"], help="c5: NCCL form of the unpadded slice exchange")
     ap.add_argument("--balance", default="nnz", choices=["nnz", "bytes"], help="c5: what the row blocks of the ranks have equal amounts of")
     ap.add_argument("--search", action="store_true", help="c5: run the quick search instead of the default one-kernel graph")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])

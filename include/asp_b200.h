@@ -187,6 +187,16 @@ asp_status asp_spmv_host(asp_ctx *ctx, asp_plan *const *plans, int n_plans, cons
 asp_status asp_spmv_host_static(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *h_x, void *h_y);
 uint64_t asp_static_stage_bytes(void);
 
+/* Publishes `bytes` of finished results at `src` (this GPU's memory) to every GPU of an NVLink
+ * multicast group: `multicast_dst` is the multicast address of the same offset of a buffer that all
+ * the GPUs mapped symmetrically (e.g. torch.distributed._symmetric_memory). The stores are issued by a
+ * small kernel (`ctas` CTAs, 0 = default) on `stream` (a cudaStream_t) and replicated by NVSwitch, so
+ * the data leaves this GPU once. `bytes` must be a multiple of 4 and src / multicast_dst congruent
+ * modulo 16. Completion on the peers is ordered by whatever the caller enqueues next on `stream`
+ * across the ranks (a collective). No counterpart in the reference, which is single-GPU
+ * (code_builder.cc:1483-1489). */
+asp_status asp_multicast_store(const void *src, void *multicast_dst, size_t bytes, void *stream, int ctas);
+
 /* replaces execute_binary + perf_result parsing (executor.cc:6-59): CUDA-event timing of
  * `reps` SpMVs after `warmup`, x and y internal (x = 100 everywhere, as the generated main()
  * does). gflops = 2*sum(true_nnz)*1e-6/ms. Returns ASP_ERR_IMPLAUSIBLE when gflops exceeds
