@@ -94,15 +94,30 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
         parity = None
         y1 = sh.spmv_slice(x0).clone()
         torch.cuda.synchronize()
-        if m.nnz <= 300_000_000:
+        if True:
             import os
             import sys
 
             sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tests"))
             import refdump
 
-            y_ref, scl = refdump.csr_ref(m, x0.cpu().numpy())
-            parity = refdump.rel_err(y1.cpu().numpy(), y_ref, scl)
+            # the CPU oracle checks whole blocks up to 3e8 non-zeros, else three row windows of the
+            # block (head, middle, tail) of about 2e7 non-zeros each
+            xh, yh = x0.cpu().numpy(), y1.cpu().numpy()
+            if m.nnz <= 300_000_000:
+                windows = [(0, m.n_rows)]
+            else:
+                windows = []
+                for frac in (0.0, 0.5, 1.0):
+                    target = int(frac * (m.nnz - 20_000_000))
+                    a = int(np.searchsorted(m.indptr, target, side="left"))
+                    b = int(np.searchsorted(m.indptr, target + 20_000_000, side="right")) - 1
+                    windows.append((min(a, m.n_rows - 1), max(min(b, m.n_rows), min(a, m.n_rows - 1) + 1)))
+            parity = 0.0
+            for a, b in windows:
+                sub = m.row_slice(a, b) if (a, b) != (0, m.n_rows) else m
+                y_ref, scl = refdump.csr_ref(sub, xh)
+                parity = max(parity, refdump.rel_err(yh[a:b], y_ref, scl))
         W, K = max(args.warmup, 3), max(args.steps, 1)
         for _ in range(W):
             sh.step_into(xa, xb)

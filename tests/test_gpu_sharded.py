@@ -1,0 +1,129 @@
+"""GPU suite, sharded repeated SpMV: row chunks with their own plan groups on one GPU, the GPU
+R-MAT generator, and (where the box has two GPUs) every exchange form against the single-rank result."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+import refdump
+from alphasparse_b200 import bench_rmat, capi, matrices as M, matrices_gpu, tuner
+from alphasparse_b200.dist import ShardedSpmv
+from alphasparse_b200.graph import partition_rows_by_nnz
+
+pytestmark = pytest.mark.gpu
+
+
+def _chunks(ctx, blk, n_chunks, keep):
+    cuts = partition_rows_by_nnz(blk.indptr, n_chunks)
+    out = []
+    for c in sorted(range(n_chunks), key=lambda c: -(int(cuts[c + 1]) - int(cuts[c]))):
+        lo, hi = int(cuts[c]), int(cuts[c + 1])
+        f, g = tuner.build(ctx, blk.row_slice(lo, hi), bench_rmat.DEFAULT_GRAPH)
+        keep.append((f, g))
+
+        def fn(xt, yt, g=g):
+            g.spmv(xt.data_ptr(), yt.data_ptr(), True)
+
+        out.append((fn, lo, hi))
+    return out
+
+
+def _reference_iterations(m, x, iters):
+    ref = x.astype(np.float64)
+    for _ in range(iters):
+        ref, _ = refdump.csr_ref(m, ref.astype(np.float32))
+    return ref
+
+
+def test_row_chunks_on_one_gpu_match_the_oracle(asp_ctx):
+    m, x = M.rmat(13, 16, seed=4)
+    m.values *= 0.02
+    keep = []
+    chunks = _chunks(asp_ctx, m, 3, keep)
+    stream = torch.cuda.ExternalStream(asp_ctx.stream)
+    with torch.cuda.stream(stream):
+        sh = ShardedSpmv(None, [0, m.n_rows], 0, 1, torch.float32, "cuda", chunks=chunks)
+        x0 = torch.from_numpy(x).cuda()
+        y = sh.spmv_slice(x0).clone()
+        xf = sh.iterate(x0.clone(), 3, sh.new_vector())
+        torch.cuda.synchronize()
+    y_ref, scale = refdump.csr_ref(m, x)
+    refdump.assert_y(y.cpu().numpy(), y_ref, scale, np.float32, "chunked slice")
+    ref = _reference_iterations(m, x, 3)
+    got = xf.cpu().numpy().astype(np.float64)
+    assert np.max(np.abs(got - ref)) <= 1e-4 * max(1e-30, np.max(np.abs(ref)))
+    for f, g in keep:
+        g.close()
+        f.close()
+
+
+def test_gpu_rmat_blocks_do_not_depend_on_the_partition():
+    dev = torch.device("cuda", 0)
+    scale, ef, seed = 12, 8, 4
+    n = 1 << scale
+    ip, cols, vals = matrices_gpu.rmat_block(scale, ef, seed, 0, n, dev)
+    whole = matrices_gpu.to_host_csr(ip, cols, vals, n)
+    deg = matrices_gpu.rmat_row_degrees(scale, ef, seed, dev).cpu().numpy()
+    assert deg.sum() == n * ef and np.all(deg >= whole.row_lengths())  # duplicates only ever merge
+    cut = 700
+    parts = [matrices_gpu.to_host_csr(*matrices_gpu.rmat_block(scale, ef, seed, a, b, dev), n) for a, b in ((0, cut), (cut, n))]
+    assert parts[0].nnz + parts[1].nnz == whole.nnz
+    assert np.array_equal(np.concatenate([parts[0].indices, parts[1].indices]), whole.indices)
+    assert np.array_equal(np.concatenate([parts[0].values, parts[1].values]), whole.values)
+    assert np.all(whole.values > 0) and np.all(whole.values <= 1)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, mode, out_dir):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    m, x = M.rmat(13, 16, seed=4)
+    m.values *= 0.02
+    bounds = partition_rows_by_nnz(m.indptr, world)
+    blk = m.row_slice(int(bounds[rank]), int(bounds[rank + 1]))
+    ctx = capi.Context(rank)
+    keep = []
+    chunks = _chunks(ctx, blk, 2, keep)
+    stream = torch.cuda.ExternalStream(ctx.stream)
+    with torch.cuda.stream(stream):
+        sh = ShardedSpmv(None, bounds, rank, world, torch.float32, torch.device("cuda", rank), chunks=chunks, exchange=mode)
+        a, b = sh.new_vector(), sh.new_vector()
+        a.copy_(torch.from_numpy(x).cuda())
+        xf = sh.iterate(a, 3, b)
+        torch.cuda.synchronize()
+    np.save(os.path.join(out_dir, f"final_{rank}.npy"), xf.cpu().numpy())
+    with open(os.path.join(out_dir, f"mode_{rank}.txt"), "w") as fh:
+        fh.write(sh._mode)
+    del sh, a, b, xf
+    for f, g in keep:
+        g.close()
+        f.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("mode", ["allgather", "a2a", "multicast"])
+def test_two_ranks_agree_with_one(mode, tmp_path):
+    import torch.multiprocessing as mp
+
+    mp.spawn(_worker, args=(2, _free_port(), mode, str(tmp_path)), nprocs=2, join=True)
+    m, x = M.rmat(13, 16, seed=4)
+    m.values *= 0.02
+    ref = _reference_iterations(m, x, 3)
+    f0, f1 = np.load(tmp_path / "final_0.npy"), np.load(tmp_path / "final_1.npy")
+    assert np.array_equal(f0.view(np.uint32), f1.view(np.uint32)), "the ranks' replicas of x differ"
+    assert np.max(np.abs(f0.astype(np.float64) - ref)) <= 1e-4 * np.max(np.abs(ref))
