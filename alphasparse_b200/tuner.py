@@ -27,6 +27,42 @@ MAX_TBLOCK_NUM = 2**31 - 1  # the reference's 65535 grid cap is obsolete on sm_1
 TEMPLATE_OF_ID = {v: k for k, v in capi.TEMPLATE.items()}
 
 
+class SearchStrategy:
+    """Stop rule of the reference's search loop (search_strategy.cc:5-80): a budget of steps that is
+    refilled whenever a trial beats the best GFLOP/s so far (5 steps per GFLOP/s gained, clamped to
+    5..25), then `struggle_step_num` further steps, and a wall-clock limit over everything."""
+
+    def __init__(self, struggle_step_num: int = 10, total_allow_search_time: float = float("inf"), clock=None):
+        import time
+
+        self._clock = clock or time.monotonic
+        self.remain_step_num = 10
+        self.struggle_step_num = int(struggle_step_num)
+        self.total_allow_search_time = float(total_allow_search_time)
+        self.begin_time = self._clock()
+        self.best_gflops = 0.0
+
+    def _out_of_time(self) -> bool:
+        return self._clock() - self.begin_time >= self.total_allow_search_time
+
+    def continue_search(self, gflops: float | None = None) -> bool:
+        """With a trial's GFLOP/s: account for it, then say whether to go on. Without: only ask."""
+        if gflops is None:
+            if self._out_of_time():
+                return False
+            return not (self.remain_step_num == 0 and self.struggle_step_num == 0)
+        if gflops > self.best_gflops:
+            self.remain_step_num = max(5, min(25, int((gflops - self.best_gflops) * 5)))
+            self.best_gflops = gflops
+        elif self.remain_step_num > 0:
+            self.remain_step_num -= 1
+        elif self.struggle_step_num > 0:
+            self.struggle_step_num -= 1
+        else:
+            return False
+        return not self._out_of_time()
+
+
 def integer_range(lo: int, hi: int, step: int):
     """register_integer_independ_param_to_enumerater semantics: lo, lo+step, ... while <= hi."""
     v = lo
@@ -147,11 +183,13 @@ def dense_strategies(quick: bool = True) -> list[str]:
     return out
 
 
-def search_sub(ctx, cm: Matrix, sub: int, n_subs: int, is_sorted: bool, quick, warmup, reps, log, dense, trials):
-    """Best (candidate, launch) for one sub-matrix of a compressed matrix."""
+def search_sub(ctx, cm: Matrix, sub: int, n_subs: int, is_sorted: bool, quick, warmup, reps, log, dense, trials, strategy=None):
+    """Best (candidate, launch) for one sub-matrix of a compressed matrix. `strategy` (SearchStrategy)
+    ends the sweep early once trials stop improving; at least one candidate is always timed."""
     rows, nnz, mn, mx = cm.sub_rows(sub)
     cands = compressed_candidates(mn, mx, nnz / max(1, rows), is_sorted, quick)
     best = None
+    stop = False
     others = "\n".join(f"sub {j} template EMPTY" for j in range(n_subs) if j != sub)
     for cand in cands:
         spec = cand.lines(sub) + ("\n" + others if others else "")
@@ -185,14 +223,23 @@ def search_sub(ctx, cm: Matrix, sub: int, n_subs: int, is_sorted: bool, quick, w
                 log(f"  sub {sub} [{rows} rows, nnz/row {mn}..{mx}] {cand.name} threads={th} reduce={red}: {ms * 1e3:.1f} us")
             if best is None or ms < best[2]:
                 best = (cand, (th, red), ms)
+            if strategy is not None and not strategy.continue_search(gf):
+                stop = True
+                break
         group.close()
         fmt.close()
+        if stop:
+            if log:
+                log(f"  sub {sub}: search budget used up after {cand.name}")
+            break
     return best
 
 
 def search(ctx: capi.Context, m: CsrMatrix, quick: bool = True, warmup: int = 2, reps: int = 10, log=None,
-           dense_list: list[str] | None = None, max_subs: int = 5):
-    """Full search. Returns (Format, PlanGroup, trials, description of the winning graph)."""
+           dense_list: list[str] | None = None, max_subs: int = 5, struggle_step_num: int | None = None, time_limit_s: float | None = None):
+    """Full search. Returns (Format, PlanGroup, trials, description of the winning graph). With
+    `struggle_step_num` and / or `time_limit_s` every sub-matrix sweep runs under the reference's stop
+    rule (SearchStrategy); by default every candidate is timed."""
     hm = Matrix.from_csr(m)
     trials: list[Trial] = []
     winner = None  # (ms, dense, [(cand, launch)])
@@ -207,7 +254,10 @@ def search(ctx: capi.Context, m: CsrMatrix, quick: bool = True, warmup: int = 2,
             log(f"dense view: {dense.replace(chr(10), ' | ')} -> {n} sub-matrices")
         picks = []
         for sub in range(n):
-            b = search_sub(ctx, cm, sub, n, "sort" in dense, quick, warmup, reps, log, dense, trials)
+            strat = None
+            if struggle_step_num is not None or time_limit_s is not None:
+                strat = SearchStrategy(struggle_step_num if struggle_step_num is not None else 10, time_limit_s if time_limit_s is not None else float("inf"))
+            b = search_sub(ctx, cm, sub, n, "sort" in dense, quick, warmup, reps, log, dense, trials, strat)
             if b is None:
                 picks = None
                 break
