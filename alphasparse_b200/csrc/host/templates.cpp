@@ -351,7 +351,11 @@ bool init_k2(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::st
     std::vector<u64> bnz(b.blb.coo_begin.v.begin(), b.blb.coo_begin.v.begin() + b.blb.block_num);
     TemplateArray &bn = add_meta(t, ASP_ARR_BLOCK_NZ_BEGIN_OFFSET, bnz, b.blb.coo_begin.dt);
     detect_linear(bnz, bn.comp);
-    TemplateArray &ts = add_meta(t, ASP_ARR_THREAD_BLOCK_SIZE_IN_BLOCK, size, suitable_dtype(size.back()));
+    // The reference narrows this array by its LAST entry (direct_atom_op_warp_compress.cc:239, 544),
+    // which is the smallest one after a descending row sort: strips
+    // whose widest TLB needs more bits are then truncated (372 stored as 116). The type here is
+    // wide enough for the largest entry; it equals the reference's whenever the reference is right.
+    TemplateArray &ts = add_meta(t, ASP_ARR_THREAD_BLOCK_SIZE_IN_BLOCK, size, suitable_dtype(*std::max_element(size.begin(), size.end())));
     if (!detect_constant(size, ts.comp)) detect_branch(size, ts.comp);
     add_perm(m, t);
     add_nnz_arrays(t, b, col, val, b.pad_col.size());

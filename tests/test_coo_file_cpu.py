@@ -37,3 +37,15 @@ def test_config1_from_coo_file_equals_from_csr(tmp_path):
         fb.close()
     a.close()
     b.close()
+
+
+def test_sell_tlb_size_array_is_wide_enough_for_its_largest_entry():
+    # reference defect (direct_atom_op_warp_compress.cc:239): typed by the LAST entry, so a strip of
+    # 372 elements per row is stored as 116 in a u8 array when the last strip is narrow
+    m, _ = M.rmat(11, 8, seed=4)
+    lens = m.row_lengths()
+    assert lens.max() > 255 and lens[-128:].max() < 256
+    fmt = Matrix.from_csr(m).execute("dense compress\nsub all row_padding 128 1\nsub all blb_row_evenly 128\nsub all tlb_row\nsub all template K2")
+    arr = fmt.arrays(0)["thread_block_size_in_block"][0]
+    assert arr.dtype == np.uint16 and int(arr.max()) == int(lens.max())
+    fmt.close()

@@ -101,3 +101,12 @@ def test_tuner_search_returns_a_correct_plan(asp_ctx, mats, mat):
     refdump.assert_y(y, y_ref, scale, m.values.dtype, f"tuner {mat}: {desc}")
     group.close()
     fmt.close()
+
+
+@pytest.mark.parametrize("dense", ["dense compress", "dense sort 1\ndense compress"])
+def test_sell_strips_wider_than_255_elements(asp_ctx, mats, dense):
+    # the reference types thread_block_size_in_block by its last entry and truncates wider strips
+    # (372 -> 116); the native lowering keeps the value
+    m, x = M.rmat(11, 8, seed=4)
+    assert m.row_lengths().max() > 255
+    run(asp_ctx, m, x, dense + "\nsub all row_padding 128 1\nsub all blb_row_evenly 128\nsub all tlb_row\nsub all template K2", f"wide SELL {dense!r}")
