@@ -416,21 +416,11 @@ __device__ __forceinline__ void sell_group(const KArgs &a, const VT *__restrict_
         for (int u = 0; u < U; u++) ld_stream_pinned<CT, V>(cp + (u64)u * n, c[u]);
 #pragma unroll
         for (int u = 0; u < U; u++) ld_stream_pinned<VT, V>(vp + (u64)u * n, v[u]);
-        // adjacent rows of block-structured matrices share their column at a step: gather once
         VT xv[U][V];
 #pragma unroll
         for (int u = 0; u < U; u++)
-        {
-            xv[u][0] = ld_x_pinned(x + c[u][0]);
 #pragma unroll
-            for (int j = 1; j < V; j++)
-            {
-                if (c[u][j] != c[u][j - 1])
-                    xv[u][j] = ld_x_pinned(x + c[u][j]);
-                else
-                    xv[u][j] = xv[u][j - 1];
-            }
-        }
+            for (int j = 0; j < V; j++) xv[u][j] = ld_x_pinned(x + c[u][j]);
 #pragma unroll
         for (int u = 0; u < U; u++)
 #pragma unroll
