@@ -56,7 +56,7 @@ class PlanDesc(C.Structure):
 
 
 EXPORTS = [
-    "asp_ctx_create", "asp_multicast_store", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_destroy",
+    "asp_ctx_create", "asp_multicast_store", "asp_probe_gather", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_destroy",
     "asp_plan_set_launch", "asp_plan_format_bytes", "asp_plan_launches", "asp_spmv", "asp_spmv_host", "asp_time",
     "asp_synchronize", "asp_status_str", "asp_last_error", "asp_built_for_sm100a", "asp_spmv_host_static",
     "asp_static_stage_bytes",
@@ -83,6 +83,8 @@ def lib() -> C.CDLL:
     L.asp_ctx_create.restype = C.c_int
     L.asp_multicast_store.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int]
     L.asp_multicast_store.restype = C.c_int
+    L.asp_probe_gather.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]
+    L.asp_probe_gather.restype = C.c_int
     L.asp_ctx_destroy.argtypes = [C.c_void_p]
     L.asp_ctx_destroy.restype = None
     L.asp_ctx_stream.argtypes = [C.c_void_p]

@@ -3,11 +3,12 @@ vector that fits L2 does one GPU sustain when nothing else is asked of it?
 
     python -m alphasparse_b200.probe_gather [--n 8388608] [--gathers 46000000] [--dtype f32]
 
-The indices are read coalesced and the gathered values are only summed (torch.index_select followed
-by a reduction is avoided: the gather itself is timed with a preallocated output, so the kernel
-moves 4 B of index, one 32-byte sector of x and 4 B of output per gather). The figure bounds every
-SpMV kernel on a matrix with uniformly random columns, whatever its format: each non-zero costs one
-such gather, and the L1 hands the L2 about one sector request per clock and SM.
+Two measurements: torch.index_select into a preallocated output (4 B of index, one 32-byte sector of
+x and 4 B of output per gather), with random and with sorted indices, and the library's gather-only
+kernel (asp_probe_gather: eight gathers per thread in flight, nothing stored) swept over launch
+shapes. The best figure bounds every SpMV kernel on a matrix with uniformly random columns, whatever
+its format: each non-zero costs one such gather, and the L1 hands the L2 about one sector request
+per clock and SM.
 """
 from __future__ import annotations
 
@@ -46,7 +47,27 @@ def main():
         us = e0.elapsed_time(e1) / args.reps * 1e3
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         res[name] = {"us": us, "gathers_per_s": args.gathers / (us * 1e-6), "gathers_per_clock_per_sm_at_1965MHz": args.gathers / (us * 1e-6) / sms / 1.965e9}
-    print(json.dumps({"probe": "gather", "n": args.n, "gathers": args.gathers, "dtype": args.dtype, **res}))
+    # the library's own gather-only kernel (f32), swept over launch shapes
+    best = None
+    if args.dtype == "f32":
+        import ctypes as C
+
+        from . import capi
+
+        L = capi.lib()
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        idx_u = idx.contiguous()
+        one = torch.zeros(1, device=dev, dtype=torch.float32)
+        torch.cuda.synchronize()
+        for threads in (128, 256, 512):
+            for per_sm in (4, 8, 16, 32):
+                ms = C.c_float()
+                capi.check(L.asp_probe_gather(idx_u.data_ptr(), x.data_ptr(), one.data_ptr(), args.gathers, threads, sms * per_sm, args.reps,
+                                              torch.cuda.current_stream().cuda_stream, C.byref(ms)))
+                rate = args.gathers / (ms.value * 1e-3)
+                if best is None or rate > best["gathers_per_s"]:
+                    best = {"us": ms.value * 1e3, "gathers_per_s": rate, "gathers_per_clock_per_sm_at_1965MHz": rate / sms / 1.965e9, "threads": threads, "ctas_per_sm": per_sm}
+    print(json.dumps({"probe": "gather", "n": args.n, "gathers": args.gathers, "dtype": args.dtype, "torch_index_select": res, "gather_only_kernel_best": best}))
 
 
 if __name__ == "__main__":

@@ -187,6 +187,14 @@ asp_status asp_spmv_host(asp_ctx *ctx, asp_plan *const *plans, int n_plans, cons
 asp_status asp_spmv_host_static(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *h_x, void *h_y);
 uint64_t asp_static_stage_bytes(void);
 
+/* Diagnostic, not part of the SpMV path: times `reps` passes of a kernel that only gathers
+ * x[idx[i]] (u32 indices read coalesced, f32 values, eight gathers per thread in flight) with the
+ * given launch shape on `stream`; all pointers are device memory, `d_out_f32` needs one element.
+ * The rate is the ceiling of any SpMV whose columns are random (one gather per non-zero). No
+ * counterpart in the reference. */
+asp_status asp_probe_gather(const void *d_idx_u32, const void *d_x_f32, void *d_out_f32, size_t n_gathers, int threads, int ctas, int reps, void *stream,
+                            float *ms_per_pass);
+
 /* Publishes `bytes` of finished results at `src` (this GPU's memory) to every GPU of an NVLink
  * multicast group: `multicast_dst` is the multicast address of the same offset of a buffer that all
  * the GPUs mapped symmetrically (e.g. torch.distributed._symmetric_memory). The stores are issued by a
