@@ -12,9 +12,13 @@ from . import capi, matrices_gpu, tuner
 from .dist import ShardedSpmv, balanced_bounds_from_degrees
 from .graph import partition_rows_by_nnz
 
-# One CSR5-like kernel over the unsorted block: no row sort, so y is written in row order and a row
-# chunk of the block is a contiguous slice of the next x.
-DEFAULT_GRAPH = {"dense": "dense compress", "subs": [{"graph": "S9_K9_s32", "nodes": ["tlb_nnz 32"], "template": "K9", "threads": 128, "row_reduce": 1}]}
+# One CSR5-like kernel over the block. The coarse row sort with a bin wider than any row is a stable
+# partition: rows keep their order, rows without non-zeros go last, where the CSR5-like lowering
+# drops them (it would otherwise store one explicit zero per empty row, and R-MAT blocks are up to
+# half empty rows). y is still written in nearly row order, so a row chunk of the block is a
+# contiguous slice of the next x.
+DEFAULT_GRAPH = {"dense": "dense sort 1073741824 | dense compress",
+                 "subs": [{"graph": "S9_K9_s32", "nodes": ["tlb_nnz 32"], "template": "K9", "threads": 128, "row_reduce": 1}]}
 
 
 def run(args, rank: int, world: int, local_rank: int, dist, log):
