@@ -52,7 +52,15 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
     t0 = time.perf_counter()
     # row chunks of this rank's block (nnz-balanced), one plan group each: chunk c is exchanged
     # while chunk c+1 is computed
-    cuts = partition_rows_by_nnz(m.indptr, n_chunks)
+    if args.chunk_shape == "geometric" and n_chunks > 1:
+        # chunk c (in row order) holds 2^c shares of the block's non-zeros: the chunk that is
+        # computed and published last is the smallest, so the exposed exchange is short
+        tot = float(m.indptr[-1])
+        fr = [(2.0 ** (c + 1) - 1.0) / (2.0 ** n_chunks - 1.0) for c in range(n_chunks - 1)]
+        cuts = np.array([0] + [int(np.searchsorted(m.indptr, f * tot, side="left")) for f in fr] + [m.n_rows], dtype=np.int64)
+        cuts = np.maximum.accumulate(cuts)
+    else:
+        cuts = partition_rows_by_nnz(m.indptr, n_chunks)
     if args.graph:
         import json
         import os
@@ -73,8 +81,18 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
         desc = DEFAULT_GRAPH
     fmts, groups, chunks = [], [], []
     # most rows first: the exchange of the last chunk is the only one no kernel hides
-    for c in sorted(range(n_chunks), key=lambda c: -(int(cuts[c + 1]) - int(cuts[c]))):
+    order = sorted(range(n_chunks), key=lambda c: -(int(cuts[c + 1]) - int(cuts[c])))
+    if args.chunk_shape == "geometric":
+        order = list(range(n_chunks - 1, -1, -1))  # the big tail chunk first, the small head chunk last
+    for c in order:
         lo, hi = int(cuts[c]), int(cuts[c + 1])
+        if hi == lo or m.indptr[hi] == m.indptr[lo]:
+            # nothing to compute: the rows (if any) stay zero; still a chunk so that every rank has as many
+            def fz(xt, yt):
+                yt.zero_()
+
+            chunks.append((fz, lo, hi))
+            continue
         mc = m.row_slice(lo, hi) if n_chunks > 1 else m
         f, g = tuner.build(ctx, mc, desc)
         fmts.append(f)

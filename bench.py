@@ -179,7 +179,7 @@ def run_c5(args, rank, world, local_rank, dist):
             "config": {"workload": "c5", "description": f"R-MAT scale {args.scale}, edge factor 16, a/b/c/d .57/.19/.19/.05, seed 4, {iters} repeated SpMVs per step",
                        "rows": n, "nnz": nnz, "rows_rank0": r["rows_local"], "nnz_rank0": r["nnz_local"], "graph_rank0": r["graph"],
                        "l2": "inputs larger than L2", "search_s": round(r["search_s"], 1), "generate_s": round(r["gen_s"], 1),
-                       "ms_per_spmv": r["ms_per_spmv"], "ms_compute_per_spmv_max_over_ranks": r["ms_compute_per_spmv_max"], "row_chunks_per_rank": r["chunks"], "balance": args.balance,
+                       "ms_per_spmv": r["ms_per_spmv"], "ms_compute_per_spmv_max_over_ranks": r["ms_compute_per_spmv_max"], "row_chunks_per_rank": r["chunks"], "chunk_shape": args.chunk_shape, "balance": args.balance,
                        "exchange": "none (1 GPU)" if world == 1 else f"{r['exchange_used']} of each row chunk on a second stream, overlapped with the next chunk's kernel"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world), "traffic": None,
                          "peak_kind": peak_kind, "algorithmic_bytes": b_alg, "note": "x gathers are random over 2^scale columns: DRAM traffic exceeds the algorithmic bytes"},
@@ -248,6 +248,7 @@ def main():
     ap.add_argument("--scale", type=int, default=26, help="c5: R-MAT scale (2^scale rows)")
     ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x by an unpadded exchange of the ranks' slices)")
     ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank whose exchange overlaps the next chunk's kernels (0: 4 when sharded, else 1)")
+    ap.add_argument("--chunk-shape", default="equal", choices=["equal", "geometric"], help="c5: equal non-zeros per chunk, or chunk sizes halving towards the one published last")
     ap.add_argument("--exchange", default="allgather", choices=["multicast", "allgather", "a2a"], help="c5: NCCL form of the unpadded slice exchange")
     ap.add_argument("--balance", default="nnz", choices=["nnz", "bytes"], help="c5: what the row blocks of the ranks have equal amounts of")
     ap.add_argument("--search", action="store_true", help="c5: run the quick search instead of the default one-kernel graph")
