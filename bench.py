@@ -130,6 +130,9 @@ def cpu_baseline(m, x, budget_s: float = 15.0, reps_min: int = 3):
 def run_reference(args, rank, world):
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every host core
+    # this process may run on (the OpenMP runtime reads the variable when the oracle library loads)
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     desc, gen = WORKLOADS[args.workload]
     m, x = gen()
     W, K = max(args.warmup, 1), max(args.steps, 1)
