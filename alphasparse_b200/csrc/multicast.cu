@@ -32,17 +32,7 @@ __global__ void __launch_bounds__(512) k_mc_store(const unsigned *__restrict__ s
     if (tid < head) mc_store1(mc + tid, src[tid]);
     const uint4 *s4 = reinterpret_cast<const uint4 *>(src + head);
     unsigned *m4 = mc + head;
-    size_t i = tid;
-    for (; i + 3 * nthr < body; i += 4 * nthr)
-    {
-        // four independent 16-byte loads in flight per thread before the stores
-        const uint4 a = __ldcs(s4 + i), b = __ldcs(s4 + i + nthr), c = __ldcs(s4 + i + 2 * nthr), d = __ldcs(s4 + i + 3 * nthr);
-        mc_store4(m4 + i * 4, a);
-        mc_store4(m4 + (i + nthr) * 4, b);
-        mc_store4(m4 + (i + 2 * nthr) * 4, c);
-        mc_store4(m4 + (i + 3 * nthr) * 4, d);
-    }
-    for (; i < body; i += nthr) mc_store4(m4 + i * 4, __ldcs(s4 + i));
+    for (size_t i = tid; i < body; i += nthr) mc_store4(m4 + i * 4, __ldcs(s4 + i));
     if (tid < words - tail0) mc_store1(mc + tail0 + tid, src[tail0 + tid]);
     __threadfence_system();
 }
