@@ -47,7 +47,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
     if log:
         log(f"rows [{r0}, {r1}) nnz {nnz_local} generated in {gen_s:.1f} s")
 
-    n_chunks = max(1, args.chunks if args.chunks > 0 else (4 if world > 1 else 1))
+    n_chunks = max(1, args.chunks if args.chunks > 0 else (2 if world > 1 else 1))
     ctx = capi.Context(local_rank)
     t0 = time.perf_counter()
     # row chunks of this rank's block (nnz-balanced), one plan group each: chunk c is exchanged

@@ -250,9 +250,10 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"])
     ap.add_argument("--scale", type=int, default=26, help="c5: R-MAT scale (2^scale rows)")
     ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x by an unpadded exchange of the ranks' slices)")
-    ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank whose exchange overlaps the next chunk's kernels (0: 4 when sharded, else 1)")
+    ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank whose exchange overlaps the next chunk's kernels (0: 2 when sharded, else 1)")
     ap.add_argument("--chunk-shape", default="equal", choices=["equal", "geometric"], help="c5: equal non-zeros per chunk, or chunk sizes halving towards the one published last")
-    ap.add_argument("--exchange", default="allgather", choices=["multicast", "allgather", "a2a"], help="c5: NCCL form of the unpadded slice exchange")
+    ap.add_argument("--exchange", default="multicast", choices=["multicast", "allgather", "a2a"],
+                    help="c5: how a rank's slice of the next x reaches the others (multicast falls back to allgather where symmetric memory has no multicast address)")
     ap.add_argument("--balance", default="nnz", choices=["nnz", "bytes"], help="c5: what the row blocks of the ranks have equal amounts of")
     ap.add_argument("--search", action="store_true", help="c5: run the quick search instead of the default one-kernel graph")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
