@@ -53,6 +53,9 @@ CASES = [
     ("mixed", _mixed, "dense sort 1\ndense compress\nsub all blb_row_nnz 4096\nsub all wlb_col_fixed 32\nsub all template K8"),
     ("mixed", _mixed, "dense sort 1\ndense rowdiv_exp 128 4096 8\ndense compress\nsub all row_padding 32 1\nsub all blb_row_evenly 32\nsub all tlb_col_fixed 4\nsub all template K6"),
     ("mixed", _mixed, "dense sort 1\ndense rowdiv_exp 512 4096 16\ndense compress\nsub all blb_row_nnz 4096\nsub all wlb_col_fixed 64\nsub all template K8"),
+    # one-bin coarse sort = stable partition that only moves rows without non-zeros to the end
+    ("rmat", lambda: M.rmat(11, 8, seed=4)[0], "dense sort 1073741824\ndense compress\nsub all tlb_nnz 8\nsub all template K9"),
+    ("rmat", lambda: M.rmat(11, 8, seed=4)[0], "dense sort 1073741824\ndense compress\nsub all tlb_nnz 32\nsub all template K10"),
 ]
 _cache = {}
 

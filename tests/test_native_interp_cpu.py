@@ -1,0 +1,58 @@
+"""CPU suite: y computed from the NATIVE format arrays by the template interpreter equals the CSR
+oracle, for every strategy on seeded and on randomly drawn matrices (rows without non-zeros, a few
+long rows, sorted and unsorted). This checks the native operators and lowerings beyond the inputs the
+reference itself can process, without a GPU."""
+import numpy as np
+import pytest
+from hypothesis import given, settings, strategies as st
+
+import plan_interp
+import refdump
+import specs
+from alphasparse_b200 import matrices as M
+from alphasparse_b200.graph import Matrix
+from native_manifest import NativeManifest
+
+
+def check(m, x, spec, what):
+    fmt = Matrix.from_csr(m).execute(spec)
+    y = plan_interp.interpret(NativeManifest(fmt, m.n_rows), x)
+    y_ref, scale = refdump.csr_ref(m, x)
+    err = refdump.rel_err(y, y_ref, scale)
+    assert err <= 1e-12, f"{what}: {err}"
+    fmt.close()
+
+
+@pytest.mark.parametrize("spec", sorted(specs.COMPRESSED_SPECS))
+def test_every_strategy_native_uniform(spec):
+    m, x = M.uniform_random(600, 9, seed=5, dtype=np.float64)
+    check(m, x, specs.full_spec(spec), spec)
+
+
+@pytest.mark.parametrize("dense", ["dense compress", "dense sort 1\ndense compress", "dense sort 1073741824\ndense compress"])
+@pytest.mark.parametrize("spec", ["S9_K9", "S9_K10", "S8_K7", "S3_K6", "S7_K8"])
+def test_rows_without_nonzeros_sorted_and_unsorted(dense, spec):
+    m, x = M.rmat(9, 6, seed=4)
+    check(m, x.astype(np.float32), specs.full_spec(spec, dense), f"{dense!r} {spec}")
+
+
+def test_wide_sell_strips_keep_their_size():
+    m, x = M.rmat(11, 8, seed=4)
+    for dense in ("dense compress", "dense sort 1\ndense compress"):
+        check(m, x, dense + "\nsub all row_padding 128 1\nsub all blb_row_evenly 128\nsub all tlb_row\nsub all template K2", f"wide SELL {dense!r}")
+
+
+@settings(max_examples=25, deadline=None)
+@given(seed=st.integers(0, 10_000), n=st.integers(40, 400), tail=st.integers(0, 3),
+       spec=st.sampled_from(["S9_K9", "S9_K10", "S8_K7", "S3_K6", "S2_K6", "S7_K8"]), sort=st.booleans())
+def test_random_matrices_with_empty_and_long_rows(seed, n, tail, spec, sort):
+    rng = np.random.default_rng(seed)
+    lengths = np.minimum(rng.zipf(1.7, size=n), n // 2)
+    lengths[rng.random(n) < 0.3] = 0  # empty rows
+    if tail:
+        lengths[rng.integers(0, n, size=tail)] = rng.integers(n // 2, n, size=tail)  # long rows
+    if lengths.sum() == 0:
+        lengths[0] = 1
+    m, x = M.from_row_lengths(lengths, n, seed=seed, dtype=np.float64)
+    dense = "dense sort 1\ndense compress" if sort else "dense compress"
+    check(m, x, specs.full_spec(spec, dense), f"seed {seed} n {n} {spec} sort {sort}")
