@@ -59,7 +59,7 @@ EXPORTS = [
     "asp_ctx_create", "asp_multicast_store", "asp_probe_gather", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_destroy",
     "asp_plan_set_launch", "asp_plan_format_bytes", "asp_plan_launches", "asp_spmv", "asp_spmv_host", "asp_time",
     "asp_synchronize", "asp_status_str", "asp_last_error", "asp_built_for_sm100a", "asp_spmv_host_static",
-    "asp_static_stage_bytes",
+    "asp_static_stage_bytes", "asp_search_gpu",
 ]
 
 _lib = None

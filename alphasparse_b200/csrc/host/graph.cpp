@@ -3,7 +3,9 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
 #include <map>
+#include <memory>
 #include <new>
 #include <sstream>
 #include <string>
@@ -14,6 +16,12 @@
 
 using namespace asp::host;
 
+static uint64_t next_format_id()
+{
+    static std::atomic<uint64_t> n{0};
+    return ++n;
+}
+
 struct asp_matrix
 {
     std::unique_ptr<Matrix> m;
@@ -21,6 +29,7 @@ struct asp_matrix
 
 struct asp_format
 {
+    uint64_t id = next_format_id(); // unique per process: addresses are reused, ids are not
     std::unique_ptr<Matrix> m; // the transformed copy (owns the shared permutation)
     std::vector<TemplateData> subs;
     std::vector<std::vector<asp_array_desc>> descs;
@@ -467,6 +476,7 @@ asp_status asp_graph_execute(const asp_matrix *in, const char *spec, asp_format 
 
 void asp_format_destroy(asp_format *f) { delete f; }
 int asp_format_num_subs(const asp_format *f) { return f ? (int)f->subs.size() : 0; }
+uint64_t asp_format_id(const asp_format *f) { return f ? f->id : 0; }
 
 asp_status asp_format_global_perm(const asp_format *f, const void **ptr, int *dtype, uint64_t *len)
 {

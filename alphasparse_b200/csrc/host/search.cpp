@@ -1,0 +1,417 @@
+// The search loop over Operator Graphs (the reference's search_strategy.cc stop rule, the whitelist
+// strategies of whilte_list_path_impl.cc:3411-4579 and the launch sweeps of
+// default_auto_tuner.cc:449-2030), written against the public host C ABI and a timing callback, so
+// that the same loop runs with the GPU as the timer or, in the CPU tests, with a model of it.
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstdio>
+#include <memory>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "../../../include/asp_b200_host.h"
+
+namespace
+{
+struct Launch
+{
+    int64_t threads, reduce;
+};
+
+struct Candidate
+{
+    std::string name;
+    std::vector<std::string> nodes; // compressed-view node lines without the "sub <id>" prefix
+    std::string templ;              // "K1" .. "K10"
+    std::vector<Launch> launches;
+
+    std::string lines(int sub) const
+    {
+        std::string s;
+        const std::string pre = "sub " + std::to_string(sub) + " ";
+        for (const std::string &n : nodes) s += pre + n + "\n";
+        s += pre + "template " + templ;
+        return s;
+    }
+};
+
+// register_integer_independ_param_to_enumerater semantics: lo, lo + step, ... while <= hi
+std::vector<int64_t> integer_range(int64_t lo, int64_t hi, int64_t step)
+{
+    std::vector<int64_t> v;
+    for (int64_t x = lo; x <= hi; x += step) v.push_back(x);
+    return v;
+}
+
+int64_t ceil32(int64_t v) { return (v + 31) / 32 * 32; }
+
+std::vector<Launch> cross(const std::vector<int64_t> &threads, const std::vector<int64_t> &reduces)
+{
+    std::vector<Launch> l;
+    for (int64_t t : threads)
+        for (int64_t r : reduces) l.push_back({t, r});
+    return l;
+}
+
+std::vector<Candidate> compressed_candidates(uint64_t mn_, uint64_t mx_, double avg, bool is_sorted, bool quick)
+{
+    const int64_t mn = (int64_t)mn_, mx = (int64_t)mx_;
+    std::vector<Candidate> out;
+    const std::vector<int64_t> T3 = quick ? std::vector<int64_t>{128, 256} : integer_range(32, 256, 32);
+    const std::vector<int64_t> T2 = {128, 256};
+    if (mn >= 128)
+    {
+        // strategy 8: BLB_COL_DIV(c) -> long-row template; c = 128 .. min(4096, ceil32(max)), doubling
+        std::vector<int64_t> cs;
+        for (int64_t c = 128; c <= std::min<int64_t>(4096, ceil32(mx)); c *= 2) cs.push_back(c);
+        const size_t from = (quick && cs.size() > 2) ? cs.size() - 2 : 0;
+        for (size_t i = from; i < cs.size(); i++)
+        {
+            const int64_t c = cs[i];
+            std::set<int64_t> th = {std::min<int64_t>(1024, std::max<int64_t>(32, c / 16)), std::min<int64_t>(1024, std::max<int64_t>(64, c / 8)),
+                                    std::min<int64_t>(1024, std::max<int64_t>(64, c / 4))};
+            out.push_back({"S8_K7_c" + std::to_string(c), {"blb_col_fixed " + std::to_string(c)}, "K7", cross(std::vector<int64_t>(th.begin(), th.end()), {1})});
+        }
+    }
+    if (mx <= 512)
+    {
+        out.push_back({"S5_K3", {"row_padding 32 1", "tlb_row"}, "K3", cross(T3, {1})});
+        for (int64_t mm : (quick ? std::vector<int64_t>{128, 256} : std::vector<int64_t>{64, 128, 192, 256}))
+            out.push_back({"S1_K2_m" + std::to_string(mm), {"row_padding " + std::to_string(mm) + " 1", "blb_row_evenly " + std::to_string(mm), "tlb_row"}, "K2", cross(T2, {1})});
+    }
+    if (!is_sorted)
+    {
+        // strategy 9: TLB_NNZ_DIV(s) -> CSR5-like templates, s = 2 .. min(avg, 32); rows of any length
+        const int64_t hi = (int64_t)std::max(2.0, std::min(avg, 32.0));
+        std::set<int64_t> ss;
+        if (quick) ss = {2, std::max<int64_t>(2, hi / 2), hi};
+        else
+        {
+            int64_t step = std::max<int64_t>(1, (hi - 2) / 3);
+            for (int64_t v : integer_range(2, hi, step)) ss.insert(v);
+        }
+        if (mx > 512)
+        {
+            ss.insert(8);
+            ss.insert(16);
+        }
+        for (int64_t s : ss)
+        {
+            out.push_back({"S9_K9_s" + std::to_string(s), {"tlb_nnz " + std::to_string(s)}, "K9", cross(T2, {1})});
+            out.push_back({"S9_K10_s" + std::to_string(s), {"tlb_nnz " + std::to_string(s)}, "K10", cross(T2, {1})});
+        }
+    }
+    if (mn >= 30 && mx <= 512)
+    {
+        // strategy 4: WLB_COL_DIV(c) -> warp per row chunk; c from 32 up past the longest row
+        const int64_t step = std::max<int64_t>(32, ceil32(std::max<int64_t>(1, (mx - mn) / 3)));
+        const std::vector<int64_t> cs = integer_range(32, ceil32(mx) + step, step);
+        std::vector<int64_t> use = cs;
+        if (quick && !cs.empty()) use = {cs.front(), cs.back()}; // (the same value twice when there is one)
+        for (int64_t c : use)
+            out.push_back({"S4_K4_c" + std::to_string(c), {"wlb_col_fixed " + std::to_string(c)}, "K4", cross(quick ? T2 : integer_range(32, 512, 64), {1})});
+    }
+    if (mn >= 32 && mx <= 1024)
+    {
+        std::vector<int64_t> cs = integer_range(32, std::min<int64_t>(128, ceil32((mx + 1) / 2)), 32);
+        if (cs.empty()) cs = {32};
+        const std::vector<int64_t> use = quick ? std::vector<int64_t>{cs.back()} : cs;
+        for (int64_t mm : (quick ? std::vector<int64_t>{4} : std::vector<int64_t>{2, 4}))
+            for (int64_t c : use)
+                out.push_back({"S6_K8_m" + std::to_string(mm) + "_c" + std::to_string(c),
+                               {"row_padding " + std::to_string(mm) + " 1", "blb_row_evenly " + std::to_string(mm), "wlb_col_fixed " + std::to_string(c)}, "K8", cross(T2, {1, 4})});
+        for (int64_t bb : (quick ? std::vector<int64_t>{512} : std::vector<int64_t>{128, 512, 896}))
+            for (int64_t c : use)
+                out.push_back({"S7_K8_b" + std::to_string(bb) + "_c" + std::to_string(c), {"blb_row_nnz " + std::to_string(bb), "wlb_col_fixed " + std::to_string(c)}, "K8", cross(T2, {1, 4})});
+    }
+    if (mx <= 1024)
+    {
+        const std::vector<int64_t> cs = integer_range(1, std::min<int64_t>(16, std::max<int64_t>(1, (mx + 1) / 2)), 3);
+        std::vector<int64_t> use = cs;
+        if (quick && cs.size() > 2) use = {cs[0], cs[1]};
+        for (int64_t mm : (quick ? std::vector<int64_t>{64} : std::vector<int64_t>{32, 64}))
+            for (int64_t c : use)
+                out.push_back({"S2_K6_m" + std::to_string(mm) + "_c" + std::to_string(c),
+                               {"row_padding " + std::to_string(mm) + " 1", "blb_row_evenly " + std::to_string(mm), "tlb_col_fixed " + std::to_string(c)}, "K6", cross(T2, {1, 4})});
+        if (!quick)
+            for (int64_t bb : {128, 512, 896})
+                for (int64_t c : cs)
+                    out.push_back({"S3_K6_b" + std::to_string(bb) + "_c" + std::to_string(c), {"blb_row_nnz " + std::to_string(bb), "tlb_col_fixed " + std::to_string(c)}, "K6", cross(T2, {1, 4, 16})});
+    }
+    return out;
+}
+
+std::vector<std::string> dense_strategies(bool quick)
+{
+    std::vector<std::string> out = {"dense compress", "dense rowdiv_exp 32 4096 4\ndense compress"};
+    std::vector<std::pair<int, int>> g3;
+    if (quick) g3 = {{128, 8}};
+    else
+        for (int mn : {512, 128, 32})
+            for (int r : {4, 8, 16}) g3.push_back({mn, r});
+    for (auto &p : g3) out.push_back("dense sort 1\ndense rowdiv_exp " + std::to_string(p.first) + " 4096 " + std::to_string(p.second) + "\ndense compress");
+    return out;
+}
+
+int template_id(const std::string &k)
+{
+    static const char *names[] = {"K1", "K2", "K3", "K5", "K6", "K7", "K8", "K4", "K9", "K10"}; // asp_template_type order
+    for (int i = 0; i < 10; i++)
+        if (k == names[i]) return i;
+    return -1;
+}
+
+int64_t derive_tblock(int templ, uint64_t n_tlb, uint64_t n_wlb, uint64_t n_blb, int64_t threads)
+{
+    // one CTA per BLB for the CTA-per-BLB templates, ceil(units / threads) otherwise
+    uint64_t n;
+    switch (templ)
+    {
+    case 0: case 1: case 3: case 4: case 5: case 6: n = n_blb; break; // K1 K2 K5 K6 K7 K8
+    case 7: n = (32 * n_wlb + (uint64_t)threads - 1) / (uint64_t)threads; break; // K4
+    default: n = (n_tlb + (uint64_t)threads - 1) / (uint64_t)threads; break;      // K3 K9 K10
+    }
+    return (int64_t)std::max<uint64_t>(1, std::min<uint64_t>(n, 2147483647ull));
+}
+
+// search_strategy.cc:5-80
+struct StopRule
+{
+    uint64_t remain = 10, struggle;
+    double limit, best = 0;
+    std::chrono::steady_clock::time_point t0 = std::chrono::steady_clock::now();
+    StopRule(uint64_t s, double l) : struggle(s), limit(l) {}
+    bool out_of_time() const { return limit > 0 && std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() >= limit; }
+    bool go_on(double gflops)
+    {
+        if (gflops > best)
+        {
+            remain = (uint64_t)std::max(5.0, std::min(25.0, std::floor((gflops - best) * 5)));
+            best = gflops;
+        }
+        else if (remain > 0) remain--;
+        else if (struggle > 0) struggle--;
+        else return false;
+        return !out_of_time();
+    }
+};
+
+struct Pick
+{
+    Candidate cand;
+    Launch launch;
+    float ms;
+};
+
+struct FormatDeleter
+{
+    void operator()(asp_format *f) const { asp_format_destroy(f); }
+};
+struct MatrixDeleter
+{
+    void operator()(asp_matrix *m) const { asp_matrix_destroy(m); }
+};
+typedef std::unique_ptr<asp_format, FormatDeleter> FormatPtr;
+typedef std::unique_ptr<asp_matrix, MatrixDeleter> MatrixPtr;
+
+std::string one_line(std::string s)
+{
+    size_t p = 0;
+    while ((p = s.find('\n', p)) != std::string::npos) s.replace(p, 1, " | ");
+    return s;
+}
+
+thread_local std::string g_text;
+} // namespace
+
+struct asp_search_result
+{
+    std::string dense;
+    std::vector<std::string> sub_spec, sub_name;
+    std::vector<Launch> launch;
+    float ms = 0;
+    std::vector<std::string> trials;
+};
+
+extern "C" {
+
+const char *asp_search_candidates(uint64_t mn, uint64_t mx, double avg, int is_sorted, int quick)
+{
+    g_text.clear();
+    for (const Candidate &c : compressed_candidates(mn, mx, avg, is_sorted != 0, quick != 0))
+    {
+        g_text += c.name + " ; " + c.templ + " ; ";
+        for (size_t i = 0; i < c.nodes.size(); i++) g_text += (i ? "|" : "") + c.nodes[i];
+        g_text += " ; ";
+        for (size_t i = 0; i < c.launches.size(); i++) g_text += (i ? "," : "") + std::to_string(c.launches[i].threads) + ":" + std::to_string(c.launches[i].reduce);
+        g_text += "\n";
+    }
+    return g_text.c_str();
+}
+
+int64_t asp_search_derive_tblock(int template_type, uint64_t n_tlb, uint64_t n_wlb, uint64_t n_blb, int64_t threads)
+{
+    return derive_tblock(template_type, n_tlb, n_wlb, n_blb, threads > 0 ? threads : 1);
+}
+
+asp_status asp_search(const asp_matrix *m, const asp_search_options *opt_, asp_time_fn time_fn, void *time_user, asp_search_result **out)
+{
+    if (!m || !time_fn || !out) return ASP_ERR_INVALID_ARG;
+    *out = nullptr;
+    asp_search_options opt = {};
+    if (opt_) opt = *opt_;
+    else
+    {
+        opt.quick = 1;
+        opt.struggle_step_num = -1;
+    }
+    if (opt.warmup <= 0) opt.warmup = 2;
+    if (opt.reps <= 0) opt.reps = 10;
+    if (opt.max_subs <= 0) opt.max_subs = 5;
+    const double pad_bound = opt.padding_rate_up_bound > 0 ? opt.padding_rate_up_bound : 4.0;
+    auto log = [&](const std::string &s) {
+        if (opt.log_fn) opt.log_fn(opt.log_user, s.c_str());
+    };
+    const uint64_t total_nnz = asp_matrix_nnz(m);
+
+    std::unique_ptr<asp_search_result> best;
+    std::vector<std::string> trials;
+    for (const std::string &dense : dense_strategies(opt.quick != 0))
+    {
+        asp_matrix *cm_raw = nullptr;
+        if (asp_dense_execute(m, dense.c_str(), &cm_raw) != ASP_OK) continue;
+        MatrixPtr cm(cm_raw);
+        const int n = asp_matrix_num_subs(cm.get());
+        // the reference abandons row divisions that give too many strips or no split at all
+        if (n <= 0 || n > opt.max_subs || (n == 1 && dense.find("rowdiv") != std::string::npos)) continue;
+        log("dense view: " + one_line(dense) + " -> " + std::to_string(n) + " sub-matrices");
+        const bool is_sorted = dense.find("sort") != std::string::npos;
+        std::vector<Pick> picks;
+        bool ok = true;
+        for (int sub = 0; sub < n && ok; sub++)
+        {
+            uint64_t rows = 0, nnz = 0, mn = 0, mx = 0;
+            if (asp_matrix_sub_rows(cm.get(), sub, &rows, &nnz, &mn, &mx) != ASP_OK)
+            {
+                ok = false;
+                break;
+            }
+            std::string others;
+            for (int j = 0; j < n; j++)
+                if (j != sub) others += "\nsub " + std::to_string(j) + " template EMPTY";
+            std::unique_ptr<StopRule> rule;
+            if (opt.struggle_step_num >= 0) rule.reset(new StopRule((uint64_t)opt.struggle_step_num, opt.time_limit_s));
+            bool have = false, stop = false;
+            Pick bestp{};
+            for (const Candidate &cand : compressed_candidates(mn, mx, rows ? (double)nnz / (double)rows : 0.0, is_sorted, opt.quick != 0))
+            {
+                asp_format *f_raw = nullptr;
+                if (asp_graph_execute(cm.get(), (cand.lines(sub) + others).c_str(), &f_raw) != ASP_OK)
+                {
+                    log("  sub " + std::to_string(sub) + " " + cand.name + ": graph rejected (" + asp_host_last_error() + ")");
+                    continue;
+                }
+                FormatPtr f(f_raw);
+                const double rate = asp_format_padding_rate(f.get(), sub);
+                if (rate > pad_bound) continue;
+                asp_sub_info info;
+                if (asp_format_sub_info(f.get(), sub, &info) != ASP_OK) continue;
+                const int tid = template_id(cand.templ);
+                for (const Launch &l : cand.launches)
+                {
+                    std::vector<int64_t> tb(n, 1), th(n, 32), rd(n, 1);
+                    tb[sub] = derive_tblock(tid, info.n_tlb, info.n_wlb, info.n_blb, l.threads);
+                    th[sub] = l.threads;
+                    rd[sub] = l.reduce;
+                    float ms = 0;
+                    if (time_fn(time_user, f.get(), tb.data(), th.data(), rd.data(), opt.warmup, opt.reps, &ms) != 0 || !(ms > 0))
+                    {
+                        log("  sub " + std::to_string(sub) + " " + cand.name + " threads=" + std::to_string(l.threads) + ": cannot run");
+                        continue;
+                    }
+                    char buf[512];
+                    snprintf(buf, sizeof buf, "%s ; sub %d ; %s ; %lld ; %lld ; %.6f ; %.4f", one_line(dense).c_str(), sub, cand.name.c_str(), (long long)l.threads,
+                             (long long)l.reduce, ms, rate);
+                    trials.push_back(buf);
+                    snprintf(buf, sizeof buf, "  sub %d [%llu rows, nnz/row %llu..%llu] %s threads=%lld reduce=%lld: %.1f us", sub, (unsigned long long)rows, (unsigned long long)mn,
+                             (unsigned long long)mx, cand.name.c_str(), (long long)l.threads, (long long)l.reduce, ms * 1e3);
+                    log(buf);
+                    if (!have || ms < bestp.ms)
+                    {
+                        bestp = {cand, l, ms};
+                        have = true;
+                    }
+                    if (rule && !rule->go_on(2.0 * (double)nnz * 1e-6 / ms))
+                    {
+                        stop = true;
+                        break;
+                    }
+                }
+                if (stop)
+                {
+                    log("  sub " + std::to_string(sub) + ": search budget used up after " + cand.name);
+                    break;
+                }
+            }
+            if (!have) ok = false;
+            else picks.push_back(bestp);
+        }
+        if (!ok || (int)picks.size() != n) continue;
+        // the whole matrix with the per-strip winners
+        std::string spec;
+        for (int i = 0; i < n; i++) spec += (i ? "\n" : "") + picks[i].cand.lines(i);
+        asp_format *f_raw = nullptr;
+        if (asp_graph_execute(cm.get(), spec.c_str(), &f_raw) != ASP_OK) continue;
+        FormatPtr f(f_raw);
+        std::vector<int64_t> tb(n), th(n), rd(n);
+        for (int i = 0; i < n; i++)
+        {
+            asp_sub_info info;
+            if (asp_format_sub_info(f.get(), i, &info) != ASP_OK) ok = false;
+            tb[i] = derive_tblock(template_id(picks[i].cand.templ), info.n_tlb, info.n_wlb, info.n_blb, picks[i].launch.threads);
+            th[i] = picks[i].launch.threads;
+            rd[i] = picks[i].launch.reduce;
+        }
+        float ms = 0;
+        if (!ok || time_fn(time_user, f.get(), tb.data(), th.data(), rd.data(), opt.warmup, std::max(opt.reps, 20), &ms) != 0 || !(ms > 0)) continue;
+        char buf[160];
+        snprintf(buf, sizeof buf, "  whole matrix: %.1f us  %.1f GFLOP/s", ms * 1e3, 2.0 * (double)total_nnz * 1e-6 / ms);
+        log(buf);
+        if (!best || ms < best->ms)
+        {
+            best.reset(new asp_search_result());
+            best->dense = dense;
+            best->ms = ms;
+            for (int i = 0; i < n; i++)
+            {
+                best->sub_spec.push_back(picks[i].cand.lines(i));
+                best->sub_name.push_back(picks[i].cand.name);
+                best->launch.push_back(picks[i].launch);
+            }
+        }
+    }
+    if (!best) return ASP_ERR_UNSUPPORTED;
+    best->trials.swap(trials);
+    *out = best.release();
+    return ASP_OK;
+}
+
+void asp_search_result_destroy(asp_search_result *r) { delete r; }
+const char *asp_search_result_dense(const asp_search_result *r) { return r ? r->dense.c_str() : ""; }
+int asp_search_result_num_subs(const asp_search_result *r) { return r ? (int)r->sub_spec.size() : 0; }
+const char *asp_search_result_sub_spec(const asp_search_result *r, int i) { return (r && i >= 0 && i < (int)r->sub_spec.size()) ? r->sub_spec[i].c_str() : ""; }
+const char *asp_search_result_sub_name(const asp_search_result *r, int i) { return (r && i >= 0 && i < (int)r->sub_name.size()) ? r->sub_name[i].c_str() : ""; }
+asp_status asp_search_result_sub_launch(const asp_search_result *r, int i, int64_t *threads, int64_t *reduce)
+{
+    if (!r || i < 0 || i >= (int)r->launch.size() || !threads || !reduce) return ASP_ERR_INVALID_ARG;
+    *threads = r->launch[i].threads;
+    *reduce = r->launch[i].reduce;
+    return ASP_OK;
+}
+float asp_search_result_ms(const asp_search_result *r) { return r ? r->ms : 0.f; }
+int asp_search_result_num_trials(const asp_search_result *r) { return r ? (int)r->trials.size() : 0; }
+const char *asp_search_result_trial(const asp_search_result *r, int i) { return (r && i >= 0 && i < (int)r->trials.size()) ? r->trials[i].c_str() : ""; }
+
+} // extern "C"

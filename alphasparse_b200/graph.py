@@ -22,8 +22,21 @@ HOST_EXPORTS = [
     "asp_matrix_from_csr", "asp_matrix_from_coo_file", "asp_matrix_destroy", "asp_matrix_rows", "asp_matrix_cols",
     "asp_matrix_nnz", "asp_graph_execute", "asp_format_destroy", "asp_format_num_subs", "asp_format_global_perm",
     "asp_format_sub_info", "asp_format_plan_descs", "asp_format_padding_rate", "asp_host_last_error",
-    "asp_dense_execute", "asp_matrix_num_subs", "asp_matrix_sub_rows", "asp_partition_rows_by_nnz",
+    "asp_dense_execute", "asp_matrix_num_subs", "asp_matrix_sub_rows", "asp_partition_rows_by_nnz", "asp_format_id",
+    "asp_search", "asp_search_result_destroy", "asp_search_result_dense", "asp_search_result_num_subs", "asp_search_result_sub_spec",
+    "asp_search_result_sub_name", "asp_search_result_sub_launch", "asp_search_result_ms", "asp_search_result_num_trials",
+    "asp_search_result_trial", "asp_search_candidates", "asp_search_derive_tblock",
 ]
+
+LOG_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_char_p)
+# int time_fn(user, fmt, tblock[], threads[], reduce[], warmup, reps, *ms)
+TIME_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_int, C.c_int, C.POINTER(C.c_float))
+
+
+class SearchOptions(C.Structure):
+    """asp_search_options"""
+    _fields_ = [("quick", C.c_int32), ("warmup", C.c_int32), ("reps", C.c_int32), ("max_subs", C.c_int32), ("struggle_step_num", C.c_int32),
+                ("time_limit_s", C.c_double), ("padding_rate_up_bound", C.c_double), ("log_fn", LOG_FN), ("log_user", C.c_void_p)]
 
 _bound = False
 
@@ -65,6 +78,31 @@ def _lib():
         L.asp_format_padding_rate.restype = C.c_double
         L.asp_host_last_error.argtypes = []
         L.asp_host_last_error.restype = C.c_char_p
+        L.asp_format_id.argtypes = [C.c_void_p]
+        L.asp_format_id.restype = C.c_uint64
+        L.asp_search.argtypes = [C.c_void_p, C.POINTER(SearchOptions), TIME_FN, C.c_void_p, C.POINTER(C.c_void_p)]
+        L.asp_search.restype = C.c_int
+        L.asp_search_gpu.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SearchOptions), C.POINTER(C.c_void_p)]
+        L.asp_search_gpu.restype = C.c_int
+        L.asp_search_result_destroy.argtypes = [C.c_void_p]
+        L.asp_search_result_destroy.restype = None
+        L.asp_search_result_dense.argtypes = [C.c_void_p]
+        L.asp_search_result_dense.restype = C.c_char_p
+        L.asp_search_result_num_subs.argtypes = [C.c_void_p]
+        L.asp_search_result_num_subs.restype = C.c_int
+        for fn in (L.asp_search_result_sub_spec, L.asp_search_result_sub_name, L.asp_search_result_trial):
+            fn.argtypes = [C.c_void_p, C.c_int]
+            fn.restype = C.c_char_p
+        L.asp_search_result_sub_launch.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+        L.asp_search_result_sub_launch.restype = C.c_int
+        L.asp_search_result_ms.argtypes = [C.c_void_p]
+        L.asp_search_result_ms.restype = C.c_float
+        L.asp_search_result_num_trials.argtypes = [C.c_void_p]
+        L.asp_search_result_num_trials.restype = C.c_int
+        L.asp_search_candidates.argtypes = [C.c_uint64, C.c_uint64, C.c_double, C.c_int, C.c_int]
+        L.asp_search_candidates.restype = C.c_char_p
+        L.asp_search_derive_tblock.argtypes = [C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int64]
+        L.asp_search_derive_tblock.restype = C.c_int64
         _bound = True
     return L
 
@@ -157,12 +195,22 @@ class Matrix:
 class Format:
     """asp_format: one lowered template per sub-matrix."""
 
-    def __init__(self, handle):
+    def __init__(self, handle, owned: bool = True):
         self._h = handle
+        self._owned = owned
         L = _lib()
         self.n_subs = L.asp_format_num_subs(handle)
         self._descs = (capi.PlanDesc * self.n_subs)()
         _check(L.asp_format_plan_descs(handle, self._descs))
+
+    @staticmethod
+    def borrowed(handle) -> "Format":
+        """View of an asp_format that somebody else owns (a timing callback of asp_search)."""
+        return Format(C.c_void_p(handle) if isinstance(handle, int) else handle, owned=False)
+
+    @property
+    def id(self) -> int:
+        return int(_lib().asp_format_id(self._h))
 
     def plan_descs(self):
         return [self._descs[i] for i in range(self.n_subs)]
@@ -212,9 +260,9 @@ class Format:
         return capi.PlanGroup(ctx, self.plan_descs(), keepalive=self)
 
     def close(self):
-        if self._h:
+        if self._h and self._owned:
             _lib().asp_format_destroy(self._h)
-            self._h = C.c_void_p()
+        self._h = C.c_void_p()
 
     def __del__(self):
         try:

@@ -212,6 +212,14 @@ asp_status asp_multicast_store(const void *src, void *multicast_dst, size_t byte
 asp_status asp_time(asp_ctx *ctx, asp_plan *const *plans, int n_plans, int warmup, int reps, int zero_y,
                     double gflops_up_bound, float *ms_per_spmv, float *gflops);
 
+/* asp_search (asp_b200_host.h) with the GPU as the timer: every trial is uploaded once
+ * (asp_plan_group_create), its launch parameters are swept with asp_plan_set_launch, and asp_time
+ * measures it on the context's stream. `matrix`, `options` and `result` are the asp_matrix,
+ * asp_search_options and asp_search_result of asp_b200_host.h (void here so that this header stays
+ * independent of the host one). Replaces the reference's compile-and-run trial
+ * (part_execute_code_builder + execute_binary, executor.cc:6-260). */
+asp_status asp_search_gpu(asp_ctx *ctx, const void *matrix, const void *options, void **result);
+
 asp_status asp_synchronize(asp_ctx *ctx);
 const char *asp_status_str(asp_status s);
 /* text of the last CUDA error seen by this thread ("" if none) */

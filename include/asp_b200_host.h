@@ -64,6 +64,8 @@ asp_status asp_matrix_sub_rows(const asp_matrix *m, int sub, uint64_t *n_rows, u
 void asp_format_destroy(asp_format *f);
 
 int asp_format_num_subs(const asp_format *f);
+/* process-unique, never reused: lets a cache of uploaded plans tell formats apart after their addresses are recycled */
+uint64_t asp_format_id(const asp_format *f);
 /* the global row permutation (sorted_row_index, new -> old); *ptr == NULL when unsorted */
 asp_status asp_format_global_perm(const asp_format *f, const void **ptr, int *dtype, uint64_t *len);
 
@@ -87,6 +89,54 @@ double asp_format_padding_rate(const asp_format *f, int sub);
  * replicated. bounds gets parts + 1 entries, bounds[p] .. bounds[p + 1] is the row range of
  * part p; a row is never split. */
 asp_status asp_partition_rows_by_nnz(uint64_t n_rows, const int64_t *indptr, int parts, uint64_t *bounds);
+
+/* ---- the search loop (search_strategy.cc, whilte_list_path_impl.cc:3411-4579, default_auto_tuner.cc:449-2030) ----
+ *
+ * Enumerate-and-time over Operator Graphs: the dense-view strategies G1 (compress only), G2 (exponential
+ * row division) and G3 (coarse sort + exponential row division); per sub-matrix the whitelist strategies
+ * that its row statistics admit, each with a small node-parameter grid, one template and a sweep of launch
+ * parameters; points whose padded / true non-zeros exceed `padding_rate_up_bound` are skipped; then the
+ * whole matrix with the per-strip winners, and the fastest dense strategy wins. A trial costs one lowering
+ * and one call of `time_fn` instead of an nvcc compile and a run of a generated program. */
+typedef struct asp_search_options
+{
+    int32_t quick;              /* 1: one or two node-parameter points per strategy and a short launch sweep */
+    int32_t warmup, reps;       /* handed to time_fn */
+    int32_t max_subs;           /* row divisions that give more strips are abandoned (reference: 5) */
+    int32_t struggle_step_num;  /* < 0: time every candidate; else the stop rule of search_strategy.cc per strip */
+    double time_limit_s;        /* <= 0: none; wall-clock limit of one strip's sweep under the stop rule */
+    double padding_rate_up_bound; /* <= 0: the reference's 4.0 (global_config.json) */
+    void (*log_fn)(void *user, const char *line); /* may be NULL */
+    void *log_user;
+} asp_search_options;
+
+/* Times one SpMV over `fmt` (sub-matrices with the EMPTY template are skipped) with the given launch
+ * parameters per sub-matrix (arrays of asp_format_num_subs(fmt) entries; entries of EMPTY sub-matrices are
+ * ignored). Returns 0 and the milliseconds per SpMV, or non-zero when this point cannot run (the search
+ * moves on, as the reference does when a generated program fails). */
+typedef int (*asp_time_fn)(void *user, const asp_format *fmt, const int64_t *tblock_num, const int64_t *thread_num_in_block,
+                           const int64_t *thread_num_of_row_reduce, int warmup, int reps, float *ms_per_spmv);
+
+typedef struct asp_search_result asp_search_result;
+asp_status asp_search(const asp_matrix *m, const asp_search_options *opt, asp_time_fn time_fn, void *time_user, asp_search_result **out);
+void asp_search_result_destroy(asp_search_result *r);
+/* the winner: dense-view spec (lines as asp_dense_execute takes them), per sub-matrix the compressed-view
+ * lines ("sub <i> ..." incl. the template line, as asp_graph_execute takes them), its strategy name and launch */
+const char *asp_search_result_dense(const asp_search_result *r);
+int asp_search_result_num_subs(const asp_search_result *r);
+const char *asp_search_result_sub_spec(const asp_search_result *r, int sub);
+const char *asp_search_result_sub_name(const asp_search_result *r, int sub);
+asp_status asp_search_result_sub_launch(const asp_search_result *r, int sub, int64_t *thread_num_in_block, int64_t *thread_num_of_row_reduce);
+float asp_search_result_ms(const asp_search_result *r);
+/* every timed point, one text line each: "<dense> ; sub <i> ; <strategy> ; threads ; reduce ; ms ; padding" */
+int asp_search_result_num_trials(const asp_search_result *r);
+const char *asp_search_result_trial(const asp_search_result *r, int i);
+
+/* The strategies that apply to a sub-matrix with row non-zeros in [min, max] (mean avg), as text: one line
+ * per candidate, "<name> ; <template> ; <node>|<node>... ; <threads>:<reduce>,..." (what asp_search sweeps). */
+const char *asp_search_candidates(uint64_t min_row_nnz, uint64_t max_row_nnz, double avg_row_nnz, int is_sorted, int quick);
+/* launch shapes the reference derives instead of searching (default_auto_tuner.cc:465-498, 688-693) */
+int64_t asp_search_derive_tblock(int template_type, uint64_t n_tlb, uint64_t n_wlb, uint64_t n_blb, int64_t thread_num_in_block);
 
 /* text of the last error a host-side entry point reported on this thread */
 const char *asp_host_last_error(void);
