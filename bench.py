@@ -1,11 +1,16 @@
 """Benchmark of the SpMV hot path: y = A x over the machine-designed formats.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c4|c4s] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c4|c4s|c5] [--impl reference]
 
 A step is one SpMV over the whole matrix. The default workload is the 5-point Laplacian on a
 2048 x 2048 grid in fp64 (4,194,304 rows, 20,963,328 non-zeros); with N > 1 every rank owns a
 row block of that size of a 2048 x (2048 N) grid (weak scaling, x replicated, no collective on
-the data path). Prints ONE JSON line on rank 0.
+the data path). Prints ONE JSON line on rank 0. The graph is searched on the GPU (asp_search_gpu)
+unless --graph replays one from an earlier line or --spec names a single strategy.
+
+--workload c5 is the sharded graph case (strong scaling): R-MAT scale --scale generated on the GPUs,
+nnz-balanced row blocks, x replicated, one step = --iters repeated SpMVs whose results reach every
+rank through an NVLink multicast store (--exchange, --chunks, --balance: see their help).
 
 --impl reference times the CPU restatement of the reference's SpMV (oracle/csr_spmv.c, OpenMP
 over all host cores) on the same workload: the reference has no host SpMV of its own and its
