@@ -4,6 +4,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <stdexcept>
 #include <fstream>
 #include <map>
 #include <numeric>
@@ -563,6 +564,10 @@ void sep_thread_level_col_ell_with_padding(CompressedBlock &b, u64 tlb_size)
         blb_first[i + 1] = wlb_pad0[B.index.v[i + 1]];
     }
     const u64 n_tlb = wlb_tlb0[W.block_num], n_pad = wlb_pad0[W.block_num];
+    // a few long rows in an ELL-shaped strip multiply the storage: stop before materialising a
+    // format that no padding gate would let through (the search bound is 4x; 64x leaves room for
+    // callers with their own bound)
+    if (n_pad > 64 * std::max<u64>(b.col.size(), 1024)) throw std::length_error("padded size exceeds 64x the non-zeros of the sub-matrix");
     b.pad_col.assign(n_pad, 0);
     b.pad_val.es = es;
     b.pad_val.resize(n_pad);

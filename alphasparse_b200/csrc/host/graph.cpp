@@ -3,6 +3,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <stdexcept>
 #include <atomic>
 #include <map>
 #include <memory>
@@ -470,6 +471,10 @@ asp_status asp_graph_execute(const asp_matrix *in, const char *spec, asp_format 
     catch (const std::bad_alloc &)
     {
         return hfail(ASP_ERR_ALLOC, "host allocation failed");
+    }
+    catch (const std::length_error &e)
+    {
+        return hfail(ASP_ERR_UNSUPPORTED, std::string("graph rejected: ") + e.what());
     }
     return ASP_OK;
 }
