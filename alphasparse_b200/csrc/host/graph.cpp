@@ -14,6 +14,7 @@
 
 #include "../../../include/asp_b200_host.h"
 #include "format.hpp"
+#include "handles.hpp"
 
 using namespace asp::host;
 
@@ -23,27 +24,73 @@ static uint64_t next_format_id()
     return ++n;
 }
 
-struct asp_matrix
-{
-    std::unique_ptr<Matrix> m;
-};
+asp_format::asp_format() : id(next_format_id()) {}
 
-struct asp_format
+void asp_format::cache_from_matrix()
 {
-    uint64_t id = next_format_id(); // unique per process: addresses are reused, ids are not
-    std::unique_ptr<Matrix> m; // the transformed copy (owns the shared permutation)
-    std::vector<TemplateData> subs;
-    std::vector<std::vector<asp_array_desc>> descs;
-};
+    val_dt = m->val_dt;
+    n_rows = m->n_rows;
+    n_cols = m->n_cols;
+    perm = m->is_sorted ? m->sorted_row_index : nullptr;
+    perm_dt = m->perm_dt;
+    infos.assign(subs.size(), asp_sub_info());
+    for (size_t i = 0; i < subs.size(); i++)
+    {
+        const CompressedBlock &b = m->blocks[i];
+        asp_sub_info &o = infos[i];
+        o.min_row = b.min_row;
+        o.max_row = b.max_row;
+        o.min_col = b.min_col;
+        o.max_col = b.max_col;
+        o.begin_coo = b.begin_coo;
+        o.end_coo = b.end_coo;
+        o.n_blb = b.blb.block_num;
+        o.n_wlb = b.wlb.block_num;
+        o.n_tlb = b.tlb.block_num;
+        o.template_type = subs[i].template_type;
+        o.n_arrays = (int32_t)subs[i].arrays.size();
+    }
+}
 
-namespace
+void asp_format::build_descs()
 {
-thread_local std::string g_host_error;
-asp_status hfail(asp_status s, const std::string &msg)
+    descs.assign(subs.size(), std::vector<asp_array_desc>());
+    for (size_t i = 0; i < subs.size(); i++)
+    {
+        for (const TemplateArray &a : subs[i].arrays)
+        {
+            asp_array_desc d;
+            memset(&d, 0, sizeof(d));
+            d.role = a.role;
+            d.dtype = a.dt;
+            d.host_ptr = a.data();
+            d.len = a.len;
+            d.compress = a.comp.kind;
+            d.coef = a.comp.coef;
+            d.icpt = a.comp.icpt;
+            d.cycle = a.comp.cycle;
+            d.n_branch = (int32_t)a.comp.val.size();
+            for (size_t k = 0; k < a.comp.val.size() && k < ASP_MAX_BRANCH; k++)
+            {
+                d.branch_lo[k] = a.comp.lo[k];
+                d.branch_hi[k] = a.comp.hi[k];
+                d.branch_val[k] = a.comp.val[k];
+            }
+            descs[i].push_back(d);
+        }
+    }
+}
+
+static thread_local std::string g_host_error;
+asp_status asp_host_fail(asp_status s, const std::string &msg)
 {
     g_host_error = msg;
     return s;
 }
+
+namespace
+{
+asp_status hfail(asp_status s, const std::string &msg) { return asp_host_fail(s, msg); }
 
 struct SubSpec
 {
@@ -440,32 +487,8 @@ asp_status asp_graph_execute(const asp_matrix *in, const char *spec, asp_format 
             std::vector<uint8_t>().swap(b.val.b);
             std::vector<u64>().swap(b.tlb.first_row.v);
         }
-        // C-ABI descriptors over the template arrays
-        F->descs.resize(nsub);
-        for (size_t i = 0; i < nsub; i++)
-        {
-            for (const TemplateArray &a : F->subs[i].arrays)
-            {
-                asp_array_desc d;
-                memset(&d, 0, sizeof(d));
-                d.role = a.role;
-                d.dtype = a.dt;
-                d.host_ptr = a.data();
-                d.len = a.len;
-                d.compress = a.comp.kind;
-                d.coef = a.comp.coef;
-                d.icpt = a.comp.icpt;
-                d.cycle = a.comp.cycle;
-                d.n_branch = (int32_t)a.comp.val.size();
-                for (size_t k = 0; k < a.comp.val.size() && k < ASP_MAX_BRANCH; k++)
-                {
-                    d.branch_lo[k] = a.comp.lo[k];
-                    d.branch_hi[k] = a.comp.hi[k];
-                    d.branch_val[k] = a.comp.val[k];
-                }
-                F->descs[i].push_back(d);
-            }
-        }
+        F->build_descs();
+        F->cache_from_matrix();
         *out = F.release();
     }
     catch (const std::bad_alloc &)
@@ -486,11 +509,11 @@ uint64_t asp_format_id(const asp_format *f) { return f ? f->id : 0; }
 asp_status asp_format_global_perm(const asp_format *f, const void **ptr, int *dtype, uint64_t *len)
 {
     if (!f || !ptr || !dtype || !len) return hfail(ASP_ERR_INVALID_ARG, "NULL argument");
-    if (f->m->is_sorted)
+    if (f->perm)
     {
-        *ptr = f->m->sorted_row_index->data();
-        *dtype = f->m->perm_dt;
-        *len = f->m->n_rows;
+        *ptr = f->perm->data();
+        *dtype = f->perm_dt;
+        *len = f->n_rows;
     }
     else
     {
@@ -504,19 +527,7 @@ asp_status asp_format_global_perm(const asp_format *f, const void **ptr, int *dt
 asp_status asp_format_sub_info(const asp_format *f, int sub, asp_sub_info *out)
 {
     if (!f || !out || sub < 0 || sub >= (int)f->subs.size()) return hfail(ASP_ERR_INVALID_ARG, "bad sub-matrix id");
-    const CompressedBlock &b = f->m->blocks[sub];
-    const TemplateData &t = f->subs[sub];
-    out->min_row = b.min_row;
-    out->max_row = b.max_row;
-    out->min_col = b.min_col;
-    out->max_col = b.max_col;
-    out->begin_coo = b.begin_coo;
-    out->end_coo = b.end_coo;
-    out->n_blb = b.blb.block_num;
-    out->n_wlb = b.wlb.block_num;
-    out->n_tlb = b.tlb.block_num;
-    out->template_type = t.template_type;
-    out->n_arrays = (int32_t)t.arrays.size();
+    *out = f->infos[sub];
     return ASP_OK;
 }
 
@@ -529,9 +540,9 @@ asp_status asp_format_plan_descs(const asp_format *f, asp_plan_desc *descs)
         asp_plan_desc &d = descs[i];
         memset(&d, 0, sizeof(d));
         d.template_type = t.template_type;
-        d.val_dtype = f->m->val_dt;
-        d.n_rows = f->m->n_rows;
-        d.n_cols = f->m->n_cols;
+        d.val_dtype = f->val_dt;
+        d.n_rows = f->n_rows;
+        d.n_cols = f->n_cols;
         d.first_row = t.first_row;
         d.first_col = t.first_col;
         d.true_nnz = t.true_nnz;

@@ -22,7 +22,7 @@ HOST_EXPORTS = [
     "asp_matrix_from_csr", "asp_matrix_from_coo_file", "asp_matrix_destroy", "asp_matrix_rows", "asp_matrix_cols",
     "asp_matrix_nnz", "asp_graph_execute", "asp_format_destroy", "asp_format_num_subs", "asp_format_global_perm",
     "asp_format_sub_info", "asp_format_plan_descs", "asp_format_padding_rate", "asp_host_last_error",
-    "asp_dense_execute", "asp_matrix_num_subs", "asp_matrix_sub_rows", "asp_partition_rows_by_nnz", "asp_format_id",
+    "asp_dense_execute", "asp_matrix_num_subs", "asp_matrix_sub_rows", "asp_partition_rows_by_nnz", "asp_format_id", "asp_format_save", "asp_format_load",
     "asp_search", "asp_search_result_destroy", "asp_search_result_dense", "asp_search_result_num_subs", "asp_search_result_sub_spec",
     "asp_search_result_sub_name", "asp_search_result_sub_launch", "asp_search_result_ms", "asp_search_result_num_trials",
     "asp_search_result_trial", "asp_search_candidates", "asp_search_derive_tblock",
@@ -80,6 +80,10 @@ def _lib():
         L.asp_host_last_error.restype = C.c_char_p
         L.asp_format_id.argtypes = [C.c_void_p]
         L.asp_format_id.restype = C.c_uint64
+        L.asp_format_save.argtypes = [C.c_void_p, C.c_char_p]
+        L.asp_format_save.restype = C.c_int
+        L.asp_format_load.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+        L.asp_format_load.restype = C.c_int
         L.asp_search.argtypes = [C.c_void_p, C.POINTER(SearchOptions), TIME_FN, C.c_void_p, C.POINTER(C.c_void_p)]
         L.asp_search.restype = C.c_int
         L.asp_search_gpu.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(SearchOptions), C.POINTER(C.c_void_p)]
@@ -211,6 +215,16 @@ class Format:
     @property
     def id(self) -> int:
         return int(_lib().asp_format_id(self._h))
+
+    def save(self, path: str) -> None:
+        """asp_format_save: everything needed to upload this format later, in one binary file."""
+        _check(_lib().asp_format_save(self._h, path.encode()))
+
+    @staticmethod
+    def load(path: str) -> "Format":
+        h = C.c_void_p()
+        _check(_lib().asp_format_load(path.encode(), C.byref(h)))
+        return Format(h)
 
     def plan_descs(self):
         return [self._descs[i] for i in range(self.n_subs)]

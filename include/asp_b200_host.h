@@ -81,6 +81,14 @@ asp_status asp_format_sub_info(const asp_format *f, int sub, asp_sub_info *out);
  * asp_format_destroy(). `descs` must have room for asp_format_num_subs() entries. */
 asp_status asp_format_plan_descs(const asp_format *f, asp_plan_desc *descs);
 
+/* Binary file of a lowered format (all template arrays, closed forms, scalars, launch parameters and the row
+ * permutation): tune once, then asp_format_load() + asp_format_plan_descs() + asp_plan_group_create() without
+ * executing the Operator Graph again. Counterpart of the reference's directory of data files next to its
+ * generated program (store_code_builder_data, code_builder.cc:2429-2517). A loaded format answers every
+ * asp_format_* query like the one that was saved. */
+asp_status asp_format_save(const asp_format *f, const char *path);
+asp_status asp_format_load(const char *path, asp_format **out);
+
 /* per-point padding rate the tuner gates on (PADDING_RATE_UP_BOUND): padded nnz / true nnz */
 double asp_format_padding_rate(const asp_format *f, int sub);
 

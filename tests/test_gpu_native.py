@@ -110,3 +110,20 @@ def test_sell_strips_wider_than_255_elements(asp_ctx, mats, dense):
     m, x = M.rmat(11, 8, seed=4)
     assert m.row_lengths().max() > 255
     run(asp_ctx, m, x, dense + "\nsub all row_padding 128 1\nsub all blb_row_evenly 128\nsub all tlb_row\nsub all template K2", f"wide SELL {dense!r}")
+
+
+def test_format_loaded_from_its_file_runs_like_the_original(asp_ctx, mats, tmp_path):
+    from alphasparse_b200.graph import Format
+
+    m, x = mats["mixed_f32"]
+    fmt = Matrix.from_csr(m).execute(specs.full_spec("S8_K7", "dense sort 1\ndense compress"))
+    path = str(tmp_path / "mixed.asp")
+    fmt.save(path)
+    back = Format.load(path)
+    g0, g1 = fmt.upload(asp_ctx), back.upload(asp_ctx)
+    y0, y1 = g0.spmv_host(x), g1.spmv_host(x)
+    y_ref, scale = refdump.csr_ref(m, x)
+    refdump.assert_y(y1, y_ref, scale, m.values.dtype, "loaded format")
+    assert np.array_equal(y0, y1) or refdump.rel_err(y1, y0.astype(np.float64), scale) <= 1e-6  # atomics may reorder sums
+    for o in (g0, g1, fmt, back):
+        o.close()
