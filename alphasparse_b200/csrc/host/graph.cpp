@@ -200,6 +200,21 @@ bool apply_dense_node(Matrix &m, const std::vector<std::string> &tok, bool &comp
         if (lo == 0 || hi < lo || rate < 2) return err = "bad dense rowdiv_exp parameters", false;
         dense_row_div(m, row_div_position_exponential(m, lo, hi, rate));
     }
+    else if (tok[0] == "rowdiv")
+    {
+        // DENSE_ROW_DIV with explicit positions (exe_dense_row_div_param_t: first row of every strip,
+        // closed by the row count): "rowdiv p1 p2 ..." cuts [0, p1), [p1, p2), ..., [pk, n_rows)
+        if (tok.size() < 2 || m.is_blocked) return err = "bad dense rowdiv", false;
+        std::vector<u64> pos(1, 0);
+        for (size_t i = 1; i < tok.size(); i++)
+        {
+            const u64 p = strtoull(tok[i].c_str(), nullptr, 10);
+            if (p <= pos.back() || p >= m.n_rows) return err = "dense rowdiv positions must increase inside (0, rows)", false;
+            pos.push_back(p);
+        }
+        pos.push_back(m.n_rows);
+        dense_row_div(m, pos);
+    }
     else if (tok[0] == "compress")
     {
         compress_dense_view(m);

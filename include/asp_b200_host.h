@@ -34,6 +34,7 @@ uint64_t asp_matrix_nnz(const asp_matrix *m);
  * `spec` is a line-oriented description of the graph, one node per line:
  *   dense sort <step>                       DENSE_ROW_COARSE_SORT (fixed-step strategy)
  *   dense rowdiv_exp <low> <high> <rate>    DENSE_ROW_DIV (exponential row-nnz ranges)
+ *   dense rowdiv <p1> <p2> ...               DENSE_ROW_DIV at explicit rows: strips [0,p1), [p1,p2), ..., [pk,rows)
  *   dense compress                          COMPRESS (implied when absent)
  *   sub <id|all> row_padding <mult> <len>   COMPRESSED_ROW_PADDING
  *   sub <id|all> blb_row_evenly <rows> | blb_row_nnz <nnz> | blb_col_fixed <nnz>

@@ -56,3 +56,23 @@ def test_random_matrices_with_empty_and_long_rows(seed, n, tail, spec, sort):
     m, x = M.from_row_lengths(lengths, n, seed=seed, dtype=np.float64)
     dense = "dense sort 1\ndense compress" if sort else "dense compress"
     check(m, x, specs.full_spec(spec, dense), f"seed {seed} n {n} {spec} sort {sort}")
+
+
+def test_explicit_row_division_with_a_template_per_strip():
+    # DENSE_ROW_DIV with explicit positions; strips without non-zeros are dropped as in the reference
+    m, x = M.uniform_random(900, 7, seed=9, dtype=np.float64)
+    hm = Matrix.from_csr(m)
+    cm = hm.dense("dense rowdiv 100 450 451\ndense compress")
+    assert cm.n_subs == 4
+    assert [cm.sub_rows(i)[0] for i in range(4)] == [100, 350, 1, 449]
+    spec = ("dense rowdiv 100 450 451\ndense compress\n" + "sub 0 tlb_nnz 4\nsub 0 template K9\n" + "sub 1 row_padding 32 1\nsub 1 tlb_row\nsub 1 template K3\n"
+            + "sub 2 template EMPTY\n" + "sub 3 blb_row_nnz 512\nsub 3 tlb_col_fixed 2\nsub 3 template K6")
+    fmt = hm.execute(spec)
+    y = plan_interp.interpret(NativeManifest(fmt, m.n_rows), x)
+    y_ref, scale = refdump.csr_ref(m, x)
+    keep = np.ones(m.n_rows, bool)
+    keep[450] = False  # the strip given the EMPTY template is not computed
+    assert refdump.rel_err(y[keep], y_ref[keep], scale[keep]) <= 1e-12 and y[450] == 0
+    for bad in ("dense rowdiv 0 10\ndense compress", "dense rowdiv 500 400\ndense compress", "dense rowdiv 900\ndense compress"):
+        with pytest.raises(Exception):
+            hm.dense(bad)
