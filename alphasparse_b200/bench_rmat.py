@@ -9,7 +9,7 @@ import numpy as np
 import torch
 
 from . import capi, matrices_gpu, tuner
-from .dist import ShardedSpmv, balanced_bounds_from_degrees
+from .dist import ShardedSpmv, all_ranks_ok, balanced_bounds_from_degrees
 from .graph import partition_rows_by_nnz
 
 # One CSR5-like kernel over the block. The coarse row sort with a bin wider than any row is a stable
@@ -80,6 +80,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
     else:
         desc = DEFAULT_GRAPH
     fmts, groups, chunks = [], [], []
+    build_error = None
     # most rows first: the exchange of the last chunk is the only one no kernel hides
     order = sorted(range(n_chunks), key=lambda c: -(int(cuts[c + 1]) - int(cuts[c])))
     if args.chunk_shape == "geometric":
@@ -94,7 +95,11 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
             chunks.append((fz, lo, hi))
             continue
         mc = m.row_slice(lo, hi) if n_chunks > 1 else m
-        f, g = tuner.build(ctx, mc, desc)
+        try:
+            f, g = tuner.build(ctx, mc, desc)
+        except Exception as e:  # reported to every rank below, before anybody enters a collective
+            build_error = e
+            break
         fmts.append(f)
         groups.append(g)
 
@@ -103,6 +108,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
 
         chunks.append((fn, lo, hi))
         del mc
+    all_ranks_ok(build_error is None, f"lowering / upload of the row block ({build_error})", dev)
     search_s = time.perf_counter() - t0
     stream = torch.cuda.ExternalStream(ctx.stream)
     x0 = matrices_gpu.rmat_x(scale, seed, dev)

@@ -174,6 +174,21 @@ class ShardedSpmv:
         return a
 
 
+def all_ranks_ok(ok: bool, what: str, device="cpu", group=None) -> None:
+    """Host-side agreement before the ranks enter a collective phase: every rank reports whether its
+    own set-up (generation, lowering, upload) succeeded, and ALL ranks raise if any of them failed, so
+    that a rank with an error never leaves the others waiting inside a collective. Call it with the
+    local outcome on every rank (also on the failing one)."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        if not ok:
+            raise RuntimeError(f"{what} failed on this rank")
+        return
+    t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+    if int(t.item()) == 0:
+        raise RuntimeError(f"{what} failed on " + ("this rank" if not ok else "another rank") + "; all ranks stop before the exchange")
+
+
 def balanced_bounds_from_degrees(deg: np.ndarray, parts: int) -> np.ndarray:
     """Row bounds with about sum(deg) / parts non-zeros per part, from per-row counts."""
     from .graph import partition_rows_by_nnz

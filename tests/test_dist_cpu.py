@@ -15,7 +15,7 @@ import torch.multiprocessing as mp
 
 import refdump
 from alphasparse_b200 import matrices as M
-from alphasparse_b200.dist import ShardedSpmv, balanced_bounds_from_degrees
+from alphasparse_b200.dist import ShardedSpmv, all_ranks_ok, balanced_bounds_from_degrees
 from alphasparse_b200.graph import partition_rows_by_nnz
 
 
@@ -92,3 +92,42 @@ def test_sharded_repeated_spmv_matches_single_rank(world, n_chunks, tmp_path):
         sl = np.load(tmp_path / f"slice_{r}.npy")
         assert np.array_equal(sl, first[bounds[r] : bounds[r + 1]])
         assert np.array_equal(np.load(tmp_path / f"final_{r}.npy"), ref)
+
+
+def _failing_worker(rank, world, port, out_dir):
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    ok = True
+    try:
+        if rank == 1:
+            raise ValueError("injected: this rank cannot build its block")  # the failure is made on the host
+    except ValueError:
+        ok = False
+    outcome = "entered the exchange"
+    try:
+        all_ranks_ok(ok, "set-up")
+        # only reached when every rank is fine: the collective phase
+        t = torch.ones(4)
+        dist.all_reduce(t)
+    except RuntimeError as e:
+        outcome = "stopped: " + str(e)
+    with open(os.path.join(out_dir, f"outcome_{rank}.txt"), "w") as fh:
+        fh.write(outcome)
+    dist.destroy_process_group()
+
+
+def test_a_failing_rank_stops_all_ranks_before_the_collective(tmp_path):
+    world = 3
+    mp.spawn(_failing_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    outcomes = [open(tmp_path / f"outcome_{r}.txt").read() for r in range(world)]
+    assert all(o.startswith("stopped:") for o in outcomes), outcomes
+    assert "this rank" in outcomes[1] and "another rank" in outcomes[0] and "another rank" in outcomes[2]
+
+
+def test_all_ranks_ok_without_a_process_group():
+    all_ranks_ok(True, "nothing")
+    with pytest.raises(RuntimeError):
+        all_ranks_ok(False, "single process")
