@@ -705,6 +705,7 @@ bool init_k9(const Matrix &m, const CompressedBlock &b, bool with_warp_reduce, T
     const u64 n = row.size(), T = n / S, Wn = T / 32;
     // row-start flags (the first non-zero of every warp always starts a sum), first rows per warp
     std::vector<uint8_t> flag(n);
+#pragma omp parallel for schedule(static) if (n > (1u << 20))
     for (u64 i = 0; i < n; i++) flag[i] = (i % wn == 0) ? 1 : (row[i] != row[i - 1]);
     std::vector<u64> wfirst(Wn);
     for (u64 w = 0; w < Wn; w++) wfirst[w] = row[w * wn];
@@ -779,6 +780,7 @@ bool init_k9(const Matrix &m, const CompressedBlock &b, bool with_warp_reduce, T
     // values / columns: element k of lane l of warp w at w*32*S + k*32 + l
     const int cb = dtype_bytes(b.col_dt), es = b.val.es;
     std::vector<uint8_t> ocol(n * cb, 0), oval(n * es, 0);
+#pragma omp parallel for schedule(static) if (n > (1u << 20))
     for (u64 i = 0; i < n; i++)
     {
         const u64 tl = i / S, k = i % S, w = tl / 32, lane = tl % 32;
