@@ -34,7 +34,11 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
         dist.all_reduce(deg)
     # "nnz": equal non-zeros per rank; "bytes": equal algorithmic bytes, i.e. a row weighs as much
     # as one non-zero (4 B of y + 4 B of row structure against 4 B value + 4 B index)
-    bounds = balanced_bounds_from_degrees((deg + (1 if args.balance == "bytes" else 0)).cpu().numpy(), world)
+    row_weight = {"nnz": 0.0, "bytes": 1.0}.get(args.balance)
+    if row_weight is None:
+        row_weight = float(args.balance)  # a row weighs this many non-zeros
+    # (weights are scaled by 8 so that fractional row weights survive the integer prefix sums)
+    bounds = balanced_bounds_from_degrees((deg * 8 + int(round(row_weight * 8))).cpu().numpy(), world)
     del deg
     r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
     # pass 2: this rank's row block (global columns), duplicates merged
