@@ -95,26 +95,28 @@ def uniform_random(n: int = 4096, mean_nnz: float = 16.0, seed: int = 0, dtype=n
     return CsrMatrix(n, n, indptr, cols, vals), x
 
 
-def laplacian_2d(grid: int = 2048, seed: int = 1, dtype=np.float64, grid_y: int | None = None):
+def laplacian_2d(grid: int = 2048, seed: int = 1, dtype=np.float64, grid_y: int | None = None, rows: tuple | None = None):
     """Config 2: 5-point Laplacian on a grid x grid_y mesh, natural ordering, diagonal 4,
-    neighbours -1; x ~ U[-1,1]. Row i = iy*grid + ix."""
+    neighbours -1; x ~ U[-1,1]. Row i = iy*grid + ix. With rows=(r0, r1) only that row block is
+    built (global column indices, the full x): what one rank of a sharded run needs."""
     gx = grid
     gy = grid if grid_y is None else grid_y
     n = gx * gy
-    i = np.arange(n, dtype=np.int64)
+    r0, r1 = (0, n) if rows is None else (int(rows[0]), int(rows[1]))
+    i = np.arange(r0, r1, dtype=np.int64)
     ix = i % gx
     iy = i // gx
     # candidate neighbours in ascending column order: i-gx, i-1, i, i+1, i+gx
     cand = np.stack([i - gx, i - 1, i, i + 1, i + gx], axis=1)
-    ok = np.stack([iy > 0, ix > 0, np.ones(n, bool), ix < gx - 1, iy < gy - 1], axis=1)
+    ok = np.stack([iy > 0, ix > 0, np.ones(i.shape[0], bool), ix < gx - 1, iy < gy - 1], axis=1)
     val = np.array([-1.0, -1.0, 4.0, -1.0, -1.0], dtype=dtype)
     lengths = ok.sum(axis=1).astype(np.int64)
     indptr = _from_lengths(lengths)
     cols = cand[ok].astype(np.uint32)
-    vals = np.broadcast_to(val, (n, 5))[ok].astype(dtype)
+    vals = np.broadcast_to(val, (i.shape[0], 5))[ok].astype(dtype)
     rng = np.random.default_rng(seed)
     x = rng.uniform(-1.0, 1.0, size=n).astype(dtype)
-    return CsrMatrix(n, n, indptr, cols, vals), x
+    return CsrMatrix(r1 - r0, n, indptr, cols, vals), x
 
 
 def power_law(n: int = 8_388_608, exponent: float = 2.1, cap: int = 500_000, seed: int = 2, dtype=np.float32):

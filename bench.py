@@ -306,12 +306,8 @@ def main():
     desc, gen = WORKLOADS[args.workload]
     if args.workload == "c2" and world > 1:
         # weak scaling: this rank's row block of the 2048 x (2048*world) grid, x replicated
-        full_rows = 2048 * 2048 * world
-        mfull, xfull = matrices.laplacian_2d(2048, 1, grid_y=2048 * world)
         r0 = rank * 2048 * 2048
-        m = mfull.row_slice(r0, r0 + 2048 * 2048)
-        x = xfull
-        del mfull
+        m, x = matrices.laplacian_2d(2048, 1, grid_y=2048 * world, rows=(r0, r0 + 2048 * 2048))
     else:
         m, x = gen()
     log = (lambda s: print(f"[rank {rank}] {s}", file=sys.stderr)) if args.verbose else None

@@ -49,3 +49,13 @@ def test_sell_tlb_size_array_is_wide_enough_for_its_largest_entry():
     arr = fmt.arrays(0)["thread_block_size_in_block"][0]
     assert arr.dtype == np.uint16 and int(arr.max()) == int(lens.max())
     fmt.close()
+
+
+def test_laplacian_row_block_equals_the_slice_of_the_whole_grid():
+    # what each rank of the weak-scaling run builds: its rows only, global columns, the full x
+    whole, x = M.laplacian_2d(48, 1, grid_y=48 * 3)
+    for r in range(3):
+        blk, xb = M.laplacian_2d(48, 1, grid_y=48 * 3, rows=(r * 48 * 48, (r + 1) * 48 * 48))
+        ref = whole.row_slice(r * 48 * 48, (r + 1) * 48 * 48)
+        assert (blk.n_rows, blk.n_cols) == (ref.n_rows, ref.n_cols) and np.array_equal(x, xb)
+        assert np.array_equal(blk.indptr, ref.indptr) and np.array_equal(blk.indices, ref.indices) and np.array_equal(blk.values, ref.values)
