@@ -319,6 +319,29 @@ asp_status asp_search(const asp_matrix *m, const asp_search_options *opt_, asp_t
                 asp_sub_info info;
                 if (asp_format_sub_info(f.get(), sub, &info) != ASP_OK) continue;
                 const int tid = template_id(cand.templ);
+                if (opt.prune_gbs > 0 && have)
+                {
+                    // sound pruning: the kernel has to read every byte of the format at least once
+                    std::vector<asp_plan_desc> descs(n);
+                    uint64_t bytes = 0;
+                    if (asp_format_plan_descs(f.get(), descs.data()) == ASP_OK)
+                        for (int a = 0; a < descs[sub].n_arrays; a++)
+                        {
+                            const asp_array_desc &ad = descs[sub].arrays[a];
+                            if (ad.compress != ASP_COMPRESS_NONE) continue; // replaced by a closed form: never read
+                            static const uint64_t es[] = {1, 2, 4, 8, 4, 8};    // asp_dtype order: u8 u16 u32 u64 f32 f64
+                            bytes += ad.len * es[ad.dtype < 6 ? ad.dtype : 2];
+                        }
+                    const uint64_t min_bytes = opt.prune_min_bytes ? opt.prune_min_bytes : (256ull << 20);
+                    const double bound_ms = (double)bytes / (opt.prune_gbs * 1e6);
+                    if (bytes >= min_bytes && bound_ms > bestp.ms)
+                    {
+                        char buf[256];
+                        snprintf(buf, sizeof buf, "  sub %d %s: not timed, %.0f MB cannot be read in under %.1f us", sub, cand.name.c_str(), bytes * 1e-6, bestp.ms * 1e3);
+                        log(buf);
+                        continue;
+                    }
+                }
                 for (const Launch &l : cand.launches)
                 {
                     std::vector<int64_t> tb(n, 1), th(n, 32), rd(n, 1);

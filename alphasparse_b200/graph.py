@@ -36,7 +36,8 @@ TIME_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.P
 class SearchOptions(C.Structure):
     """asp_search_options"""
     _fields_ = [("quick", C.c_int32), ("warmup", C.c_int32), ("reps", C.c_int32), ("max_subs", C.c_int32), ("struggle_step_num", C.c_int32),
-                ("time_limit_s", C.c_double), ("padding_rate_up_bound", C.c_double), ("log_fn", LOG_FN), ("log_user", C.c_void_p)]
+                ("time_limit_s", C.c_double), ("padding_rate_up_bound", C.c_double), ("prune_gbs", C.c_double), ("prune_min_bytes", C.c_uint64),
+                ("log_fn", LOG_FN), ("log_user", C.c_void_p)]
 
 _bound = False
 

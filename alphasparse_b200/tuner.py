@@ -84,13 +84,14 @@ def set_launch(fmt: Format, group: capi.PlanGroup, sub: int, threads: int, reduc
     group.set_launch(sub, derive_tblock(t, info.n_tlb, info.n_wlb, info.n_blb, threads), threads, reduce)
 
 
-def _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log):
+def _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs=0.0, prune_min_bytes=0):
     opt = graph.SearchOptions()
     opt.quick = int(bool(quick))
     opt.warmup, opt.reps, opt.max_subs = int(warmup), int(reps), int(max_subs)
     opt.struggle_step_num = -1 if struggle_step_num is None else int(struggle_step_num)
     opt.time_limit_s = 0.0 if time_limit_s is None else float(time_limit_s)
     opt.padding_rate_up_bound = PADDING_RATE_UP_BOUND
+    opt.prune_gbs, opt.prune_min_bytes = float(prune_gbs), int(prune_min_bytes)
     cb = graph.LOG_FN(lambda user, line: log(line.decode())) if log else graph.LOG_FN()
     opt.log_fn = cb
     return opt, cb  # the callback object must outlive the call
@@ -119,12 +120,14 @@ def _result(res_handle):
 
 
 def search(ctx: capi.Context, m: CsrMatrix, quick: bool = True, warmup: int = 2, reps: int = 10, log=None, max_subs: int = 5,
-           struggle_step_num: int | None = None, time_limit_s: float | None = None):
+           struggle_step_num: int | None = None, time_limit_s: float | None = None, prune_gbs: float = 0.0):
     """Full search on the GPU of `ctx` (asp_search_gpu). Returns (Format, PlanGroup, trials,
     description of the winning graph). With `struggle_step_num` and / or `time_limit_s` every
-    sub-matrix sweep runs under the reference's stop rule; by default every candidate is timed."""
+    sub-matrix sweep runs under the reference's stop rule; by default every candidate is timed.
+    `prune_gbs` > 0 (an upper bound of the memory bandwidth in GB/s) skips candidates whose format
+    cannot be read in the best time found so far."""
     hm = Matrix.from_csr(m)
-    opt, keep = _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log)
+    opt, keep = _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs)
     res = C.c_void_p()
     graph._check(graph._lib().asp_search_gpu(ctx.handle, hm._h, C.byref(opt), C.byref(res)))
     del keep
@@ -135,12 +138,12 @@ def search(ctx: capi.Context, m: CsrMatrix, quick: bool = True, warmup: int = 2,
 
 
 def search_with_timer(m: CsrMatrix, time_fn, quick: bool = True, warmup: int = 2, reps: int = 10, log=None, max_subs: int = 5,
-                      struggle_step_num: int | None = None, time_limit_s: float | None = None):
+                      struggle_step_num: int | None = None, time_limit_s: float | None = None, prune_gbs: float = 0.0, prune_min_bytes: int = 0):
     """asp_search with a caller-supplied timer `time_fn(fmt: Format, tblock, threads, reduce) -> ms or
     None` (None: the point cannot run). No GPU involved: used to test the loop against a model.
     Returns (description, trials, ms of the winner)."""
     hm = Matrix.from_csr(m)
-    opt, keep = _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log)
+    opt, keep = _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs, prune_min_bytes)
 
     def cb(user, fmt_handle, tb, th, rd, w, r, ms_out):
         view = Format.borrowed(fmt_handle)

@@ -273,6 +273,7 @@ def main():
     ap.add_argument("--spec", default=None, help="run exactly this compressed-view graph (name from the candidate list)")
     ap.add_argument("--threads", type=int, default=0, help="with --spec: thread_num_in_block")
     ap.add_argument("--graph", default=None, help="skip the search: a bench JSON line file (its config.graph is used) or the graph JSON itself")
+    ap.add_argument("--prune-gbs", type=float, default=0.0, help="search: skip candidates whose format cannot be read in the best time so far at this bandwidth (GB/s, an upper bound such as 8000); 0 = time everything")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
@@ -339,7 +340,7 @@ def main():
         fmt, group = tuner.build(ctx, m, graph_desc)
         trials = []
     else:
-        fmt, group, trials, graph_desc = tuner.search(ctx, m, quick=not args.full_search, log=log)
+        fmt, group, trials, graph_desc = tuner.search(ctx, m, quick=not args.full_search, log=log, prune_gbs=args.prune_gbs)
     search_s = time.perf_counter() - t_s
     padding_rate = max(fmt.padding_rate(i) for i in range(fmt.n_subs))
 

@@ -115,6 +115,10 @@ typedef struct asp_search_options
     int32_t struggle_step_num;  /* < 0: time every candidate; else the stop rule of search_strategy.cc per strip */
     double time_limit_s;        /* <= 0: none; wall-clock limit of one strip's sweep under the stop rule */
     double padding_rate_up_bound; /* <= 0: the reference's 4.0 (global_config.json) */
+    double prune_gbs;           /* > 0: a point whose format bytes / prune_gbs (an upper bound of the memory bandwidth, GB/s)
+                                 * already exceed the best time of its strip is not timed: it cannot win. Only applied to
+                                 * formats of at least prune_min_bytes (cache-resident ones can beat the memory bound). */
+    uint64_t prune_min_bytes;   /* 0: 256 MiB */
     void (*log_fn)(void *user, const char *line); /* may be NULL */
     void *log_user;
 } asp_search_options;

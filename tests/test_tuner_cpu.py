@@ -113,3 +113,20 @@ def test_stop_rule_ends_a_sweep_that_no_longer_improves():
     assert all(len(v) <= 7 for v in per_dense.values()) and len(trials) < len(all_trials)
     desc3, trials3, _ = tuner.search_with_timer(m, lambda f, tb, th, rd: 1.0, struggle_step_num=3)
     assert len(trials) < len(trials3) <= len(all_trials)
+
+
+def test_bandwidth_bound_pruning_skips_only_points_that_cannot_win():
+    m, _ = M.uniform_random(3000, 12, seed=6)
+    timer = model_timer()  # ms = padded non-zeros * 1e-6: "1 non-zero per nanosecond"
+    desc, trials, ms = tuner.search_with_timer(m, timer)
+    logs = []
+    # 12 bytes per fp32 non-zero at the model's speed would be 12 GB/s; with an upper bound of 6 GB/s a format
+    # must be smaller than half the best one to be timed at all, so that nearly everything after the first point is skipped
+    d2, t2, ms2 = tuner.search_with_timer(m, timer, prune_gbs=6.0, prune_min_bytes=1, log=logs.append)
+    assert len(t2) < len(trials) and any("not timed" in l for l in logs)
+    # a generous bound (1000 GB/s) prunes nothing and finds the same winner
+    d3, t3, ms3 = tuner.search_with_timer(m, timer, prune_gbs=1000.0, prune_min_bytes=1)
+    assert len(t3) == len(trials) and d3 == desc and ms3 == ms
+    # formats below the size threshold are never pruned (cache-resident kernels beat the memory bound)
+    d4, t4, _ = tuner.search_with_timer(m, timer, prune_gbs=6.0)
+    assert len(t4) == len(trials) and d4 == desc
