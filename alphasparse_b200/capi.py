@@ -56,8 +56,8 @@ class PlanDesc(C.Structure):
 
 
 EXPORTS = [
-    "asp_ctx_create", "asp_multicast_store", "asp_probe_gather", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_destroy",
-    "asp_plan_set_launch", "asp_plan_format_bytes", "asp_plan_launches", "asp_spmv", "asp_spmv_host", "asp_time",
+    "asp_ctx_create", "asp_multicast_store", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_descs_validate", "asp_plan_destroy",
+    "asp_plan_set_launch", "asp_plan_get_launch", "asp_plan_set_tuning", "asp_plan_format_bytes", "asp_plan_launches", "asp_spmv", "asp_spmv_host", "asp_time",
     "asp_synchronize", "asp_status_str", "asp_last_error", "asp_built_for_sm100a", "asp_spmv_host_static",
     "asp_static_stage_bytes", "asp_search_gpu",
 ]
@@ -83,18 +83,22 @@ def lib() -> C.CDLL:
     L.asp_ctx_create.restype = C.c_int
     L.asp_multicast_store.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int]
     L.asp_multicast_store.restype = C.c_int
-    L.asp_probe_gather.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]
-    L.asp_probe_gather.restype = C.c_int
     L.asp_ctx_destroy.argtypes = [C.c_void_p]
     L.asp_ctx_destroy.restype = None
     L.asp_ctx_stream.argtypes = [C.c_void_p]
     L.asp_ctx_stream.restype = C.c_void_p
     L.asp_plan_group_create.argtypes = [C.c_void_p, C.POINTER(PlanDesc), C.c_int, C.POINTER(C.c_void_p)]
     L.asp_plan_group_create.restype = C.c_int
+    L.asp_plan_descs_validate.argtypes = [C.POINTER(PlanDesc), C.c_int]
+    L.asp_plan_descs_validate.restype = C.c_int
     L.asp_plan_destroy.argtypes = [C.c_void_p]
     L.asp_plan_destroy.restype = None
     L.asp_plan_set_launch.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int64]
     L.asp_plan_set_launch.restype = C.c_int
+    L.asp_plan_get_launch.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+    L.asp_plan_get_launch.restype = C.c_int
+    L.asp_plan_set_tuning.argtypes = [C.c_void_p, C.c_int, C.c_int]
+    L.asp_plan_set_tuning.restype = C.c_int
     L.asp_plan_format_bytes.argtypes = [C.c_void_p]
     L.asp_plan_format_bytes.restype = C.c_uint64
     L.asp_plan_launches.argtypes = [C.c_void_p]
@@ -191,6 +195,13 @@ def make_array_desc(name: str, arr, compress: dict | None, length: int | None = 
     return d
 
 
+def validate_descs(descs: list[PlanDesc]) -> None:
+    """asp_plan_descs_validate: the checks of PlanGroup() without a GPU; raises AspError."""
+    n = len(descs)
+    arr = (PlanDesc * n)(*descs)
+    check(lib().asp_plan_descs_validate(arr, n))
+
+
 class PlanGroup:
     """All sub-matrix plans of one matrix (asp_plan_group_create). Keeps the host arrays alive
     until upload has finished."""
@@ -210,6 +221,15 @@ class PlanGroup:
 
     def set_launch(self, i: int, tblock: int, threads: int, reduce: int = 1):
         check(lib().asp_plan_set_launch(self._plans[i], tblock, threads, reduce))
+
+    def get_launch(self, i: int):
+        """(tblock_num, thread_num_in_block, thread_num_of_row_reduce) the kernel of plan i is launched with."""
+        a, b, c = C.c_int64(), C.c_int64(), C.c_int64()
+        check(lib().asp_plan_get_launch(self._plans[i], C.byref(a), C.byref(b), C.byref(c)))
+        return a.value, b.value, c.value
+
+    def set_tuning(self, i: int, vec: int = 0, path: int = -1):
+        check(lib().asp_plan_set_tuning(self._plans[i], vec, path))
 
     def format_bytes(self) -> int:
         return sum(lib().asp_plan_format_bytes(self._plans[i]) for i in range(self.n))

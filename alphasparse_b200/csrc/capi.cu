@@ -38,6 +38,28 @@ asp_status fail(asp_status s, const std::string &msg)
         if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
     } while (0)
 
+// Makes `device` current for the lifetime of the object and restores the caller's device afterwards:
+// every entry point that launches or allocates runs under one, so a process that holds contexts on
+// several GPUs never launches into a stream of a device that is not current.
+struct DeviceGuard
+{
+    int prev = -1;
+    cudaError_t err = cudaSuccess;
+    explicit DeviceGuard(int device)
+    {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != device) err = cudaSetDevice(device);
+        else if (err == cudaSuccess) prev = -1; // nothing to restore
+    }
+    ~DeviceGuard()
+    {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+#define ASP_ON_DEVICE(ctx)                \
+    DeviceGuard guard__((ctx)->device); \
+    if (guard__.err != cudaSuccess) return cuda_fail(guard__.err, "cudaSetDevice")
+
 int dtype_size(int dt)
 {
     switch (dt)
@@ -133,7 +155,9 @@ struct asp_plan
     uint64_t smem_elems = 0; // partial results per CTA (shared-memory family)
     uint64_t units_for_grid = 0;
     uint64_t warp_tasks = 0; // SELL-like with equal strips: warp-sized work items
+    uint64_t sell_strip = 0; // SELL-like: TLBs per strip when all strips are equal, else 0
     bool needs_zero = false;
+    int64_t asked_tblock = 0, asked_threads = 0, asked_reduce = 0; // the launch last requested (re-applied when vec / path change)
 };
 
 namespace
@@ -196,6 +220,9 @@ bool perm_on_device(int t)
 asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threads, int64_t reduce)
 {
     if (threads <= 0 || threads > 1024) return fail(ASP_ERR_INVALID_ARG, "thread_num_in_block must be in 1..1024");
+    p->asked_tblock = tblock;
+    p->asked_threads = threads;
+    p->asked_reduce = reduce;
     const int t = p->templ;
     const bool warp_based = t != ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS && t != ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS;
     if (warp_based && (threads % 32) != 0) return fail(ASP_ERR_INVALID_ARG, "thread_num_in_block must be a multiple of 32 for this template");
@@ -219,8 +246,6 @@ asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threa
         }
         const int64_t needed = (int64_t)((p->units_for_grid + (uint64_t)threads - 1) / (uint64_t)threads);
         if (tblock > needed) tblock = needed > 0 ? needed : 1;
-        static const char *cap = getenv("ASP_ELL_MAX_GRID");
-        if (cap && atoll(cap) > 0 && tblock > atoll(cap)) tblock = atoll(cap);
     }
     if ((t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE) && threads > 256)
     {
@@ -247,6 +272,158 @@ asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threa
 }
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---- content validation --------------------------------------------------------------------------
+// The structural checks of asp_plan_group_create look at lengths and offsets; these look at what the
+// arrays SAY: every column a kernel will gather and every row it will write must lie inside x and y.
+// A caller that hands over one bad index would otherwise make a kernel read or write outside its
+// buffers on a GPU it shares with other jobs. Cost: one OpenMP pass over each index array.
+uint64_t max_of(const HostMeta &h, uint64_t count)
+{
+    if (count == 0) return 0;
+    switch (h.kind)
+    {
+    case ASP_COMPRESS_NONE:
+    {
+        uint64_t mx = 0;
+        const int64_t n = (int64_t)count;
+        switch (h.dtype)
+        {
+#define ASP_MAX_CASE(DT, T)                                                            \
+    case DT:                                                                           \
+    {                                                                                  \
+        const T *q = (const T *)h.p;                                                   \
+        _Pragma("omp parallel for reduction(max : mx) schedule(static)") for (int64_t i = 0; i < n; i++) mx = q[i] > mx ? (uint64_t)q[i] : mx; \
+        break;                                                                         \
+    }
+            ASP_MAX_CASE(ASP_U8, uint8_t)
+            ASP_MAX_CASE(ASP_U16, uint16_t)
+            ASP_MAX_CASE(ASP_U32, uint32_t)
+        default:
+            ASP_MAX_CASE(ASP_U64, uint64_t)
+#undef ASP_MAX_CASE
+        }
+        return mx;
+    }
+    case ASP_COMPRESS_LINEAR: return (count - 1) * h.coef + h.icpt;
+    case ASP_COMPRESS_CONSTANT: return h.icpt;
+    case ASP_COMPRESS_CYCLE_LINEAR: return (std::min<uint64_t>(count, h.cycle) - 1) * h.coef + h.icpt;
+    case ASP_COMPRESS_CYCLE_INCREASE: return (count - 1) / h.cycle + h.icpt;
+    default:
+    {
+        uint64_t mx = 0;
+        for (int b = 0; b < h.nb && b < 5; b++) mx = std::max(mx, h.bval[b]);
+        return mx;
+    }
+    }
+}
+
+// the largest y index a device-permuted template (shared-memory and CSR5-like families) can write for
+// relative rows [0, rows); false when the permutation itself is too short
+bool device_rows_in_bounds(const asp_plan_desc &d, const HostMeta &perm, uint64_t rows, std::string &why)
+{
+    if (rows == 0) return true;
+    if (d.sort_kind == ASP_SORT_GLOBAL)
+    {
+        if (rows + d.first_row > perm.len) return why = "row_index_before_sort is shorter than first_row + the rows of this sub-matrix", false;
+        if (max_of(perm, perm.len) >= d.n_rows) return why = "row_index_before_sort names a row outside y", false;
+    }
+    else if (d.sort_kind == ASP_SORT_LOCAL)
+    {
+        if (rows > perm.len) return why = "row_index_before_sort is shorter than the rows of this sub-matrix", false;
+        if (max_of(perm, perm.len) + d.first_row >= d.n_rows) return why = "row_index_before_sort + first_row names a row outside y", false;
+    }
+    else if (rows + d.first_row > d.n_rows)
+        return why = "the sub-matrix has more rows than y below first_row", false;
+    return true;
+}
+
+bool validate_contents(const asp_plan_desc &d, const std::vector<HostMeta> &hm, const HostMeta &perm, const asp_array_desc *col, const asp::KArgs &a,
+                       std::string &why)
+{
+    using namespace asp;
+    {
+        HostMeta c;
+        c.p = col->host_ptr;
+        c.dtype = col->dtype;
+        c.kind = ASP_COMPRESS_NONE;
+        if (max_of(c, col->len) + d.first_col >= d.n_cols) return why = "col_index_arr names a column outside x", false;
+    }
+    const uint64_t radd = (d.sort_kind == ASP_SORT_GLOBAL) ? 0 : d.first_row;
+    switch (d.template_type)
+    {
+    case ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS:
+    case ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS:
+        if (max_of(hm[MS_ROW_OF_TLB], a.effective) + radd >= d.n_rows) return why = "global_row_index_of_thread_level_block names a row outside y", false;
+        return true;
+    case ASP_DIRECT_ATOM_TEMPLATE:
+        if (hm[MS_ROW_OF_TLB].kind == ASP_COMPRESS_NONE && hm[MS_ROW_OF_TLB].len < a.n_tlb) return why = "3-level: row map shorter than the TLB count", false;
+        if (max_of(hm[MS_ROW_OF_TLB], a.n_tlb) + radd >= d.n_rows) return why = "global_row_index_of_thread_level_block names a row outside y", false;
+        return true;
+    case ASP_DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE:
+        if (max_of(hm[MS_ROW_OF_UNIT], a.effective) + radd >= d.n_rows) return why = "global_row_index_of_warp_level_block names a row outside y", false;
+        return true;
+    case ASP_SHARED_MEMORY_LONG_ROW_TEMPLATE:
+        if (max_of(hm[MS_ROW_OF_UNIT], a.n_units) + radd >= d.n_rows) return why = "row_index_of_block_level_block names a row outside y", false;
+        return true;
+    case ASP_SHARED_MEMORY_TEMPLATE:
+    case ASP_SHARED_MEMORY_TEMPLATE_WARP_COMPRESS:
+    case ASP_SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE:
+    {
+        // rows: block_first_row_index is a CSR over BLBs; the partial-result offsets of every BLB must stay
+        // inside the BLB's own partials (they index shared memory)
+        const uint64_t B = a.n_units;
+        const HostMeta &br = hm[MS_BLK_ROW], &ro = hm[MS_ROW_OFF];
+        const uint64_t rows_all = br.get(B);
+        if (ro.kind == ASP_COMPRESS_NONE && ro.len < rows_all + 1) return why = "row offsets shorter than the row count", false;
+        bool ok = true;
+#pragma omp parallel for schedule(static) reduction(&& : ok)
+        for (int64_t b = 0; b < (int64_t)B; b++)
+        {
+            const uint64_t r0 = br.get(b), r1 = br.get(b + 1);
+            if (r1 < r0 || r1 > rows_all) { ok = false; continue; }
+            uint64_t partials;
+            if (d.template_type == ASP_SHARED_MEMORY_TEMPLATE_WARP_COMPRESS) partials = hm[MS_BLK_THR].get(b + 1) - hm[MS_BLK_THR].get(b);
+            else if (d.template_type == ASP_SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE) partials = hm[MS_BLK_WARP].get(b + 1) - hm[MS_BLK_WARP].get(b);
+            else partials = hm[MS_WARP_THR].get(hm[MS_BLK_WARP].get(b + 1)) - hm[MS_WARP_THR].get(hm[MS_BLK_WARP].get(b));
+            const uint64_t g0 = ro.get(r0);
+            uint64_t prev = g0;
+            for (uint64_t r = r0; r < r1; r++)
+            {
+                const uint64_t nx = ro.get(r + 1);
+                if (nx < prev || nx - g0 > partials) { ok = false; break; }
+                prev = nx;
+            }
+        }
+        if (!ok) return why = "a row's partial-result range leaves its BLB (row offsets / block_first_row_index inconsistent)", false;
+        return device_rows_in_bounds(d, perm, std::min<uint64_t>(rows_all, a.effective), why);
+    }
+    case ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE:
+    case ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE:
+    {
+        // thread t of warp w writes rows R0[w] + frow .. + (#row starts in t) - 1
+        const HostMeta &cm = hm[MS_COMBINE], &fr = hm[MS_ROW_OF_UNIT];
+        const uint64_t W = a.n_units;
+        const int S = (int)d.tlb_size, bw = d.bits_word;
+        const uint64_t rmask = (1ull << d.bits_row) - 1;
+        uint64_t top = 0; // one past the largest relative row written
+#pragma omp parallel for schedule(static) reduction(max : top)
+        for (int64_t w = 0; w < (int64_t)W; w++)
+        {
+            const uint64_t R0 = fr.get(w);
+            for (int l = 0; l < 32; l++)
+            {
+                const uint64_t m = cm.get((uint64_t)w * 32 + l);
+                const uint64_t flags = S >= 64 ? m : (m >> (bw - S)) & ((S >= 64) ? ~0ull : ((1ull << S) - 1));
+                const int starts = __builtin_popcountll(flags);
+                if (starts) top = std::max<uint64_t>(top, R0 + (m & rmask) + starts);
+            }
+        }
+        return device_rows_in_bounds(d, perm, top, why);
+    }
+    default: return true;
+    }
+}
 
 asp_status ensure_xy(asp_ctx *ctx, size_t xb, size_t yb)
 {
@@ -305,7 +482,8 @@ asp_status asp_ctx_create(int device, asp_ctx **out)
     int n = 0;
     ASP_CUDA(cudaGetDeviceCount(&n));
     if (device < 0 || device >= n) return fail(ASP_ERR_INVALID_ARG, "no such CUDA device");
-    ASP_CUDA(cudaSetDevice(device));
+    DeviceGuard guard(device); // the caller's current device is left as it was
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err, "cudaSetDevice");
     asp_ctx *c = new (std::nothrow) asp_ctx();
     if (!c) return fail(ASP_ERR_ALLOC, "host allocation failed");
     c->device = device;
@@ -332,7 +510,7 @@ asp_status asp_ctx_create(int device, asp_ctx **out)
 void asp_ctx_destroy(asp_ctx *c)
 {
     if (!c) return;
-    cudaSetDevice(c->device);
+    DeviceGuard guard(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->x) cudaFree(c->x);
     if (c->y) cudaFree(c->y);
@@ -353,15 +531,19 @@ void *asp_ctx_stream(asp_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr;
 asp_status asp_synchronize(asp_ctx *ctx)
 {
     if (!ctx) return fail(ASP_ERR_INVALID_ARG, "ctx is NULL");
+    ASP_ON_DEVICE(ctx);
     ASP_CUDA(cudaStreamSynchronize(ctx->stream));
     return ASP_OK;
 }
 
-asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp_plan **out_plans)
+} // extern "C"
+
+namespace
 {
-    if (!ctx || !descs || !out_plans || n <= 0) return fail(ASP_ERR_INVALID_ARG, "NULL argument or n <= 0");
-    for (int i = 0; i < n; i++) out_plans[i] = nullptr;
-    ASP_CUDA(cudaSetDevice(ctx->device));
+// dry == true: everything asp_plan_group_create checks, without a device (no allocation, no upload, no
+// plan objects returned); ctx may then be NULL.
+asp_status plan_group_build(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp_plan **out_plans, bool dry)
+{
 
     // ---- pass 1: validate descriptors, lay out the arena (arrays sharing a host pointer once)
     struct Slot
@@ -376,9 +558,11 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
     for (int i = 0; i < n; i++)
     {
         const asp_plan_desc &d = descs[i];
-        if (d.template_type == ASP_EMPTY_TEMPLATE) continue;
         if (d.template_type < 0 || d.template_type > ASP_EMPTY_TEMPLATE) return fail(ASP_ERR_INVALID_ARG, "unknown template_type");
+        // (also for EMPTY plans: the host-buffer entry points size x and y from the value type)
         if (d.val_dtype != ASP_F32 && d.val_dtype != ASP_F64) return fail(ASP_ERR_UNSUPPORTED, "val_dtype must be f32 or f64");
+        if (d.n_rows == 0 || d.n_cols == 0) return fail(ASP_ERR_INVALID_ARG, "matrix without rows or columns");
+        if (d.template_type == ASP_EMPTY_TEMPLATE) continue;
         if (!d.arrays || d.n_arrays <= 0) return fail(ASP_ERR_INVALID_ARG, "plan without arrays");
         if (d.first_row >= d.n_rows || d.first_col >= d.n_cols) return fail(ASP_ERR_BOUNDS, "first_row/first_col outside the matrix");
         for (int k = 0; k < d.n_arrays; k++)
@@ -444,8 +628,9 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
 
     std::shared_ptr<Arena> arena(new (std::nothrow) Arena());
     if (!arena) return fail(ASP_ERR_ALLOC, "host allocation failed");
-    arena->device = ctx->device;
+    arena->device = dry ? 0 : ctx->device;
     arena->bytes = std::max<size_t>(total, 256);
+    if (!dry)
     {
         cudaError_t e = cudaMalloc(&arena->base, arena->bytes);
         if (e != cudaSuccess)
@@ -455,8 +640,9 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
             return fail(ASP_ERR_ALLOC, std::string("cudaMalloc of the plan arena failed: ") + cudaGetErrorString(e));
         }
     }
-    for (auto &kv : placed)
-        ASP_CUDA(cudaMemcpyAsync((char *)arena->base + kv.second.off, kv.first, kv.second.bytes, cudaMemcpyHostToDevice, ctx->stream));
+    if (!dry)
+        for (auto &kv : placed)
+            ASP_CUDA(cudaMemcpyAsync((char *)arena->base + kv.second.off, kv.first, kv.second.bytes, cudaMemcpyHostToDevice, ctx->stream));
 
     // ---- pass 2: build the kernel arguments
     auto dev_meta = [&](const HostMeta &h) {
@@ -499,8 +685,8 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
         p->n_cols = d.n_cols;
         p->true_nnz = d.true_nnz;
         memset(&p->args, 0, sizeof(p->args));
-        if (d.template_type == ASP_EMPTY_TEMPLATE) continue;
         p->val_is_f64 = d.val_dtype == ASP_F64;
+        if (d.template_type == ASP_EMPTY_TEMPLATE) continue;
         p->col_width = dtype_size(cols[i]->dtype);
         asp::KArgs &a = p->args;
         a.val = (char *)arena->base + placed[vals[i]->host_ptr].off;
@@ -539,7 +725,6 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
             if (d.tlb_size == 0 || P == 0 || P * d.tlb_size != nnz_pad) st = ASP_ERR_BOUNDS, why = "ELL-like: #TLB * TLB size != padded nnz";
             // TLBs per thread: the widest group that keeps 16-byte alignment of every k-slice
             int v = 4;
-            if (const char *e = getenv("ASP_ELL_VEC")) v = atoi(e) > 0 ? atoi(e) : v;
             while (v > 1 && (P % v) != 0) v >>= 1;
             p->vec = v;
             p->units_for_grid = (P + v - 1) / v;
@@ -567,16 +752,11 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
                 const HostMeta &bt = hm[asp::MS_BLK_THR];
                 const bool eq128 = bt.kind == ASP_COMPRESS_LINEAR && bt.coef > 0 && bt.coef % 128 == 0;
                 p->vec = (p->val_is_f64 && !eq128) ? 2 : 4;
+                p->sell_strip = (bt.kind == ASP_COMPRESS_LINEAR && bt.coef > 0) ? bt.coef : 0;
             }
-            if (const char *e = getenv("ASP_SELL_VEC")) p->vec = atoi(e) > 0 ? atoi(e) : p->vec; // tuning knob
-            if (const char *e = getenv("ASP_SELL_PATH")) a.path = atoi(e);                      // tuning knob
             p->units_for_grid = B;
-            if ((a.path & 1) == 0)
-            {
-                // equal strips: the kernel walks warp tasks of 32 * vec TLBs (see k_sell)
-                const HostMeta &bt = hm[asp::MS_BLK_THR];
-                if (bt.kind == ASP_COMPRESS_LINEAR && bt.coef > 0 && bt.coef % (32ull * p->vec) == 0) p->warp_tasks = B * (bt.coef / (32ull * p->vec));
-            }
+            // equal strips: the kernel walks warp tasks of 32 * vec TLBs (see k_sell)
+            if (p->sell_strip && p->sell_strip % (32ull * p->vec) == 0) p->warp_tasks = B * (p->sell_strip / (32ull * p->vec));
             break;
         }
         case ASP_DIRECT_ATOM_TEMPLATE:
@@ -682,6 +862,7 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
         }
         default: st = ASP_ERR_UNSUPPORTED; why = "template not implemented"; break;
         }
+        if (st == ASP_OK && !validate_contents(d, hm, perms[i], cols[i], a, why)) st = ASP_ERR_BOUNDS;
         if (st != ASP_OK)
         {
             cleanup();
@@ -690,12 +871,12 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
         if (is_smem_family(d.template_type))
         {
             p->smem = align_up((size_t)p->smem_elems * (p->val_is_f64 ? 8 : 4), 16);
-            if (p->smem > (size_t)ctx->max_smem_optin)
+            if (p->smem > (size_t)(dry ? 227 * 1024 : ctx->max_smem_optin))
             {
                 cleanup();
                 return fail(ASP_ERR_UNSUPPORTED, "partial results of one BLB do not fit in shared memory");
             }
-            cudaError_t e = asp::allow_dynamic_smem(d.template_type, p->val_is_f64, p->col_width, p->smem);
+            cudaError_t e = dry ? cudaSuccess : asp::allow_dynamic_smem(d.template_type, p->val_is_f64, p->col_width, p->smem);
             if (e != cudaSuccess)
             {
                 cleanup();
@@ -711,6 +892,11 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
             return st;
         }
     }
+    if (dry)
+    {
+        cleanup();
+        return ASP_OK;
+    }
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess)
     {
@@ -718,6 +904,24 @@ asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n
         return cuda_fail(e, "plan upload");
     }
     return ASP_OK;
+}
+} // namespace
+
+extern "C" {
+
+asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp_plan **out_plans)
+{
+    if (!ctx || !descs || !out_plans || n <= 0) return fail(ASP_ERR_INVALID_ARG, "NULL argument or n <= 0");
+    for (int i = 0; i < n; i++) out_plans[i] = nullptr;
+    ASP_ON_DEVICE(ctx);
+    return plan_group_build(ctx, descs, n, out_plans, false);
+}
+
+asp_status asp_plan_descs_validate(const asp_plan_desc *descs, int n)
+{
+    if (!descs || n <= 0) return fail(ASP_ERR_INVALID_ARG, "NULL argument or n <= 0");
+    std::vector<asp_plan *> scratch((size_t)n, nullptr);
+    return plan_group_build(nullptr, descs, n, scratch.data(), true);
 }
 
 void asp_plan_destroy(asp_plan *plan) { delete plan; }
@@ -729,35 +933,107 @@ asp_status asp_plan_set_launch(asp_plan *plan, int64_t tblock_num, int64_t threa
     return apply_launch(nullptr, plan, tblock_num, thread_num_in_block, thread_num_of_row_reduce);
 }
 
+asp_status asp_plan_get_launch(const asp_plan *plan, int64_t *tblock_num, int64_t *thread_num_in_block, int64_t *thread_num_of_row_reduce)
+{
+    if (!plan) return fail(ASP_ERR_INVALID_ARG, "plan is NULL");
+    const bool empty = plan->templ == ASP_EMPTY_TEMPLATE;
+    if (tblock_num) *tblock_num = empty ? 0 : (int64_t)plan->grid;
+    if (thread_num_in_block) *thread_num_in_block = empty ? 0 : (int64_t)plan->block;
+    if (thread_num_of_row_reduce) *thread_num_of_row_reduce = empty ? 0 : (int64_t)plan->args.row_reduce;
+    return ASP_OK;
+}
+
+asp_status asp_plan_set_tuning(asp_plan *plan, int vec, int path)
+{
+    if (!plan) return fail(ASP_ERR_INVALID_ARG, "plan is NULL");
+    const int t = plan->templ;
+    if (t != ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS && t != ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS)
+        return fail(ASP_ERR_UNSUPPORTED, "only the ELL-like and SELL-like families have tuning knobs");
+    if (vec != 0 && vec != 1 && vec != 2 && vec != 4 && vec != 8) return fail(ASP_ERR_INVALID_ARG, "vec must be 0 (keep), 1, 2, 4 or 8");
+    if (t == ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS)
+    {
+        if (vec)
+        {
+            if (plan->args.n_tlb % (uint64_t)vec) return fail(ASP_ERR_INVALID_ARG, "vec must divide the padded TLB count");
+            plan->vec = vec;
+            plan->units_for_grid = (plan->args.n_tlb + vec - 1) / vec;
+        }
+    }
+    else
+    {
+        if (vec == 8) return fail(ASP_ERR_INVALID_ARG, "the SELL-like family takes vec 1, 2 or 4");
+        if (vec) plan->vec = vec;
+        if (path >= 0) plan->args.path = path;
+        plan->warp_tasks = 0;
+        if ((plan->args.path & 1) == 0 && plan->sell_strip && plan->sell_strip % (32ull * plan->vec) == 0)
+            plan->warp_tasks = plan->args.n_units * (plan->sell_strip / (32ull * plan->vec));
+    }
+    if (plan->asked_threads > 0) return apply_launch(nullptr, plan, plan->asked_tblock, plan->asked_threads, plan->asked_reduce);
+    return ASP_OK;
+}
+
 uint64_t asp_plan_format_bytes(const asp_plan *plan) { return plan ? plan->fmt_bytes : 0; }
 int asp_plan_launches(const asp_plan *plan) { return (plan && plan->templ != ASP_EMPTY_TEMPLATE) ? 1 : 0; }
+
+} // extern "C"
+
+namespace
+{
+// x / y lengths and the value size of a plan group: from the first plan that has a kernel, else from
+// plans[0] (a group of EMPTY plans still describes a matrix: y = 0)
+struct GroupShape
+{
+    const asp_plan *first = nullptr; // first non-EMPTY plan, may stay NULL
+    uint64_t n_rows = 0, n_cols = 0;
+    size_t es = 4;
+};
+asp_status group_shape(asp_plan *const *plans, int n_plans, GroupShape *g)
+{
+    for (int i = 0; i < n_plans; i++)
+    {
+        if (!plans[i]) return fail(ASP_ERR_INVALID_ARG, "NULL plan");
+        if (plans[i]->templ != ASP_EMPTY_TEMPLATE && !g->first) g->first = plans[i];
+    }
+    const asp_plan *ref = g->first ? g->first : plans[0];
+    g->n_rows = ref->n_rows;
+    g->n_cols = ref->n_cols;
+    g->es = ref->val_is_f64 ? 8 : 4;
+    for (int i = 0; i < n_plans; i++)
+        if (plans[i]->val_is_f64 != ref->val_is_f64 || plans[i]->n_rows != ref->n_rows || plans[i]->n_cols != ref->n_cols)
+            return fail(ASP_ERR_INVALID_ARG, "plans of different matrices in one call");
+    return ASP_OK;
+}
+} // namespace
+
+extern "C" {
 
 asp_status asp_spmv(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *d_x, void *d_y, int zero_y)
 {
     if (!ctx || !plans || n_plans <= 0 || !d_x || !d_y) return fail(ASP_ERR_INVALID_ARG, "NULL argument");
-    const asp_plan *first = nullptr;
-    for (int i = 0; i < n_plans; i++)
-    {
-        if (!plans[i]) return fail(ASP_ERR_INVALID_ARG, "NULL plan");
-        if (plans[i]->templ != ASP_EMPTY_TEMPLATE && !first) first = plans[i];
-    }
-    if (!first) return ASP_OK;
+    GroupShape g;
+    asp_status gs = group_shape(plans, n_plans, &g);
+    if (gs != ASP_OK) return gs;
+    ASP_ON_DEVICE(ctx);
     bool clear = zero_y == 1;
     if (zero_y == 2)
+    {
+        // a group without any kernel is the zero matrix: "clear when needed" means clear
+        clear = g.first == nullptr;
         for (int i = 0; i < n_plans; i++) clear = clear || (plans[i]->templ != ASP_EMPTY_TEMPLATE && plans[i]->needs_zero);
-    if (clear) ASP_CUDA(cudaMemsetAsync(d_y, 0, first->n_rows * (first->val_is_f64 ? 8 : 4), ctx->stream));
+    }
+    if (clear) ASP_CUDA(cudaMemsetAsync(d_y, 0, g.n_rows * g.es, ctx->stream));
+    if (!g.first) return ASP_OK;
     int active = 0;
     for (int i = 0; i < n_plans; i++) active += plans[i]->templ != ASP_EMPTY_TEMPLATE;
     const bool fork = active > 1;
     if (fork) ASP_CUDA(cudaEventRecord(ctx->ev_fork, ctx->stream));
     bool used[asp_ctx::kAux] = {false, false, false};
     int k = 0;
-    for (int i = 0; i < n_plans; i++)
+    asp_status result = ASP_OK;
+    for (int i = 0; i < n_plans && result == ASP_OK; i++)
     {
-        asp_plan *p = plans[i];
+        const asp_plan *p = plans[i];
         if (p->templ == ASP_EMPTY_TEMPLATE) continue;
-        if (p->val_is_f64 != first->val_is_f64 || p->n_rows != first->n_rows || p->n_cols != first->n_cols)
-            return fail(ASP_ERR_INVALID_ARG, "plans of different matrices in one call");
         cudaStream_t st = ctx->stream;
         if (fork && k > 0)
         {
@@ -765,30 +1041,42 @@ asp_status asp_spmv(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const voi
             st = ctx->aux[j];
             if (!used[j])
             {
-                ASP_CUDA(cudaStreamWaitEvent(st, ctx->ev_fork, 0));
+                cudaError_t e = cudaStreamWaitEvent(st, ctx->ev_fork, 0);
+                if (e != cudaSuccess)
+                {
+                    result = cuda_fail(e, "cudaStreamWaitEvent");
+                    break;
+                }
                 used[j] = true;
             }
         }
         k++;
-        p->args.x = d_x;
-        p->args.y = d_y;
-        ASP_CUDA(asp::launch_template(p->templ, p->val_is_f64, p->col_width, p->args, p->grid, p->block, p->smem, st, p->vec));
+        asp::KArgs args = p->args; // plans are shared, read-only objects: x / y travel in a copy
+        args.x = d_x;
+        args.y = d_y;
+        cudaError_t e = asp::launch_template(p->templ, p->val_is_f64, p->col_width, args, p->grid, p->block, p->smem, st, p->vec);
+        if (e != cudaSuccess) result = cuda_fail(e, "kernel launch");
     }
+    // always join the side streams that were forked, also after a failed launch
     for (int j = 0; j < asp_ctx::kAux; j++)
         if (used[j])
         {
-            ASP_CUDA(cudaEventRecord(ctx->ev_join[j], ctx->aux[j]));
-            ASP_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_join[j], 0));
+            cudaError_t e = cudaEventRecord(ctx->ev_join[j], ctx->aux[j]);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->stream, ctx->ev_join[j], 0);
+            if (e != cudaSuccess && result == ASP_OK) result = cuda_fail(e, "joining a side stream");
         }
-    return ASP_OK;
+    return result;
 }
 
 asp_status asp_spmv_host(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *h_x, void *h_y)
 {
-    if (!ctx || !plans || n_plans <= 0 || !plans[0] || !h_x || !h_y) return fail(ASP_ERR_INVALID_ARG, "NULL argument");
-    const size_t es = plans[0]->val_is_f64 ? 8 : 4;
-    const size_t xb = plans[0]->n_cols * es, yb = plans[0]->n_rows * es;
-    asp_status st = ensure_xy(ctx, xb, yb);
+    if (!ctx || !plans || n_plans <= 0 || !h_x || !h_y) return fail(ASP_ERR_INVALID_ARG, "NULL argument");
+    GroupShape g;
+    asp_status st = group_shape(plans, n_plans, &g);
+    if (st != ASP_OK) return st;
+    ASP_ON_DEVICE(ctx);
+    const size_t xb = g.n_cols * g.es, yb = g.n_rows * g.es;
+    st = ensure_xy(ctx, xb, yb);
     if (st != ASP_OK) return st;
     ASP_CUDA(cudaMemcpyAsync(ctx->x, h_x, xb, cudaMemcpyHostToDevice, ctx->stream));
     st = asp_spmv(ctx, plans, n_plans, ctx->x, ctx->y, 1);
@@ -828,10 +1116,11 @@ unsigned char *g_static_stage_addr[kMaxDevices]; // per device, filled on first 
 
 asp_status static_stage_address(asp_ctx *ctx, unsigned char **out)
 {
+    // (called with ctx->device current; the table is written with the same value by whichever
+    // thread gets there first)
     if (ctx->device < 0 || ctx->device >= kMaxDevices) return fail(ASP_ERR_UNSUPPORTED, "device ordinal too large for the static staging table");
     if (!g_static_stage_addr[ctx->device])
     {
-        ASP_CUDA(cudaSetDevice(ctx->device));
         void *p = nullptr;
         ASP_CUDA(cudaGetSymbolAddress(&p, g_static_stage));
         g_static_stage_addr[ctx->device] = (unsigned char *)p;
@@ -843,14 +1132,17 @@ asp_status static_stage_address(asp_ctx *ctx, unsigned char **out)
 
 asp_status asp_spmv_host_static(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *h_x, void *h_y)
 {
-    if (!ctx || !plans || n_plans <= 0 || !plans[0] || !h_x || !h_y) return fail(ASP_ERR_INVALID_ARG, "NULL argument");
-    const size_t es = plans[0]->val_is_f64 ? 8 : 4;
-    const size_t xb = plans[0]->n_cols * es, yb = plans[0]->n_rows * es;
+    if (!ctx || !plans || n_plans <= 0 || !h_x || !h_y) return fail(ASP_ERR_INVALID_ARG, "NULL argument");
+    GroupShape g;
+    asp_status st = group_shape(plans, n_plans, &g);
+    if (st != ASP_OK) return st;
+    const size_t xb = g.n_cols * g.es, yb = g.n_rows * g.es;
     const size_t half = ASP_STATIC_STAGE_BYTES / 2;
     if (xb > half || yb > half)
         return fail(ASP_ERR_INVALID_ARG, "matrix too large for the static staging area: x and y must each fit in " + std::to_string(half) + " bytes");
+    ASP_ON_DEVICE(ctx);
     unsigned char *stage = nullptr;
-    asp_status st = static_stage_address(ctx, &stage);
+    st = static_stage_address(ctx, &stage);
     if (st != ASP_OK) return st;
     unsigned char *sx = stage, *sy = stage + half;
     ASP_CUDA(cudaMemcpyAsync(sx, h_x, xb, cudaMemcpyHostToDevice, ctx->stream));
@@ -866,10 +1158,14 @@ uint64_t asp_static_stage_bytes(void) { return ASP_STATIC_STAGE_BYTES; }
 asp_status asp_time(asp_ctx *ctx, asp_plan *const *plans, int n_plans, int warmup, int reps, int zero_y,
                     double gflops_up_bound, float *ms_per_spmv, float *gflops)
 {
-    if (!ctx || !plans || n_plans <= 0 || !plans[0] || reps <= 0 || !ms_per_spmv) return fail(ASP_ERR_INVALID_ARG, "NULL argument or reps <= 0");
-    const size_t es = plans[0]->val_is_f64 ? 8 : 4;
-    const size_t xn = plans[0]->n_cols, yn = plans[0]->n_rows;
-    asp_status st = ensure_xy(ctx, xn * es, yn * es);
+    if (!ctx || !plans || n_plans <= 0 || reps <= 0 || !ms_per_spmv) return fail(ASP_ERR_INVALID_ARG, "NULL argument or reps <= 0");
+    GroupShape g;
+    asp_status st = group_shape(plans, n_plans, &g);
+    if (st != ASP_OK) return st;
+    ASP_ON_DEVICE(ctx);
+    const size_t es = g.es;
+    const size_t xn = g.n_cols, yn = g.n_rows;
+    st = ensure_xy(ctx, xn * es, yn * es);
     if (st != ASP_OK) return st;
     {
         // x = 100 everywhere, as the reference's generated main() sets it (code_builder.cc:1508-1509)
@@ -899,9 +1195,9 @@ asp_status asp_time(asp_ctx *ctx, asp_plan *const *plans, int n_plans, int warmu
     *ms_per_spmv = ms;
     uint64_t nnz = 0;
     for (int i = 0; i < n_plans; i++) nnz += plans[i]->true_nnz;
-    const double g = ms > 0 ? 2.0 * (double)nnz * 1e-6 / ms : 0.0;
-    if (gflops) *gflops = (float)g;
-    if (gflops_up_bound > 0 && g > gflops_up_bound) return fail(ASP_ERR_IMPLAUSIBLE, "throughput above the configured GFLOPS_UP_BOUND");
+    const double gf = ms > 0 ? 2.0 * (double)nnz * 1e-6 / ms : 0.0;
+    if (gflops) *gflops = (float)gf;
+    if (gflops_up_bound > 0 && gf > gflops_up_bound) return fail(ASP_ERR_IMPLAUSIBLE, "throughput above the configured GFLOPS_UP_BOUND");
     return ASP_OK;
 }
 

@@ -132,6 +132,9 @@ asp_status asp_format_load(const char *path, asp_format **out)
             uint64_t n_arrays = 0;
             ok = get(in.f, s) && get(in.f, F->infos[i]) && get(in.f, n_arrays);
             if (!ok || n_arrays > 64) return asp_host_fail(ASP_ERR_INVALID_ARG, "corrupt sub-matrix record");
+            if (s.template_type < 0 || s.template_type > ASP_EMPTY_TEMPLATE || (s.template_type != ASP_EMPTY_TEMPLATE && s.val_dt != val_dt) || s.sort_kind < ASP_SORT_NONE || s.sort_kind > ASP_SORT_LOCAL)
+                return asp_host_fail(ASP_ERR_INVALID_ARG, "corrupt sub-matrix record: template, value type or sort kind out of range");
+            if (s.first_row >= F->n_rows || s.first_col >= F->n_cols) return asp_host_fail(ASP_ERR_INVALID_ARG, "corrupt sub-matrix record: first row / column outside the matrix");
             TemplateData &t = F->subs[i];
             t.template_type = s.template_type, t.val_dt = s.val_dt, t.bits_word = s.bits_word, t.bits_flag = s.bits_flag, t.bits_row = s.bits_row;
             t.bits_off = s.bits_off, t.is_atom_add = s.is_atom_add != 0, t.sort_kind = s.sort_kind;
@@ -144,6 +147,10 @@ asp_status asp_format_load(const char *path, asp_format **out)
                 ArrayHead h;
                 ok = get(in.f, h);
                 if (!ok || h.n_branch < 0 || h.n_branch > ASP_MAX_BRANCH) return asp_host_fail(ASP_ERR_INVALID_ARG, "corrupt array record");
+                if (h.role < 0 || h.role >= ASP_ARR_ROLE_COUNT || h.dt < ASP_U8 || h.dt > ASP_F64 || h.kind < ASP_COMPRESS_NONE || h.kind > ASP_COMPRESS_CYCLE_INCREASE)
+                    return asp_host_fail(ASP_ERR_INVALID_ARG, "corrupt array record: role, element type or closed-form kind out of range");
+                if ((h.kind == ASP_COMPRESS_CYCLE_LINEAR || h.kind == ASP_COMPRESS_CYCLE_INCREASE) && h.cycle == 0)
+                    return asp_host_fail(ASP_ERR_INVALID_ARG, "corrupt array record: cycle of length 0");
                 TemplateArray &a = t.arrays[k];
                 a.role = h.role, a.dt = h.dt, a.len = h.len;
                 a.comp.kind = h.kind, a.comp.coef = h.coef, a.comp.icpt = h.icpt, a.comp.cycle = h.cycle;
@@ -151,12 +158,18 @@ asp_status asp_format_load(const char *path, asp_format **out)
                 if (h.shared_perm)
                 {
                     if (!F->perm) return asp_host_fail(ASP_ERR_INVALID_ARG, "array refers to a permutation the file does not hold");
+                    if (h.len != F->n_rows || h.dt != perm_dt) return asp_host_fail(ASP_ERR_INVALID_ARG, "array refers to the shared permutation with another length or element type");
                     a.shared = F->perm;
                 }
                 else
                 {
                     // the payload may be shorter than len * element size only for arrays replaced by a closed form
-                    if (h.payload_bytes > (1ull << 40)) return asp_host_fail(ASP_ERR_INVALID_ARG, "corrupt array size");
+                    if (h.payload_bytes > (1ull << 40) || h.len > (1ull << 40)) return asp_host_fail(ASP_ERR_INVALID_ARG, "corrupt array size");
+                    // an array that is loaded element by element must be there in full; one that a closed form replaces may be
+                    // stored or not, but never longer than it claims to be
+                    const uint64_t full = h.len * (uint64_t)dtype_bytes(h.dt);
+                    if ((h.kind == ASP_COMPRESS_NONE && h.payload_bytes != full) || h.payload_bytes > full)
+                        return asp_host_fail(ASP_ERR_INVALID_ARG, "array payload does not match its length and element type");
                     a.bytes.resize(h.payload_bytes);
                     if (h.payload_bytes) ok = fread(a.bytes.data(), 1, h.payload_bytes, in.f) == h.payload_bytes;
                 }

@@ -70,7 +70,9 @@ class ShardedSpmv:
         # NVSwitch replicates it into every rank's buffer (asp_multicast_store); x and x_next must
         # then come from new_vector(), which maps them symmetrically on all ranks. A one-element
         # all-reduce after the last chunk orders the stores of all ranks before the next SpMV.
-        self._mode = exchange if (world > 1 and dist.get_backend(group) == "nccl") else "bcast_loop"
+        nccl = world > 1 and dist.get_backend(group) == "nccl"
+        self._mode = exchange if nccl else "bcast_loop"
+        self._fallback_mode = "allgather" if nccl else "bcast_loop"
         if self._mode not in ("allgather", "a2a", "bcast_loop", "multicast"):
             raise ValueError(f"unknown exchange mode {exchange}")
         self._dtype = dtype
@@ -78,32 +80,55 @@ class ShardedSpmv:
         self._symm_keep = []
         self._flag = torch.zeros(1, dtype=torch.float32, device=device) if self._mode == "multicast" else None
 
+    def _all_agree(self, ok: bool) -> bool:
+        """Collective: True only when `ok` holds on every rank. Every rank calls it at the same points
+        of new_vector(), whatever happened locally, so a rank with a local failure never leaves the
+        others waiting in a rendezvous or a collective it has skipped."""
+        t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+        return int(t.item()) == 1
+
+    def _symm_alloc(self):
+        """Local part of a symmetric allocation (may raise on this rank only)."""
+        import torch.distributed._symmetric_memory as symm
+
+        gname = (self.group or dist.group.WORLD).group_name
+        try:
+            symm.enable_symm_mem_for_group(gname)
+        except Exception:
+            pass
+        return symm, gname, symm.empty(self.n, dtype=self._dtype, device=self.device)
+
+    def _fall_back(self, why: str) -> None:
+        self._mode = self._fallback_mode
+        self.fallback_reason = why[:200]
+
     def new_vector(self) -> torch.Tensor:
         """A length-n vector usable as x / x_next. In multicast mode it is symmetric memory mapped
-        on every rank and bound to a multicast object; falls back to the unequal all_gather when
-        the platform offers no multicast (then an ordinary tensor is returned)."""
+        on every rank and bound to a multicast object; when any rank cannot provide that, ALL ranks
+        fall back to the plain exchange together (then an ordinary tensor is returned)."""
         if self._mode == "multicast":
+            t = hdl = None
+            err = ""
             try:
-                import torch.distributed._symmetric_memory as symm
-
-                gname = (self.group or dist.group.WORLD).group_name
+                symm, gname, t = self._symm_alloc()
+            except Exception as e:  # local: import, out of memory, ...
+                err = repr(e)
+            if not self._all_agree(t is not None):
+                self._fall_back(err or "symmetric allocation failed on another rank")
+            else:
+                mc = 0
                 try:
-                    symm.enable_symm_mem_for_group(gname)
-                except Exception:
-                    pass
-                t = symm.empty(self.n, dtype=self._dtype, device=self.device)
-                hdl = symm.rendezvous(t, gname)
-                mc = int(hdl.multicast_ptr)
-                ok = torch.tensor([1 if mc else 0], device=self.device)
-                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
-                if int(ok.item()) == 0:
-                    raise RuntimeError("no multicast address for symmetric memory")
-                self._mc[t.data_ptr()] = mc
-                self._symm_keep.append((t, hdl))
-                return t
-            except Exception as e:  # every rank takes the same branch: the check above is collective
-                self._mode = "allgather"
-                self.fallback_reason = repr(e)[:200]
+                    hdl = symm.rendezvous(t, gname)
+                    mc = int(hdl.multicast_ptr)
+                except Exception as e:
+                    err = repr(e)
+                if not self._all_agree(mc != 0):
+                    self._fall_back(err or "no multicast address for symmetric memory on some rank")
+                else:
+                    self._mc[t.data_ptr()] = mc
+                    self._symm_keep.append((t, hdl))
+                    return t
         return torch.empty(self.n, dtype=self._dtype, device=self.device)
 
     # -- one SpMV of this rank's block, no communication -------------------------------------

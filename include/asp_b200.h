@@ -153,13 +153,35 @@ void *asp_ctx_stream(asp_ctx *ctx);
 /* replaces store_code_builder_data + read_dense_block_k_from_file + the cudaMalloc/cudaMemcpy
  * block (code_builder.cc:2429-2517, 2119-2129; e.g. direct_atom_op.cc:289-370,1524-1692):
  * validates and uploads all sub-matrix templates of one matrix. Arrays that share a host
- * pointer (the global row permutation) are uploaded once. */
+ * pointer (the global row permutation) are uploaded once. Validation covers the contents too:
+ * every column index must lie inside x, every row a kernel can write inside y, every offset
+ * inside the array it indexes (ASP_ERR_BOUNDS otherwise; one parallel pass over each index array).
+ * Every entry point makes the context's device current for its own duration and restores the
+ * caller's device before it returns. */
 asp_status asp_plan_group_create(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp_plan **out_plans);
 void asp_plan_destroy(asp_plan *plan);
+/* The validation of asp_plan_group_create on its own: same checks, same status and message, no device
+ * needed, nothing allocated or uploaded. For a caller that wants to vet template arrays (a loaded
+ * format file, the output of its own operators) before it touches a GPU. The reference has no
+ * counterpart: its init_<template> functions assert (e.g. direct_atom_op_warp_compress.cc:88-92). */
+asp_status asp_plan_descs_validate(const asp_plan_desc *descs, int n);
 
 /* replaces re-emitting + recompiling the program for every launch-parameter trial
  * (default_auto_tuner.cc:449-2030): tblock_num / thread_num_in_block / thread_num_of_row_reduce. */
 asp_status asp_plan_set_launch(asp_plan *plan, int64_t tblock_num, int64_t thread_num_in_block, int64_t thread_num_of_row_reduce);
+/* The launch asp_spmv will actually use. The kernels are compiled for a bounded CTA width per family
+ * (ELL-like 512, SELL-like and CSR5-like 256 threads) and never launch CTAs without work, so a request
+ * outside those bounds is folded into an equivalent launch (wider requests become more CTAs); a tuner
+ * that sweeps thread_num_in_block reads back here which points of its sweep coincide. The reference has
+ * no such query: its launch is the literal it printed into the program (code_of_kernal_function_call,
+ * e.g. direct_atom_op_warp_block_compress.cc:1012-1040). Any pointer may be NULL. */
+asp_status asp_plan_get_launch(const asp_plan *plan, int64_t *tblock_num, int64_t *thread_num_in_block, int64_t *thread_num_of_row_reduce);
+/* Work decomposition knobs of the ELL-like and SELL-like families, for launch-space experiments (the
+ * defaults are what the measurements in this repository use): `vec` = TLBs per thread (1, 2, 4, 8 for
+ * ELL-like; 1, 2, 4 for SELL-like; 0 keeps the current value), `path` (SELL-like only; -1 keeps) 0 = warp
+ * tasks over equal strips, 1 = one CTA per strip. Re-applies the last requested launch. No counterpart in
+ * the reference (its generated kernels handle one TLB per thread). */
+asp_status asp_plan_set_tuning(asp_plan *plan, int vec, int path);
 /* bytes of device memory the plan's format arrays occupy (B_fmt without x and y) */
 uint64_t asp_plan_format_bytes(const asp_plan *plan);
 /* number of kernel launches one asp_spmv over this plan issues (excluding the y clear) */
@@ -186,14 +208,6 @@ asp_status asp_spmv_host(asp_ctx *ctx, asp_plan *const *plans, int n_plans, cons
  * should be made before any stream capture; calls that overlap on one GPU race on the array. */
 asp_status asp_spmv_host_static(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *h_x, void *h_y);
 uint64_t asp_static_stage_bytes(void);
-
-/* Diagnostic, not part of the SpMV path: times `reps` passes of a kernel that only gathers
- * x[idx[i]] (u32 indices read coalesced, f32 values, eight gathers per thread in flight) with the
- * given launch shape on `stream`; all pointers are device memory, `d_out_f32` needs one element.
- * The rate is the ceiling of any SpMV whose columns are random (one gather per non-zero). No
- * counterpart in the reference. */
-asp_status asp_probe_gather(const void *d_idx_u32, const void *d_x_f32, void *d_out_f32, size_t n_gathers, int threads, int ctas, int reps, void *stream,
-                            float *ms_per_pass);
 
 /* Publishes `bytes` of finished results at `src` (this GPU's memory) to every GPU of an NVLink
  * multicast group: `multicast_dst` is the multicast address of the same offset of a buffer that all

@@ -352,13 +352,6 @@ void dump_template(code_builder_t *builder, unsigned long sub, const sub_spec &s
         exit(3);
     }
     g_js << "\n   ]";
-    if (getenv("ASP_REF_EMIT_KERNEL") != NULL)
-    {
-        // study aid only: the kernel text the reference would have handed to nvcc
-        std::ofstream kf(std::string(getenv("ASP_REF_EMIT_KERNEL")) + "/kernel_" + std::to_string(sub) + ".cu.txt");
-        kf << code_of_template_kernal(g_tp, g_tt, sub);
-        kf << "\n// ---- call ----\n" << code_of_kernal_function_call(g_tp, g_tt, sub);
-    }
 }
 
 void add_sub_node(exe_compressed_sub_graph_t *g, param_strategy_of_sub_graph_t *p, const std::vector<std::string> &tok)

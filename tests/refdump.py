@@ -11,6 +11,7 @@ import ctypes as C
 import json
 import os
 import subprocess
+import sys
 import tempfile
 
 import numpy as np
@@ -34,8 +35,12 @@ def have_ref_dump() -> bool:
 def build_oracles() -> None:
     """Compile the C y-oracle, and the reference format oracle when the reference tree exists."""
     subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle"), "cpu"], check=True)
-    if os.path.isdir("/root/reference"):
-        subprocess.run(["make", "-s", "-j8", "-C", os.path.join(ROOT, "oracle"), "ref"], check=True)
+    sys.path.insert(0, ROOT)
+    from __graft_entry__ import reference_dir
+
+    ref = reference_dir()
+    if ref:
+        subprocess.run(["make", "-s", "-j8", "-C", os.path.join(ROOT, "oracle"), "ref", "REF=" + ref], check=True)
 
 
 _olib = None

@@ -131,3 +131,43 @@ def test_all_ranks_ok_without_a_process_group():
     all_ranks_ok(True, "nothing")
     with pytest.raises(RuntimeError):
         all_ranks_ok(False, "single process")
+
+
+def _symm_failure_worker(rank, world, port, out_dir):
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    bounds = [0, 5, 12]
+    sh = ShardedSpmv(lambda xt, yt: yt.copy_(xt[bounds[rank] : bounds[rank + 1]] * 2.0), bounds, rank, world, torch.float32, "cpu")
+    # put the object in the state an NCCL run starts in, with the local allocation replaced by one that
+    # fails on rank 1 only (out of memory, a missing module: anything that happens on one host)
+    sh._mode = "multicast"
+
+    def alloc():
+        if rank == 1:
+            raise MemoryError("injected: symmetric allocation failed on this rank")
+        raise AssertionError("rank 0 must not go on to the rendezvous alone")
+
+    if rank == 1:
+        sh._symm_alloc = alloc
+    else:
+        # rank 0's allocation would succeed; it must still drop to the fallback because rank 1 could not
+        sh._symm_alloc = lambda: (None, None, torch.empty(12))
+    v = sh.new_vector()
+    xt = torch.arange(12, dtype=torch.float32)
+    want = (xt * 4).tolist()  # (iterate reuses x0 as one of its two buffers)
+    out = sh.iterate(xt, 2)
+    with open(os.path.join(out_dir, f"mode_{rank}.txt"), "w") as fh:
+        fh.write(f"{sh._mode};{getattr(sh, 'fallback_reason', '')};{out.tolist() == want};{v.shape[0]}")
+    dist.destroy_process_group()
+
+
+def test_a_local_allocation_failure_makes_every_rank_fall_back_together(tmp_path):
+    world = 2
+    mp.spawn(_symm_failure_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    modes = [open(tmp_path / f"mode_{r}.txt").read().split(";") for r in range(world)]
+    assert modes[0][0] == modes[1][0] == "bcast_loop", modes
+    assert "injected" in modes[1][1] and "another rank" in modes[0][1], modes
+    assert modes[0][2] == modes[1][2] == "True" and modes[0][3] == "12"

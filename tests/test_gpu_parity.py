@@ -6,7 +6,8 @@ import numpy as np
 import pytest
 
 import refdump
-from alphasparse_b200 import capi
+from alphasparse_b200 import capi, matrices as M
+from alphasparse_b200.graph import Matrix
 from golden_util import golden_names, load_golden
 
 pytestmark = pytest.mark.gpu
@@ -145,3 +146,78 @@ def test_empty_template_is_skipped(asp_ctx):
     assert np.all(y[s0["min_row"] : s0["max_row"] + 1] == 0)
     assert np.array_equal(y[s0["max_row"] + 1 :], y_full[s0["max_row"] + 1 :])
     part.close()
+
+
+def test_fp64_group_whose_first_strip_is_empty(asp_ctx):
+    """The host-buffer entry points size x and y from the group, not from plans[0]: an fp64 matrix
+    whose strip 0 carries the EMPTY template (what the search builds for every strip but the one it
+    is timing) must still move 8-byte elements."""
+    m, x = M.rmat(10, 6, seed=4)
+    m64 = M.CsrMatrix(m.n_rows, m.n_cols, m.indptr, m.indices, m.values.astype(np.float64))
+    x64 = x.astype(np.float64)
+    hm = Matrix.from_csr(m64)
+    cm = hm.dense("dense sort 1\ndense rowdiv_exp 32 4096 4\ndense compress")
+    assert cm.n_subs >= 2
+    lines = ["sub 0 template EMPTY"]
+    for i in range(1, cm.n_subs):
+        lines += [f"sub {i} row_padding 32 1", f"sub {i} tlb_row", f"sub {i} template K3"]
+    fmt = cm.execute("\n".join(lines))
+    g = fmt.upload(capi.Context(0))  # a fresh context: its staging buffers start empty
+    y_ref, scale = refdump.csr_ref(m64, x64)
+    info0 = fmt.sub_info(0)
+    perm = fmt.global_perm()
+    rows0 = perm[info0.min_row : info0.max_row + 1].astype(np.int64)  # original rows of strip 0
+    keep_rows = np.ones(m.n_rows, dtype=bool)
+    keep_rows[rows0] = False
+    for fn in (g.spmv_host, g.spmv_host_static, g.spmv_host):
+        y = fn(x64)
+        assert y.dtype == np.float64 and np.all(y[rows0] == 0)
+        assert refdump.rel_err(y[keep_rows], y_ref[keep_rows], scale[keep_rows]) <= refdump.TOL[np.dtype(np.float64)]
+    g.close()
+    fmt.close()
+
+
+def test_group_of_empty_templates_yields_zeros(asp_ctx):
+    """A group in which every strip is EMPTY is the zero matrix: y must come back cleared, not as
+    whatever the staging buffer held from the previous call."""
+    m, x, _, man = load_golden("uniform1024_f32_S5_K3")
+    descs, keep = refdump.plan_descs(man)
+    live = capi.PlanGroup(asp_ctx, descs, keep)
+    assert np.abs(live.spmv_host(x)).max() > 0 and np.abs(live.spmv_host_static(x)).max() > 0  # leaves non-zero results behind
+    descs2, keep2 = refdump.plan_descs(man)
+    descs2[0].template_type = capi.TEMPLATE["EMPTY"]
+    dead = capi.PlanGroup(asp_ctx, descs2, keep2)
+    assert np.all(dead.spmv_host(x) == 0)
+    assert np.all(dead.spmv_host_static(x) == 0)
+    import torch
+
+    dx = torch.from_numpy(x).cuda()
+    dy = torch.full((m.n_rows,), 7.0, dtype=torch.float32, device="cuda")
+    dead.spmv(dx.data_ptr(), dy.data_ptr(), "auto")
+    asp_ctx.synchronize()
+    assert float(dy.abs().max()) == 0.0
+    live.close()
+    dead.close()
+
+
+def test_reported_launch_is_the_launch_used(asp_ctx):
+    """asp_plan_get_launch: requests the kernels fold into an equivalent launch are reported as such."""
+    _, _, _, man = load_golden("uniform1024_f32_S5_K3")
+    descs, keep = refdump.plan_descs(man)
+    g = capi.PlanGroup(asp_ctx, descs, keep)
+    g.set_launch(0, 4, 1024, 1)
+    tb, th, _ = g.get_launch(0)
+    assert th == 512 and tb >= 1  # the ELL-like kernel is compiled for at most 512 threads per CTA
+    g.set_launch(0, 1000000, 128, 1)
+    tb, th, _ = g.get_launch(0)
+    assert th == 128 and tb * th * 4 < 1024 * 4 + 128 * 4  # never more CTAs than work (4 TLBs per thread)
+    g.close()
+
+
+def test_a_bad_column_never_reaches_a_kernel(asp_ctx):
+    m, x, _, man = load_golden("uniform1024_f32_S9_K9")
+    descs, keep = refdump.plan_descs(man)
+    descs[0].n_cols = 512  # x shorter than the columns the arrays name
+    with pytest.raises(capi.AspError) as e:
+        capi.PlanGroup(asp_ctx, descs, keep)
+    assert e.value.status == 5 and "column outside x" in str(e.value)
