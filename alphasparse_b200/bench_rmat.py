@@ -1,6 +1,10 @@
 """The sharded graph workload of bench.py: R-MAT adjacency, nnz-balanced row blocks over the ranks,
-x replicated, `iters` repeated SpMVs with an all-gather of y into the next x (strong scaling: the
-matrix is the same at every N). Returns the fields bench.py prints."""
+x replicated, `iters` repeated SpMVs whose results reach every rank before the next one (strong
+scaling: the matrix is the same at every N). Returns the fields bench.py prints.
+
+Nothing here checks results: bench.py hands in `check_fn` (the CPU oracle lives with the tests) and
+this module only calls it with the first SpMV's output.
+"""
 from __future__ import annotations
 
 import time
@@ -15,30 +19,38 @@ from .graph import partition_rows_by_nnz
 # One CSR5-like kernel over the block. The coarse row sort with a bin wider than any row is a stable
 # partition: rows keep their order, rows without non-zeros go last, where the CSR5-like lowering
 # drops them (it would otherwise store one explicit zero per empty row, and R-MAT blocks are up to
-# half empty rows). y is still written in nearly row order, so a row chunk of the block is a
-# contiguous slice of the next x.
+# half empty rows). y is still written in row order, so a row chunk of the block is a contiguous
+# slice of the next x.
 DEFAULT_GRAPH = {"dense": "dense sort 1073741824 | dense compress",
                  "subs": [{"graph": "S9_K9_s32", "nodes": ["tlb_nnz 32"], "template": "K9", "threads": 128, "row_reduce": 1}]}
 
 
-def run(args, rank: int, world: int, local_rank: int, dist, log):
+def graph_with_tlb_size(s: int) -> dict:
+    return {"dense": DEFAULT_GRAPH["dense"],
+            "subs": [{"graph": f"S9_K9_s{s}", "nodes": [f"tlb_nnz {s}"], "template": "K9", "threads": 128, "row_reduce": 1}]}
+
+
+def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
     dev = torch.device("cuda", local_rank)
     scale, ef, seed, iters = args.scale, 16, 4, args.iters
     n = 1 << scale
     t0 = time.perf_counter()
     # pass 1: per-row edge counts (every rank takes a share of the chunks), summed over ranks
     total = n * ef
-    n_chunks = (total + matrices_gpu.CHUNK - 1) // matrices_gpu.CHUNK
-    deg = matrices_gpu.rmat_row_degrees(scale, ef, seed, dev, chunk_ids=range(rank, n_chunks, world))
+    n_gen = (total + matrices_gpu.CHUNK - 1) // matrices_gpu.CHUNK
+    deg = matrices_gpu.rmat_row_degrees(scale, ef, seed, dev, chunk_ids=range(rank, n_gen, world))
     if dist:
         dist.all_reduce(deg)
     # "nnz": equal non-zeros per rank; "bytes": equal algorithmic bytes, i.e. a row weighs as much
-    # as one non-zero (4 B of y + 4 B of row structure against 4 B value + 4 B index)
+    # as one non-zero (4 B of y + 4 B of row structure against 4 B value + 4 B index); a number w:
+    # a row weighs w non-zeros
     row_weight = {"nnz": 0.0, "bytes": 1.0}.get(args.balance)
     if row_weight is None:
-        row_weight = float(args.balance)  # a row weighs this many non-zeros
-    # (weights are scaled by 8 so that fractional row weights survive the integer prefix sums)
-    bounds = balanced_bounds_from_degrees((deg * 8 + int(round(row_weight * 8))).cpu().numpy(), world)
+        row_weight = float(args.balance)
+    # (weights are scaled by 8 so that fractional row weights survive the integer prefix sums; rows
+    # without non-zeros cost nothing: the format drops them)
+    w8 = int(round(row_weight * 8))
+    bounds = balanced_bounds_from_degrees((deg * 8 + (deg > 0) * w8).cpu().numpy(), world)
     del deg
     r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
     # pass 2: this rank's row block (global columns), duplicates merged
@@ -51,20 +63,11 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
     if log:
         log(f"rows [{r0}, {r1}) nnz {nnz_local} generated in {gen_s:.1f} s")
 
-    n_chunks = max(1, args.chunks if args.chunks > 0 else (2 if world > 1 else 1))
+    exchange = args.exchange if world > 1 else "none"
+    n_chunks = max(1, args.chunks if args.chunks > 0 else (1 if exchange in ("publish", "none") else 2))
     ctx = capi.Context(local_rank)
     t0 = time.perf_counter()
-    # row chunks of this rank's block (nnz-balanced), one plan group each: chunk c is exchanged
-    # while chunk c+1 is computed
-    if args.chunk_shape == "geometric" and n_chunks > 1:
-        # chunk c (in row order) holds 2^c shares of the block's non-zeros: the chunk that is
-        # computed and published last is the smallest, so the exposed exchange is short
-        tot = float(m.indptr[-1])
-        fr = [(2.0 ** (c + 1) - 1.0) / (2.0 ** n_chunks - 1.0) for c in range(n_chunks - 1)]
-        cuts = np.array([0] + [int(np.searchsorted(m.indptr, f * tot, side="left")) for f in fr] + [m.n_rows], dtype=np.int64)
-        cuts = np.maximum.accumulate(cuts)
-    else:
-        cuts = partition_rows_by_nnz(m.indptr, n_chunks)
+    cuts = partition_rows_by_nnz(m.indptr, n_chunks)
     if args.graph:
         import json
         import os
@@ -82,25 +85,26 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
         group_.close()
         del fmt_, group_, mc
     else:
-        desc = DEFAULT_GRAPH
+        desc = graph_with_tlb_size(args.tlb) if args.tlb else DEFAULT_GRAPH
     fmts, groups, chunks = [], [], []
     build_error = None
-    # most rows first: the exchange of the last chunk is the only one no kernel hides
+    # most rows first: with a separate store pass the exchange of the last chunk is the only one no kernel hides
     order = sorted(range(n_chunks), key=lambda c: -(int(cuts[c + 1]) - int(cuts[c])))
-    if args.chunk_shape == "geometric":
-        order = list(range(n_chunks - 1, -1, -1))  # the big tail chunk first, the small head chunk last
     for c in order:
         lo, hi = int(cuts[c]), int(cuts[c + 1])
         if hi == lo or m.indptr[hi] == m.indptr[lo]:
-            # nothing to compute: the rows (if any) stay zero; still a chunk so that every rank has as many
+            # nothing to compute: the rows (if any) are zero
             def fz(xt, yt):
                 yt.zero_()
 
-            chunks.append((fz, lo, hi))
+            chunks.append((fz, lo, hi, (lambda xp, yp, mp: None)))
             continue
         mc = m.row_slice(lo, hi) if n_chunks > 1 else m
         try:
             f, g = tuner.build(ctx, mc, desc)
+            if args.stage:
+                for i in range(g.n):
+                    g.set_tuning(i, 0, 1)
         except Exception as e:  # reported to every rank below, before anybody enters a collective
             build_error = e
             break
@@ -110,7 +114,10 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
         def fn(xt, yt, g=g):
             g.spmv(xt.data_ptr(), yt.data_ptr(), True)  # empty rows are never stored by a kernel: clear y
 
-        chunks.append((fn, lo, hi))
+        def pub(xp, yp, mp, g=g):
+            g.spmv_publish(xp, yp, mp)
+
+        chunks.append((fn, lo, hi, pub))
         del mc
     all_ranks_ok(build_error is None, f"lowering / upload of the row block ({build_error})", dev)
     search_s = time.perf_counter() - t0
@@ -121,38 +128,16 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
         sh = ShardedSpmv(None, bounds, rank, world, torch.float32, dev, chunks=chunks, exchange=args.exchange)
         xa = sh.new_vector()
         xb = sh.new_vector()
-        xa.copy_(x0)
-        # parity of the first SpMV of this rank's slice against the CPU oracle (bounded sizes only)
+        # parity of the first SpMV of this rank's slice (the caller's checker; bounded sizes only)
         parity = None
         y1 = sh.spmv_slice(x0).clone()
         torch.cuda.synchronize()
-        if True:
-            import os
-            import sys
-
-            sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tests"))
-            import refdump
-
-            # the CPU oracle checks whole blocks up to 3e8 non-zeros, else three row windows of the
-            # block (head, middle, tail) of about 2e7 non-zeros each
-            xh, yh = x0.cpu().numpy(), y1.cpu().numpy()
-            if m.nnz <= 300_000_000:
-                windows = [(0, m.n_rows)]
-            else:
-                windows = []
-                for frac in (0.0, 0.5, 1.0):
-                    target = int(frac * (m.nnz - 20_000_000))
-                    a = int(np.searchsorted(m.indptr, target, side="left"))
-                    b = int(np.searchsorted(m.indptr, target + 20_000_000, side="right")) - 1
-                    windows.append((min(a, m.n_rows - 1), max(min(b, m.n_rows), min(a, m.n_rows - 1) + 1)))
-            parity = 0.0
-            for a, b in windows:
-                sub = m.row_slice(a, b) if (a, b) != (0, m.n_rows) else m
-                y_ref, scl = refdump.csr_ref(sub, xh)
-                parity = max(parity, refdump.rel_err(yh[a:b], y_ref, scl))
+        if check_fn is not None:
+            parity = check_fn(m, x0.cpu().numpy(), y1.cpu().numpy())
+        del y1
         W, K = max(args.warmup, 3), max(args.steps, 1)
         for _ in range(W):
-            sh.step_into(xa, xb)
+            sh.iterate(x0, 2, xa, xb)
         torch.cuda.synchronize()
         if dist:
             dist.barrier()
@@ -160,14 +145,20 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
         e1 = torch.cuda.Event(enable_timing=True)
         c0 = torch.cuda.Event(enable_timing=True)
         c1 = torch.cuda.Event(enable_timing=True)
+        step_ev = [torch.cuda.Event(enable_timing=True) for _ in range(K + 1)]
         torch.cuda.synchronize()
+        t_host0 = time.perf_counter()
         e0.record(stream)
-        for _ in range(K):
-            xa.copy_(x0)
-            sh.iterate(xa, iters, xb)
+        step_ev[0].record(stream)
+        for k in range(K):
+            sh.iterate(x0, iters, xa, xb)  # x0 is only read: every step starts from the same vector
+            step_ev[k + 1].record(stream)
         e1.record(stream)
         e1.synchronize()
+        timed_wall_s = time.perf_counter() - t_host0
         ms_total = e0.elapsed_time(e1)
+        per_step = [step_ev[k].elapsed_time(step_ev[k + 1]) for k in range(K)]
+        sh.check_barrier_status()
         # compute-only time of the same number of local SpMVs (no exchange), for the breakdown
         c0.record(stream)
         for _ in range(iters):
@@ -176,17 +167,24 @@ def run(args, rank: int, world: int, local_rank: int, dist, log):
         c1.synchronize()
         ms_compute = c0.elapsed_time(c1) / iters
     nnz_total = torch.tensor([nnz_local], dtype=torch.int64, device=dev)
-    t = torch.tensor([ms_total, ms_compute], device=dev)
+    t = torch.tensor([ms_total, ms_compute, float(np.median(per_step))], device=dev)
     if dist:
         dist.all_reduce(nnz_total)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t[0].item()) / K  # one step = `iters` repeated SpMVs
     nnz_all = int(nnz_total.item())
+    launches = int(sum(g.launches() for g in groups))
+    if sh._mode == "publish":
+        launches = 3 * launches + 1  # clear end rows, compute + publish, send end rows; one barrier kernel per SpMV
+    elif sh._mode == "multicast":
+        launches = 2 * launches + (1 if sh._flags is not None else 0)
     out = {
-        "ms_per_step": ms_step, "ms_per_spmv": ms_step / iters, "ms_compute_per_spmv_max": float(t[1].item()),
+        "ms_per_step": ms_step, "ms_per_spmv": ms_step / iters, "ms_compute_per_spmv_max": float(t[1].item()), "ms_per_step_median": float(t[2].item()),
         "gflops": 2.0 * nnz_all * iters / (ms_step * 1e-3) * 1e-9, "nnz": nnz_all, "rows": n, "iters": iters, "graph": desc,
-        "search_s": search_s, "gen_s": gen_s, "parity": parity, "rows_local": r1 - r0, "nnz_local": nnz_local,
-        "format_bytes": int(sum(g.format_bytes() for g in groups)), "launches_per_spmv": int(sum(g.launches() for g in groups)), "chunks": n_chunks, "exchange_used": sh._mode,
-        "m_local": m, "group": groups, "ctx": ctx, "x0": x0, "sharded": sh, "fmt": fmts,
+        "search_s": search_s, "gen_s": gen_s, "parity": parity, "rows_local": r1 - r0, "nnz_local": nnz_local, "timed_wall_s": timed_wall_s,
+        "format_bytes": int(sum(g.format_bytes() for g in groups)), "launches_per_spmv": launches, "chunks": n_chunks, "exchange_used": sh._mode if world > 1 else "none",
+        "fallback_reason": getattr(sh, "fallback_reason", None), "barrier": "flag kernel" if sh._flags is not None else ("nccl all_reduce" if world > 1 else "none"),
+        "end_rows_local": int(sum(g.end_rows() for g in groups)), "staged": bool(args.stage),
+        "m_local": m, "group": groups, "ctx": ctx, "x0": x0, "sharded": sh, "fmt": fmts, "bufs": (xa, xb),
     }
     return out

@@ -56,7 +56,7 @@ class PlanDesc(C.Structure):
 
 
 EXPORTS = [
-    "asp_ctx_create", "asp_multicast_store", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_descs_validate", "asp_plan_destroy",
+    "asp_ctx_create", "asp_multicast_store", "asp_spmv_publish", "asp_plan_end_rows", "asp_rank_barrier", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_descs_validate", "asp_plan_destroy",
     "asp_plan_set_launch", "asp_plan_get_launch", "asp_plan_set_tuning", "asp_plan_format_bytes", "asp_plan_launches", "asp_spmv", "asp_spmv_host", "asp_time",
     "asp_synchronize", "asp_status_str", "asp_last_error", "asp_built_for_sm100a", "asp_spmv_host_static",
     "asp_static_stage_bytes", "asp_search_gpu",
@@ -83,6 +83,12 @@ def lib() -> C.CDLL:
     L.asp_ctx_create.restype = C.c_int
     L.asp_multicast_store.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int]
     L.asp_multicast_store.restype = C.c_int
+    L.asp_spmv_publish.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.asp_spmv_publish.restype = C.c_int
+    L.asp_plan_end_rows.argtypes = [C.c_void_p]
+    L.asp_plan_end_rows.restype = C.c_uint64
+    L.asp_rank_barrier.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_uint, C.c_void_p, C.c_uint, C.c_void_p]
+    L.asp_rank_barrier.restype = C.c_int
     L.asp_ctx_destroy.argtypes = [C.c_void_p]
     L.asp_ctx_destroy.restype = None
     L.asp_ctx_stream.argtypes = [C.c_void_p]
@@ -135,6 +141,11 @@ def check(status: int) -> None:
 def multicast_store(src_ptr: int, multicast_ptr: int, nbytes: int, stream: int, ctas: int = 0) -> None:
     """asp_multicast_store: one-to-all store of a slice through an NVLink multicast address."""
     check(lib().asp_multicast_store(src_ptr, multicast_ptr, nbytes, stream, ctas))
+
+
+def rank_barrier(flags_local: int, flags_multicast: int, rank: int, world: int, epoch: int, status_ptr: int, stream: int, max_polls: int = 0) -> None:
+    """asp_rank_barrier: bounded-wait barrier of the ranks of a multicast group, enqueued on `stream`."""
+    check(lib().asp_rank_barrier(flags_local, flags_multicast, rank, world, epoch & 0xFFFFFFFF, status_ptr, max_polls, stream))
 
 
 class Context:
@@ -242,6 +253,13 @@ class PlanGroup:
         (clear y only when a plan accumulates with atomics)."""
         z = 2 if zero_y == "auto" else (1 if zero_y else 0)
         check(lib().asp_spmv(self.ctx.handle, self._plans, self.n, C.c_void_p(d_x), C.c_void_p(d_y), z))
+
+    def spmv_publish(self, d_x: int, d_y: int, d_y_multicast: int):
+        """asp_spmv_publish: y = A x computed and sent to every rank of the multicast group from one kernel."""
+        check(lib().asp_spmv_publish(self.ctx.handle, self._plans, self.n, C.c_void_p(d_x), C.c_void_p(d_y), C.c_void_p(d_y_multicast)))
+
+    def end_rows(self) -> int:
+        return sum(lib().asp_plan_end_rows(self._plans[i]) for i in range(self.n))
 
     def spmv_host(self, x: np.ndarray) -> np.ndarray:
         x = np.ascontiguousarray(x, dtype=self.val_dtype)

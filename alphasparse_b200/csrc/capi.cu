@@ -157,6 +157,10 @@ struct asp_plan
     uint64_t warp_tasks = 0; // SELL-like with equal strips: warp-sized work items
     uint64_t sell_strip = 0; // SELL-like: TLBs per strip when all strips are equal, else 0
     bool needs_zero = false;
+    // CSR5-like family: the rows of y that warps accumulate with `red` (first and last row of every warp), as
+    // indices into y; kept on the device for the publishing SpMV (asp_spmv_publish)
+    std::shared_ptr<Arena> end_rows;
+    uint64_t n_end_rows = 0;
     int64_t asked_tblock = 0, asked_threads = 0, asked_reduce = 0; // the launch last requested (re-applied when vec / path change)
 };
 
@@ -858,6 +862,49 @@ asp_status plan_group_build(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp
             else if (d.bits_word != 8 * dtype_size(hm[asp::MS_COMBINE].dtype) || d.bits_row <= 0 || d.bits_off <= 0 || (int)d.tlb_size + d.bits_row + d.bits_off > d.bits_word)
                 st = ASP_ERR_INVALID_ARG, why = "CSR5-like: inconsistent combine-meta bit layout";
             p->units_for_grid = W;
+            if (st == ASP_OK && !dry && d.n_rows <= 0xffffffffull && d.bits_word - (int)d.tlb_size >= 0 && d.tlb_size <= 64)
+            {
+                // first and last row of every warp, mapped to y (duplicates of neighbouring warps dropped)
+                const HostMeta &cm = hm[asp::MS_COMBINE], &fr = hm[asp::MS_ROW_OF_UNIT], &pm = perms[i];
+                const int S = (int)d.tlb_size, bw = d.bits_word;
+                auto row_of = [&](uint64_t r) -> uint64_t {
+                    if (d.sort_kind == ASP_SORT_GLOBAL) return pm.get(r + d.first_row);
+                    if (d.sort_kind == ASP_SORT_LOCAL) return pm.get(r) + d.first_row;
+                    return r + d.first_row;
+                };
+                std::vector<uint32_t> rows(2 * W);
+#pragma omp parallel for schedule(static)
+                for (int64_t w = 0; w < (int64_t)W; w++)
+                {
+                    uint64_t starts = 0;
+                    for (int l = 0; l < 32; l++)
+                    {
+                        const uint64_t m = cm.get((uint64_t)w * 32 + l);
+                        const uint64_t flags = S >= 64 ? m : ((m >> (bw - S)) & ((1ull << S) - 1));
+                        starts += (uint64_t)__builtin_popcountll(flags);
+                    }
+                    const uint64_t R0 = fr.get(w);
+                    rows[2 * w] = (uint32_t)row_of(R0);
+                    rows[2 * w + 1] = (uint32_t)row_of(R0 + (starts ? starts - 1 : 0));
+                }
+                rows.erase(std::unique(rows.begin(), rows.end()), rows.end());
+                std::shared_ptr<Arena> er(new (std::nothrow) Arena());
+                if (!er || cudaMalloc(&er->base, std::max<size_t>(rows.size() * 4, 4)) != cudaSuccess)
+                {
+                    cudaGetLastError();
+                    cleanup();
+                    return fail(ASP_ERR_ALLOC, "allocation of the end-row list failed");
+                }
+                er->device = ctx->device;
+                cudaError_t ce = cudaMemcpy(er->base, rows.data(), rows.size() * 4, cudaMemcpyHostToDevice);
+                if (ce != cudaSuccess)
+                {
+                    cleanup();
+                    return cuda_fail(ce, "upload of the end-row list");
+                }
+                p->end_rows = er;
+                p->n_end_rows = rows.size();
+            }
             break;
         }
         default: st = ASP_ERR_UNSUPPORTED; why = "template not implemented"; break;
@@ -947,8 +994,14 @@ asp_status asp_plan_set_tuning(asp_plan *plan, int vec, int path)
 {
     if (!plan) return fail(ASP_ERR_INVALID_ARG, "plan is NULL");
     const int t = plan->templ;
+    if (t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE)
+    {
+        if (vec != 0) return fail(ASP_ERR_INVALID_ARG, "the CSR5-like family has no vec knob");
+        if (path >= 0) plan->args.path = path & 1;
+        return ASP_OK;
+    }
     if (t != ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS && t != ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS)
-        return fail(ASP_ERR_UNSUPPORTED, "only the ELL-like and SELL-like families have tuning knobs");
+        return fail(ASP_ERR_UNSUPPORTED, "only the ELL-like, SELL-like and CSR5-like families have tuning knobs");
     if (vec != 0 && vec != 1 && vec != 2 && vec != 4 && vec != 8) return fail(ASP_ERR_INVALID_ARG, "vec must be 0 (keep), 1, 2, 4 or 8");
     if (t == ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS)
     {
@@ -974,6 +1027,7 @@ asp_status asp_plan_set_tuning(asp_plan *plan, int vec, int path)
 
 uint64_t asp_plan_format_bytes(const asp_plan *plan) { return plan ? plan->fmt_bytes : 0; }
 int asp_plan_launches(const asp_plan *plan) { return (plan && plan->templ != ASP_EMPTY_TEMPLATE) ? 1 : 0; }
+uint64_t asp_plan_end_rows(const asp_plan *plan) { return plan ? plan->n_end_rows : 0; }
 
 } // extern "C"
 
@@ -1083,6 +1137,47 @@ asp_status asp_spmv_host(asp_ctx *ctx, asp_plan *const *plans, int n_plans, cons
     if (st != ASP_OK) return st;
     ASP_CUDA(cudaMemcpyAsync(h_y, ctx->y, yb, cudaMemcpyDeviceToHost, ctx->stream));
     ASP_CUDA(cudaStreamSynchronize(ctx->stream));
+    return ASP_OK;
+}
+
+asp_status asp_spmv_publish(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *d_x, void *d_y, void *d_y_multicast)
+{
+    if (!ctx || !plans || n_plans <= 0 || !d_x || !d_y || !d_y_multicast) return fail(ASP_ERR_INVALID_ARG, "NULL argument");
+    GroupShape g;
+    asp_status gs = group_shape(plans, n_plans, &g);
+    if (gs != ASP_OK) return gs;
+    for (int i = 0; i < n_plans; i++)
+    {
+        const asp_plan *p = plans[i];
+        if (p->templ == ASP_EMPTY_TEMPLATE) continue;
+        const bool csr5 = p->templ == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || p->templ == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE;
+        if (!csr5 || !p->end_rows || p->args.atomic || !asp::csr5_specialised((int)p->args.tlb_size, p->col_width, p->args.bits_word))
+            return fail(ASP_ERR_UNSUPPORTED, "publishing SpMV: every plan must be a CSR5-like template with TLB size 4, 8, 16 or 32 and 16- or 32-bit columns");
+    }
+    ASP_ON_DEVICE(ctx);
+    // the three steps of every plan run back to back on the context's stream
+    for (int i = 0; i < n_plans; i++)
+    {
+        const asp_plan *p = plans[i];
+        if (p->templ == ASP_EMPTY_TEMPLATE) continue;
+        ASP_CUDA(asp::launch_zero_rows(p->val_is_f64, d_y, (const unsigned *)p->end_rows->base, p->n_end_rows, ctx->stream));
+    }
+    for (int i = 0; i < n_plans; i++)
+    {
+        const asp_plan *p = plans[i];
+        if (p->templ == ASP_EMPTY_TEMPLATE) continue;
+        asp::KArgs args = p->args;
+        args.x = d_x;
+        args.y = d_y;
+        args.y_mc = d_y_multicast;
+        ASP_CUDA(asp::launch_template(p->templ, p->val_is_f64, p->col_width, args, p->grid, p->block, p->smem, ctx->stream, p->vec));
+    }
+    for (int i = 0; i < n_plans; i++)
+    {
+        const asp_plan *p = plans[i];
+        if (p->templ == ASP_EMPTY_TEMPLATE) continue;
+        ASP_CUDA(asp::launch_publish_rows(p->val_is_f64, d_y, d_y_multicast, (const unsigned *)p->end_rows->base, p->n_end_rows, ctx->stream));
+    }
     return ASP_OK;
 }
 

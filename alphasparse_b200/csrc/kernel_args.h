@@ -60,6 +60,7 @@ struct KArgs
     const void *col;
     const void *x;
     void *y;
+    void *y_mc; // CSR5-like family in publish mode: NVLink multicast address of y (same offsets), else NULL
     Meta m[MS_COUNT];
     Meta perm; // row_index_before_sort
     unsigned long long first_row, first_col;
@@ -73,7 +74,8 @@ struct KArgs
     int row_reduce; // thread_num_of_row_reduce
     int bits_word, bits_flag, bits_row, bits_off;
     int warps_first_row_len; // length of the WLB first-row array (K10 has a +1 sentinel)
-    int path;                // kernel-specific walk: SELL-like 0 = warp tasks when strips are equal, 1 = one CTA per strip
+    int path;                // kernel-specific walk: SELL-like 0 = warp tasks when strips are equal, 1 = one CTA per strip;
+                             // CSR5-like 1 = the row sums of a warp go through shared memory and out as one contiguous run
 };
 
 } // namespace asp

@@ -36,7 +36,52 @@ __global__ void __launch_bounds__(512) k_mc_store(const unsigned *__restrict__ s
     if (tid < words - tail0) mc_store1(mc + tail0 + tid, src[tail0 + tid]);
     __threadfence_system();
 }
+// Barrier of the ranks of one NVLink multicast group, as a kernel on the stream that carries the SpMV:
+// every rank announces `epoch` in its own slot of a small symmetric flag array (one multicast store reaches
+// all replicas) and then waits until every slot of its LOCAL replica has reached `epoch`. The announcing
+// thread first issues a system-scope fence, so everything this GPU stored before the barrier (the rows it
+// published from the kernels launched earlier on the stream) is visible to a peer that sees the flag.
+//
+// The wait is bounded: after `max_polls` polls of a slot the thread records 1 + the slot it gave up on in
+// *status and returns, so a rank that never arrives costs a second or two, not a hung GPU. Ranks live on
+// different GPUs; two ranks of one group must never share a GPU (nothing guarantees that kernels that wait
+// on one another run at the same time).
+__global__ void __launch_bounds__(32) k_rank_barrier(const unsigned *flags_local, unsigned *flags_mc, int rank, int world, unsigned epoch,
+                                                     unsigned *status, unsigned max_polls)
+{
+    if (threadIdx.x == 0)
+    {
+        __threadfence_system();
+        asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(flags_mc + rank), "r"(epoch) : "memory");
+    }
+    if ((int)threadIdx.x < world)
+    {
+        unsigned seen = 0, polls = 0;
+        for (;;)
+        {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags_local + threadIdx.x) : "memory");
+            if ((int)(seen - epoch) >= 0) break; // (wrap-safe comparison of epochs)
+            if (++polls >= max_polls)
+            {
+                atomicExch(status, 1u + threadIdx.x);
+                break;
+            }
+            __nanosleep(200);
+        }
+    }
+    __syncwarp();
+    __threadfence_system();
+}
 } // namespace
+
+extern "C" asp_status asp_rank_barrier(const void *flags_local, void *flags_multicast, int rank, int world, unsigned epoch, void *status_u32, unsigned max_polls,
+                                       void *stream)
+{
+    if (!flags_local || !flags_multicast || !status_u32 || world < 1 || world > 32 || rank < 0 || rank >= world) return ASP_ERR_INVALID_ARG;
+    if (max_polls == 0) max_polls = 4000000u; // about a second or two
+    k_rank_barrier<<<1, 32, 0, (cudaStream_t)stream>>>((const unsigned *)flags_local, (unsigned *)flags_multicast, rank, world, epoch, (unsigned *)status_u32, max_polls);
+    return cudaGetLastError() == cudaSuccess ? ASP_OK : ASP_ERR_CUDA;
+}
 
 extern "C" asp_status asp_multicast_store(const void *src, void *multicast_dst, size_t bytes, void *stream, int ctas)
 {

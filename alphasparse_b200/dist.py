@@ -28,7 +28,15 @@ class ShardedSpmv:
     `chunks`, if given, replaces `local_spmv` by a list of `(fn, lo, hi)`: fn(x, y_rows) produces the
     local rows [lo, hi) (relative to bounds[rank]); the ranges must tile the rank's block. They are
     computed and exchanged in list order, and only the last exchange is not hidden behind a kernel,
-    so the chunk with the fewest rows belongs last.
+    so the chunk with the fewest rows belongs last. The ranks may cut their blocks into different
+    numbers of chunks, except with the pairwise exchanges ("a2a", "allgather", the gloo loop), which
+    pair the c-th chunks of all ranks.
+
+    exchange="publish": a chunk may carry a 4th entry `pub(x_ptr, y_ptr, y_multicast_ptr)` that computes
+    AND publishes its rows from one kernel (PlanGroup.spmv_publish); then nothing is exchanged
+    afterwards, and one bounded-wait barrier kernel per SpMV (asp_rank_barrier) orders the ranks.
+    Vectors must come from new_vector(), which returns them zero-filled: rows that no kernel ever
+    writes (rows without non-zeros that a format dropped) stay zero in every replica.
     """
 
     def __init__(self, local_spmv, bounds, rank: int, world: int, dtype, device, group=None, chunks=None, exchange: str = "allgather"):
@@ -39,6 +47,8 @@ class ShardedSpmv:
         self.device = torch.device(device)
         my_rows = self.rows[rank]
         self.chunks = [tuple(c) for c in chunks] if chunks is not None else [(local_spmv, 0, my_rows)]
+        self._pub = [c[3] if len(c) > 3 else None for c in self.chunks]
+        self.chunks = [c[:3] for c in self.chunks]
         tiled = sorted((lo, hi) for _, lo, hi in self.chunks)
         assert tiled[0][0] == 0 and tiled[-1][1] == my_rows and all(tiled[i][1] == tiled[i + 1][0] for i in range(len(tiled) - 1))
         self.y_local = torch.zeros(max(1, my_rows), dtype=dtype, device=device)
@@ -49,13 +59,17 @@ class ShardedSpmv:
         if world > 1:
             counts = [torch.zeros(1, dtype=torch.int64, device=device) for _ in range(world)]
             dist.all_gather(counts, torch.tensor([C], dtype=torch.int64, device=device), group=group)
-            if any(int(c.item()) != C for c in counts):
-                raise ValueError("all ranks must cut their block into the same number of chunks")
-            allc = [torch.zeros(2 * C, dtype=torch.int64, device=device) for _ in range(world)]
-            dist.all_gather(allc, mine.to(device), group=group)
-            self.span = [[(int(t[2 * c]), int(t[2 * c + 1])) for c in range(C)] for t in (u.cpu() for u in allc)]
+            counts = [int(c.item()) for c in counts]
+            self._equal_chunks = all(c == C for c in counts)
+            cmax = max(counts)
+            padded = torch.zeros(2 * cmax, dtype=torch.int64)
+            padded[: 2 * C] = mine
+            allc = [torch.zeros(2 * cmax, dtype=torch.int64, device=device) for _ in range(world)]
+            dist.all_gather(allc, padded.to(device), group=group)
+            self.span = [[(int(t[2 * c]), int(t[2 * c + 1])) for c in range(counts[p])] for p, t in enumerate(u.cpu() for u in allc)]
         else:
             self.span = [[(int(mine[2 * c]), int(mine[2 * c + 1])) for c in range(C)]]
+            self._equal_chunks = True
         self.on_gpu = self.device.type == "cuda"
         # (default priority: a high-priority exchange stream was measured and lost at 8 GPUs,
         # 0.85 -> 0.95 ms per SpMV at scale 26)
@@ -73,12 +87,25 @@ class ShardedSpmv:
         nccl = world > 1 and dist.get_backend(group) == "nccl"
         self._mode = exchange if nccl else "bcast_loop"
         self._fallback_mode = "allgather" if nccl else "bcast_loop"
-        if self._mode not in ("allgather", "a2a", "bcast_loop", "multicast"):
+        if self._mode not in ("allgather", "a2a", "bcast_loop", "multicast", "publish"):
             raise ValueError(f"unknown exchange mode {exchange}")
+        if self._mode == "publish" and any(p is None for p, (_, lo, hi) in zip(self._pub, self.chunks) if hi > lo):
+            self._mode = "multicast"  # a chunk without a publishing kernel: separate store pass
+        # the ranks must agree on the mode (one rank's chunks may lack a publishing kernel)
+        if nccl:
+            code = {"publish": 3, "multicast": 2}.get(self._mode, 1)
+            t = torch.tensor([code], dtype=torch.int32, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+            if int(t.item()) != code:
+                self._mode = {3: "publish", 2: "multicast"}.get(int(t.item()), exchange if exchange in ("allgather", "a2a") else "allgather")
+        if self._mode in ("allgather", "a2a", "bcast_loop") and not self._equal_chunks:
+            raise ValueError("the pairwise exchanges need the same number of chunks on every rank")
+        self._epoch = 0
+        self._flags = self._flags_mc = self._status = None
         self._dtype = dtype
         self._mc = {}  # data_ptr of a symmetric vector -> its multicast address
         self._symm_keep = []
-        self._flag = torch.zeros(1, dtype=torch.float32, device=device) if self._mode == "multicast" else None
+        self._flag = torch.zeros(1, dtype=torch.float32, device=device) if self._mode in ("multicast", "publish") else None
 
     def _all_agree(self, ok: bool) -> bool:
         """Collective: True only when `ok` holds on every rank. Every rank calls it at the same points
@@ -100,6 +127,10 @@ class ShardedSpmv:
         return symm, gname, symm.empty(self.n, dtype=self._dtype, device=self.device)
 
     def _fall_back(self, why: str) -> None:
+        # (called on every rank with the collectively agreed outcome, so all ranks take the same path)
+        if not self._equal_chunks:
+            raise RuntimeError("no NVLink multicast (" + why[:120] + ") and the ranks cut their blocks into different numbers of chunks: "
+                               "the pairwise exchanges cannot pair them")
         self._mode = self._fallback_mode
         self.fallback_reason = why[:200]
 
@@ -107,7 +138,7 @@ class ShardedSpmv:
         """A length-n vector usable as x / x_next. In multicast mode it is symmetric memory mapped
         on every rank and bound to a multicast object; when any rank cannot provide that, ALL ranks
         fall back to the plain exchange together (then an ordinary tensor is returned)."""
-        if self._mode == "multicast":
+        if self._mode in ("multicast", "publish"):
             t = hdl = None
             err = ""
             try:
@@ -126,10 +157,54 @@ class ShardedSpmv:
                 if not self._all_agree(mc != 0):
                     self._fall_back(err or "no multicast address for symmetric memory on some rank")
                 else:
+                    t.zero_()
                     self._mc[t.data_ptr()] = mc
                     self._symm_keep.append((t, hdl))
+                    if self._flags is None:
+                        self._make_flags(symm, gname)
+                    torch.cuda.synchronize(self.device)
+                    dist.barrier(group=self.group)  # nobody publishes into a vector that a peer is still clearing
                     return t
-        return torch.empty(self.n, dtype=self._dtype, device=self.device)
+        return torch.zeros(self.n, dtype=self._dtype, device=self.device)
+
+    def _make_flags(self, symm, gname) -> None:
+        """Symmetric flag words of the barrier kernel (one slot per rank); on any failure the ranks keep
+        the NCCL all-reduce as their barrier (agreed collectively)."""
+        f = hdl = None
+        try:
+            f = symm.empty(64, dtype=torch.int32, device=self.device)
+            f.zero_()
+        except Exception:
+            f = None
+        if not self._all_agree(f is not None):
+            return
+        mc = 0
+        try:
+            hdl = symm.rendezvous(f, gname)
+            mc = int(hdl.multicast_ptr)
+        except Exception:
+            mc = 0
+        if not self._all_agree(mc != 0):
+            return
+        self._flags, self._flags_mc = f, mc
+        self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._symm_keep.append((f, hdl))
+
+    def _barrier(self) -> None:
+        """All ranks' published rows are in every replica past this point (on the current stream)."""
+        if self._flags is not None:
+            from . import capi
+
+            self._epoch += 1
+            capi.rank_barrier(self._flags.data_ptr(), self._flags_mc, self.rank, self.world, self._epoch, self._status.data_ptr(),
+                              torch.cuda.current_stream(self.device).cuda_stream)
+        else:
+            dist.all_reduce(self._flag, group=self.group)
+
+    def check_barrier_status(self) -> None:
+        """Raises if a barrier kernel gave up waiting for a rank (the wait is bounded by design)."""
+        if self._status is not None and int(self._status.item()) != 0:
+            raise RuntimeError(f"rank barrier timed out waiting for rank {int(self._status.item()) - 1}")
 
     # -- one SpMV of this rank's block, no communication -------------------------------------
     def spmv_slice(self, x: torch.Tensor) -> torch.Tensor:
@@ -157,7 +232,7 @@ class ShardedSpmv:
                 off = self.span[me][c][0] * src.element_size()
                 capi.multicast_store(src.data_ptr(), mc + off, src.numel() * src.element_size(), torch.cuda.current_stream(self.device).cuda_stream, 0)
             if c == len(self.chunks) - 1:
-                dist.all_reduce(self._flag, group=self.group)  # every rank's stores are done past this point
+                self._barrier()  # every rank's stores are done past this point
         elif self._mode == "allgather":
             outs = [x_next[self.span[p][c][0] : self.span[p][c][1]] for p in range(self.world)]
             dist.all_gather(outs, src, group=self.group)
@@ -172,6 +247,16 @@ class ShardedSpmv:
         # (Running the chunks' kernels concurrently on prioritised streams was measured and lost:
         # the chunks then finish together and no exchange is hidden.)
         base = self.bounds[self.rank]
+        if self._mode == "publish":
+            mc = self._mc.get(x_next.data_ptr())
+            if mc is None:
+                raise ValueError("the publishing exchange needs vectors from new_vector()")
+            es = x_next.element_size()
+            for (fn, lo, hi), pub in zip(self.chunks, self._pub):
+                if hi > lo:
+                    pub(x.data_ptr(), x_next.data_ptr() + (base + lo) * es, mc + (base + lo) * es)
+            self._barrier()
+            return
         cur = torch.cuda.current_stream(self.device) if self._comm is not None else None
         for c, (fn, lo, hi) in enumerate(self.chunks):
             if hi > lo:
@@ -189,8 +274,19 @@ class ShardedSpmv:
             self._done.record(self._comm)
             cur.wait_event(self._done)
 
-    def iterate(self, x0: torch.Tensor, iters: int, scratch: torch.Tensor | None = None) -> torch.Tensor:
-        """x <- A x, `iters` times (square matrices); returns the final replicated x."""
+    def iterate(self, x0: torch.Tensor, iters: int, scratch: torch.Tensor | None = None, scratch2: torch.Tensor | None = None) -> torch.Tensor:
+        """x <- A x, `iters` times (square matrices); returns the final replicated x. With two scratch
+        vectors x0 is only read (the results alternate between the two); with one, x0 itself is the
+        second buffer and is overwritten from the second iteration on. The publishing exchange needs
+        two, both from new_vector(): it relies on rows that are never written staying zero."""
+        if scratch2 is not None:
+            a, outs = x0, (scratch, scratch2)
+            for i in range(iters):
+                self.step_into(a, outs[i & 1])
+                a = outs[i & 1]
+            return a
+        if self._mode == "publish":
+            raise ValueError("the publishing exchange needs two scratch vectors from new_vector()")
         a = x0
         b = scratch if scratch is not None else torch.empty_like(x0)
         for _ in range(iters):

@@ -1,20 +1,24 @@
 """Benchmark of the SpMV hot path: y = A x over the machine-designed formats.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c4|c4s|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c1|c2|c3|c4|c4s] [--impl reference]
 
-A step is one SpMV over the whole matrix. The default workload is the 5-point Laplacian on a
-2048 x 2048 grid in fp64 (4,194,304 rows, 20,963,328 non-zeros); with N > 1 every rank owns a
-row block of that size of a 2048 x (2048 N) grid (weak scaling, x replicated, no collective on
-the data path). Prints ONE JSON line on rank 0. The graph is searched on the GPU (asp_search_gpu)
-unless --graph replays one from an earlier line or --spec names a single strategy.
+Default workload (every N, N = 1 included): the sharded graph configuration, R-MAT scale 26
+(67,108,864 rows, ~1.06e9 non-zeros, fp32) generated on the GPUs, nnz-balanced row blocks, x
+replicated, ONE STEP = 100 repeated SpMVs (x <- A x). Strong scaling: the matrix is the same at every
+N. With N > 1 every rank's rows of the next x reach all ranks from inside the SpMV kernel (NVLink
+multicast stores, --exchange publish) and one bounded-wait barrier kernel per SpMV orders the ranks.
+At N = 1 the line also carries `configs`: the four single-GPU configurations (c1..c4) replayed with the
+graphs the search picked for them, each with its own time, roofline fraction and parity.
 
---workload c5 is the sharded graph case (strong scaling): R-MAT scale --scale generated on the GPUs,
-nnz-balanced row blocks, x replicated, one step = --iters repeated SpMVs whose results reach every
-rank through an NVLink multicast store (--exchange, --chunks, --balance: see their help).
+--workload c1|c2|c3|c4|c4s runs one single-GPU configuration as the main line (a step is one SpMV);
+the graph is searched on the GPU (asp_search_gpu) unless --graph / --spec fixes it.
 
---impl reference times the CPU restatement of the reference's SpMV (oracle/csr_spmv.c, OpenMP
-over all host cores) on the same workload: the reference has no host SpMV of its own and its
-GPU path needs nvcc at run time plus a per-matrix generated program.
+--impl reference times the CPU restatement of the reference's SpMV (oracle/csr_spmv.c, OpenMP over all
+host cores) on the SAME matrix (for c5: the same scale-26 R-MAT, generated on the GPU and copied to the
+host), one SpMV pass per step: the reference has no host SpMV of its own and its GPU path needs nvcc at
+run time plus a per-matrix generated program.
+
+Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
@@ -22,6 +26,7 @@ import argparse
 import ctypes as C
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -42,24 +47,34 @@ WORKLOADS = {
     "c4s": ("3x3-block FEM-like fp64, 1048576 block rows x 9 blocks, seed 3", lambda: matrices.block_fem(1_048_576, 9, 4096, 3)),
 }
 
-
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (bytes; keyed by workload and the graph's first node list).
-# c4 is too large for a full-set capture: its figure is the c4s capture scaled by the non-zeros
-# (values and indices are 98 % of the bytes of either).
-PROFILED_TRAFFIC = {
-    ("c2", "S5_K3"): 291.7e6,
-    ("c4s", "S1_K2_m128"): 1.05e9,
-    ("c4", "S1_K2_m128"): 1.05e9 * 254_803_968 / 84_934_656,
-    ("c3", "S9_K9_s16"): 433.6e6,
+# The graphs the GPU search (`bench.py --workload cK`) picked for the single-GPU configurations; the default
+# run replays them after its own timed region instead of searching again.
+COMMITTED_GRAPHS = {
+    "c1": {"dense": "dense compress", "subs": [{"graph": "S5_K3", "nodes": ["row_padding 32 1", "tlb_row"], "template": "K3", "threads": 128, "row_reduce": 1}]},
+    "c2": {"dense": "dense compress", "subs": [{"graph": "S5_K3", "nodes": ["row_padding 32 1", "tlb_row"], "template": "K3", "threads": 128, "row_reduce": 1}]},
+    "c3": {"dense": "dense compress", "subs": [{"graph": "S9_K9_s16", "nodes": ["tlb_nnz 16"], "template": "K9", "threads": 128, "row_reduce": 1}]},
+    "c4": {"dense": "dense compress", "subs": [{"graph": "S1_K2_m128", "nodes": ["row_padding 128 1", "blb_row_evenly 128", "tlb_row"], "template": "K2", "threads": 256, "row_reduce": 1}]},
 }
+COMMITTED_GRAPHS["c4s"] = COMMITTED_GRAPHS["c4"]
 
 
-def profiled_traffic(workload, graph_desc, world):
+def profiled_traffic(workload: str, graph_desc) -> float | None:
+    """dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the table in
+    profiles/dram_traffic.md (rows `| workload | graph | bytes | ...`); None when this graph has no capture."""
     subs = graph_desc.get("subs", []) if isinstance(graph_desc, dict) else []
-    if world != 1 or len(subs) != 1:
+    if len(subs) != 1:
         return None
-    return PROFILED_TRAFFIC.get((workload, subs[0].get("graph")))
+    p = os.path.join(ROOT, "profiles", "dram_traffic.md")
+    if not os.path.exists(p):
+        return None
+    for line in open(p):
+        f = [c.strip() for c in line.strip().strip("|").split("|")]
+        if len(f) >= 3 and f[0] == workload and f[1] == subs[0].get("graph"):
+            try:
+                return float(f[2])
+            except ValueError:
+                return None
+    return None
 
 
 def measured_peak_gbs():
@@ -99,226 +114,354 @@ class ClockSampler(threading.Thread):
                             self.reasons.add(n)
             except Exception:
                 pass
-            self.stop_flag.wait(0.2)
+            self.stop_flag.wait(0.1)
 
     def summary(self):
         return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def oracle_lib():
+def use_all_host_cores(share: int = 1):
+    """torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU legs are meant to use every host core this
+    process may run on (the OpenMP runtime reads the variable when the first OpenMP library loads). `share`:
+    number of local ranks that build their formats at the same time and split the cores."""
+    os.environ["OMP_NUM_THREADS"] = str(max(1, len(os.sched_getaffinity(0)) // max(1, share)))
+
+
+def oracle():
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import refdump
 
     return refdump
 
 
-def cpu_baseline(m, x, budget_s: float = 15.0, reps_min: int = 3):
-    """The CPU restatement of the reference's SpMV, timed on all host cores over repeated passes
-    of the same matrix until `budget_s` is used. Returns (GFLOP/s, threads, passes)."""
-    rd = oracle_lib()
-    L = rd.oracle_lib()
-    threads = int(L.asp_oracle_max_threads())
+def cpu_baseline(m, x, budget_s: float = 12.0, reps_min: int = 2, reps_max: int = 200):
+    """The CPU restatement of the reference's SpMV, timed on all host cores over repeated passes of the same
+    matrix until `budget_s` is used. Returns (GFLOP/s, threads, passes, median seconds)."""
+    rd = oracle()
+    threads = int(rd.oracle_lib().asp_oracle_max_threads())
     rd.csr_native(m, x)  # warm-up and page touch
     t0 = time.perf_counter()
-    n = 0
     times = []
-    while n < reps_min or (time.perf_counter() - t0 < budget_s and n < 200):
+    while len(times) < reps_min or (time.perf_counter() - t0 < budget_s and len(times) < reps_max):
         s = time.perf_counter()
         rd.csr_native(m, x)
         times.append(time.perf_counter() - s)
-        n += 1
     med = float(np.median(times))
-    return 2.0 * m.nnz / med * 1e-9, threads, n, med
+    return 2.0 * m.nnz / med * 1e-9, threads, len(times), med
+
+
+def check_against_oracle(m, x_host, y_host) -> float:
+    """max_i |y_i - y_ref_i| / sum_j |a_ij||x_j| against the CPU oracle: the whole matrix up to 3e8 non-zeros, else
+    three row windows (head, middle, tail) of about 2e7 non-zeros each."""
+    rd = oracle()
+    if m.nnz <= 300_000_000:
+        windows = [(0, m.n_rows)]
+    else:
+        windows = []
+        for frac in (0.0, 0.5, 1.0):
+            target = int(frac * (m.nnz - 20_000_000))
+            a = int(np.searchsorted(m.indptr, target, side="left"))
+            b = int(np.searchsorted(m.indptr, target + 20_000_000, side="right")) - 1
+            a = min(a, m.n_rows - 1)
+            windows.append((a, max(min(b, m.n_rows), a + 1)))
+    worst = 0.0
+    for a, b in windows:
+        sub = m.row_slice(a, b) if (a, b) != (0, m.n_rows) else m
+        y_ref, scl = rd.csr_ref(sub, x_host)
+        worst = max(worst, rd.rel_err(y_host[a:b], y_ref, scl))
+    return worst
+
+
+def c5_host_matrix(scale: int):
+    """The sharded workload's matrix as one host CSR: generated on the GPU (as the native arm does) when there is
+    one, else with the numpy generator at a scale the host builds in seconds (then the sample says so)."""
+    try:
+        import torch
+
+        if torch.cuda.is_available():
+            from alphasparse_b200 import matrices_gpu
+
+            dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+            indptr, cols, vals = matrices_gpu.rmat_block(scale, 16, 4, 0, 1 << scale, dev)
+            m = matrices_gpu.to_host_csr(indptr, cols, vals, 1 << scale)
+            x = matrices_gpu.rmat_x(scale, 4, dev).cpu().numpy()
+            del indptr, cols, vals
+            torch.cuda.empty_cache()
+            return m, x, scale
+    except Exception as e:  # no usable GPU: fall through to the host generator
+        print(f"[reference] GPU generation unavailable ({e!r}); using the host generator", file=sys.stderr)
+    sc = min(scale, 20)
+    m, x = matrices.rmat(sc, 16, seed=4)
+    return m, x, sc
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every host core
-    # this process may run on (the OpenMP runtime reads the variable when the oracle library loads)
-    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+    use_all_host_cores()
     if args.workload == "c5":
-        # bounded sample of the graph workload: the same generator parameters at a scale the host builds in seconds
-        sc = min(args.scale, 20)
-        desc, gen = f"R-MAT scale {sc} (sample of the scale-{args.scale} workload), edge factor 16, seed 4", (lambda: matrices.rmat(sc, 16, seed=4))
+        m, x, sc = c5_host_matrix(args.scale)
+        desc = f"R-MAT scale {sc}, edge factor 16, a/b/c/d .57/.19/.19/.05, seed 4"
+        sample = (f"each step is ONE SpMV pass over the whole scale-{sc} matrix ({m.nnz} non-zeros) out of the 100 a native step runs"
+                  + ("" if sc == args.scale else f"; scale {sc} instead of {args.scale}: no GPU to generate the matrix on"))
     else:
         desc, gen = WORKLOADS[args.workload]
-    m, x = gen()
+        m, x = gen()
+        sample = f"each step is one full SpMV pass of the {args.workload} matrix"
     W, K = max(args.warmup, 1), max(args.steps, 1)
-    rd = oracle_lib()
-    for _ in range(W):
+    rd = oracle()
+    threads = int(rd.oracle_lib().asp_oracle_max_threads())
+    t_w = time.perf_counter()
+    rd.csr_native(m, x)
+    first = time.perf_counter() - t_w
+    # bounded: the whole run is meant to end within a few minutes
+    if first * (W + K) > 240.0:
+        W = 1
+    for _ in range(W - 1):
         rd.csr_native(m, x)
     t0 = time.perf_counter()
     for _ in range(K):
         rd.csr_native(m, x)
     dt = (time.perf_counter() - t0) / K
-    threads = int(rd.oracle_lib().asp_oracle_max_threads())
     gf = 2.0 * m.nnz / dt * 1e-9
+    es = m.values.dtype.itemsize
+    b_alg = m.nnz * (es + 4) + 4 * (m.n_rows + 1) + es * (m.n_rows + m.n_cols)
     line = {
-        "impl": "reference", "metric": "SpMV GFLOP/s", "value": gf, "unit": "GFLOP/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
-        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f64" if m.values.dtype == np.float64 else "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "description": desc, "rows": m.n_rows, "nnz": m.nnz},
-        "cpu_baseline": {"value": gf, "unit": "GFLOP/s", "cores": threads, "kind": "port",
-                         "sample": f"{K} full SpMV passes of the {args.workload} matrix, OpenMP row-parallel CSR loop"},
+        "impl": "reference", "metric": "SpMV GFLOP/s", "value": gf, "unit": "GFLOP/s", "n_gpus": args.gpus, "steps": K, "warmup": max(args.warmup, 1),
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong" if args.workload == "c5" else "weak", "vs_baseline": None,
+        "dtype": "f64" if es == 8 else "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "description": desc, "rows": m.n_rows, "nnz": m.nnz, "algorithmic_GBs": b_alg / dt * 1e-9},
+        "cpu_baseline": {"value": gf, "unit": "GFLOP/s", "cores": threads, "kind": "port", "sample": sample + "; OpenMP row-parallel CSR loop, accumulation in the value type"},
         "e2e": {"value": gf, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
 
-def run_c5(args, rank, world, local_rank, dist):
-    """Sharded R-MAT, repeated SpMV (see alphasparse_b200/bench_rmat.py). One step = `iters` SpMVs."""
+def time_group(ctx, group, dx, dy, zero_y, stream, warmup: int, min_batch_s: float = 0.2, batches: int = 5):
+    """Median over `batches` batches, each long enough (>= min_batch_s) that clock samples fall inside it, of
+    the time per SpMV (CUDA events on the launching stream). Returns (ms per SpMV, reps per batch, all batch ms)."""
     import torch
 
-    from alphasparse_b200 import bench_rmat
+    def step():
+        group.spmv(dx.data_ptr(), dy.data_ptr(), zero_y)
+
+    for _ in range(max(warmup, 3)):
+        step()
+    ctx.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(10):
+        step()
+    e1.record(stream)
+    e1.synchronize()
+    est = max(e0.elapsed_time(e1) / 10, 1e-3)
+    reps = int(min(max(50, min_batch_s * 1e3 / est), 20000))
+    out = []
+    for _ in range(batches):
+        e0.record(stream)
+        for _ in range(reps):
+            step()
+        e1.record(stream)
+        e1.synchronize()
+        out.append(e0.elapsed_time(e1) / reps)
+    return float(np.median(out)), reps, out
+
+
+def run_single(ctx, name: str, graph_desc, peak: float, log=None, searched=None):
+    """One single-GPU configuration: build the matrix, lower `graph_desc` (or search when None), time, check."""
+    import torch
+
+    from alphasparse_b200 import capi, tuner
+
+    desc, gen = WORKLOADS[name]
+    t0 = time.perf_counter()
+    m, x = gen()
+    gen_s = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    trials = []
+    if graph_desc is None:
+        fmt, group, trials, graph_desc = tuner.search(ctx, m, quick=True, log=log)
+    else:
+        fmt, group = tuner.build(ctx, m, graph_desc)
+    build_s = time.perf_counter() - t0
+    val_t = torch.float64 if m.values.dtype == np.float64 else torch.float32
+    dx = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    dy = torch.zeros(m.n_rows, dtype=val_t, device="cuda")
+    stream = torch.cuda.ExternalStream(ctx.stream)
+    zero_y = "auto" if int(m.row_lengths().min()) > 0 else True
+    ms, reps, batches = time_group(ctx, group, dx, dy, zero_y, stream, warmup=5)
+    ctx.synchronize()
+    rd = oracle()
+    y_ref, scale = rd.csr_ref(m, x)
+    parity = rd.rel_err(dy.cpu().numpy(), y_ref, scale)
+    b_alg = m.algorithmic_bytes()
+    achieved = b_alg / (ms * 1e-3) * 1e-9
+    out = {"description": desc, "rows": m.n_rows, "nnz": m.nnz, "dtype": "f64" if m.values.dtype == np.float64 else "f32", "graph": graph_desc,
+           "ms_per_spmv": ms, "gflops": 2.0 * m.nnz / (ms * 1e-3) * 1e-9, "achieved_GBs": achieved, "frac": achieved / peak, "algorithmic_bytes": b_alg,
+           "traffic": profiled_traffic(name, graph_desc), "parity_max_rel_err": parity, "reps_per_batch": reps, "batches_ms": [round(b, 5) for b in batches],
+           "padding_rate": round(max(fmt.padding_rate(i) for i in range(fmt.n_subs)), 4), "format_MB": round(group.format_bytes() / 1e6, 1),
+           "generate_s": round(gen_s, 1), "build_s": round(build_s, 1), "trials": len(trials)}
+    keep = {"m": m, "x": x, "fmt": fmt, "group": group, "dx": dx, "dy": dy, "stream": stream, "zero_y": zero_y}
+    return out, keep
+
+
+def release(keep):
+    import torch
+
+    torch.cuda.synchronize()
+    keep["group"].close()
+    keep["fmt"].close()
+    keep.clear()
+    torch.cuda.empty_cache()
+
+
+def run_c5(args, rank, world, local_rank, dist):
+    """Sharded R-MAT, repeated SpMV (alphasparse_b200/bench_rmat.py). One step = `iters` SpMVs."""
+    import torch
+
+    from alphasparse_b200 import bench_rmat, capi
 
     log = (lambda s: print(f"[rank {rank}] {s}", file=sys.stderr)) if args.verbose else None
-    if args.steps == 200:
-        args.steps = 3  # a step is 100 SpMVs of a ~1e9-nnz matrix
     sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()
-    r = bench_rmat.run(args, rank, world, local_rank, dist, log)
+        sampler.start()  # stopped right after the timed region: its samples cover set-up (idle) and the timed steps
+    t_start = time.perf_counter()
+    r = bench_rmat.run(args, rank, world, local_rank, dist, log, check_fn=check_against_oracle)
+    n_before = len(sampler.samples)
     sampler.stop_flag.set()
     n, nnz, iters = r["rows"], r["nnz"], r["iters"]
+    K, W = max(args.steps, 1), max(args.warmup, 3)
     b_alg = nnz * 8 + 4 * (n + 1) + 4 * (n + n)
     achieved = b_alg * iters / (r["ms_per_step"] * 1e-3) * 1e-9
     peak, peak_kind = measured_peak_gbs()
+    # clock samples of the timed region only: the last timed_wall_s seconds before the sampler stopped
+    # (0.1 s apart; the compute-only pass that follows the timed region is also under load)
+    in_region = sampler.samples[-max(3, int(r["timed_wall_s"] / 0.13)) :] if sampler.samples else []
+    clocks = sampler.summary()
+    if in_region:
+        clocks["sm_mhz"] = float(np.median(in_region))
+        clocks["samples_in_timed_region"] = len(in_region)
+    line = None
     if rank == 0:
         line = {
-            "metric": "SpMV GFLOP/s", "value": r["gflops"], "unit": "GFLOP/s", "n_gpus": world, "steps": max(args.steps, 1), "warmup": max(args.warmup, 3),
+            "metric": "SpMV GFLOP/s", "value": r["gflops"], "unit": "GFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "c5", "description": f"R-MAT scale {args.scale}, edge factor 16, a/b/c/d .57/.19/.19/.05, seed 4, {iters} repeated SpMVs per step",
-                       "rows": n, "nnz": nnz, "rows_rank0": r["rows_local"], "nnz_rank0": r["nnz_local"], "graph_rank0": r["graph"],
-                       "l2": "inputs larger than L2", "search_s": round(r["search_s"], 1), "generate_s": round(r["gen_s"], 1),
-                       "ms_per_spmv": r["ms_per_spmv"], "ms_compute_per_spmv_max_over_ranks": r["ms_compute_per_spmv_max"], "row_chunks_per_rank": r["chunks"], "chunk_shape": args.chunk_shape, "balance": args.balance,
-                       "exchange": "none (1 GPU)" if world == 1 else f"{r['exchange_used']} of each row chunk on a second stream, overlapped with the next chunk's kernel"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world), "traffic": None,
-                         "peak_kind": peak_kind, "algorithmic_bytes": b_alg, "note": "x gathers are random over 2^scale columns: DRAM traffic exceeds the algorithmic bytes"},
-            "gpu_launches": int(max(args.steps, 1) * iters * r["launches_per_spmv"]),
-            "clocks": sampler.summary(), "parity_max_rel_err": r["parity"],
+            "config": {"workload": "c5", "description": f"R-MAT scale {args.scale}, edge factor 16, a/b/c/d .57/.19/.19/.05, seed 4, {iters} repeated SpMVs per step (x <- A x)",
+                       "rows": n, "nnz": nnz, "rows_rank0": r["rows_local"], "nnz_rank0": r["nnz_local"], "graph": r["graph"],
+                       "l2": "inputs larger than L2", "build_s": round(r["search_s"], 1), "generate_s": round(r["gen_s"], 1),
+                       "ms_per_spmv": r["ms_per_spmv"], "ms_per_step_median": r["ms_per_step_median"], "ms_compute_per_spmv_max_over_ranks": r["ms_compute_per_spmv_max"],
+                       "row_chunks_per_rank": r["chunks"], "balance": args.balance, "staged_row_sums": r["staged"],
+                       "exchange": "none (1 GPU)" if world == 1 else {"publish": "rows leave the SpMV kernel through the NVLink multicast address (multimem.st), end rows of the warps by a small kernel after it",
+                                                                       "multicast": "multicast store pass per row chunk on a second stream, overlapped with the next chunk's kernel"}.get(r["exchange_used"], r["exchange_used"]),
+                       "barrier": r["barrier"], "exchange_fallback": r["fallback_reason"],
+                       "values": "x grows by about 8x per SpMV and overflows fp32 after ~40 of the 100: the later SpMVs multiply inf / NaN (same memory traffic); parity is checked on the first SpMV"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world), "traffic": profiled_traffic("c5", r["graph"]) if world == 1 else None,
+                         "peak_kind": peak_kind, "algorithmic_bytes": b_alg, "launch": f"{iters} SpMV launches per step; peak = {world} x the measured copy bandwidth",
+                         "note": "the gathers of x are bound by cache-line look-ups per SM (one per clock), not by DRAM: see profiles/"},
+            "gpu_launches": int(K * iters * r["launches_per_spmv"]),
+            "clocks": clocks, "parity_max_rel_err": r["parity"],
         }
-    # end to end (all ranks take part): x0 from pinned host memory in, final x out
+    # end to end (all ranks take part): x0 from pinned host memory in, final x out, every step
+    sh, (xa, xb) = r["sharded"], r["bufs"]
     hx = r["x0"].cpu().pin_memory()
     hy = torch.empty_like(hx).pin_memory()
-    dev_x = r["sharded"].new_vector()
-    scratch = r["sharded"].new_vector()
+    dev_x = torch.empty_like(r["x0"])
     stream = torch.cuda.ExternalStream(r["ctx"].stream)
+    Ke = max(1, min(K, 3))
     torch.cuda.synchronize()
     if dist:
         dist.barrier()
     t0 = time.perf_counter()
     with torch.cuda.stream(stream):
-        dev_x.copy_(hx, non_blocking=True)
-        xf = r["sharded"].iterate(dev_x, iters, scratch)
-        hy.copy_(xf, non_blocking=True)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+        for _ in range(Ke):
+            dev_x.copy_(hx, non_blocking=True)
+            xf = sh.iterate(dev_x, iters, xa, xb)
+            hy.copy_(xf, non_blocking=True)
+            stream.synchronize()
+    e2e_s = (time.perf_counter() - t0) / Ke
+    sh.check_barrier_status()
     replicas_agree = None
     if dist:
         t = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
         # every rank must hold the same final x, bit for bit
-        # (compared as bit patterns: padded formats turn an overflowed x into NaN, and NaN != NaN)
+        # (compared as bit patterns: an overflowed x turns into NaN, and NaN != NaN)
         bits = xf.view(torch.int32).to(torch.int64)
         chk = torch.stack([bits.sum(), (bits * (torch.arange(bits.numel(), device=bits.device) % 8191 + 1)).sum()])
         lo, hi = chk.clone(), chk.clone()
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         replicas_agree = bool(torch.equal(lo, hi))
+        del bits, chk
     if rank == 0:
-        line["e2e"] = {"value": 2.0 * nnz * iters / e2e_s * 1e-9, "unit": "GFLOP/s", "h2d_bytes_per_step": int(4 * n), "d2h_bytes_per_step": int(4 * n), "ms_per_step": e2e_s * 1e3}
+        line["e2e"] = {"value": 2.0 * nnz * iters / e2e_s * 1e-9, "unit": "GFLOP/s", "h2d_bytes_per_step": int(4 * n), "d2h_bytes_per_step": int(4 * n),
+                       "ms_per_step": e2e_s * 1e3, "steps": Ke}
         line["replicas_agree"] = replicas_agree
-        if not args.no_cpu_baseline and r["m_local"].nnz <= 300_000_000:
-            gf, threads, passes, med = cpu_baseline(r["m_local"], r["x0"].cpu().numpy(), budget_s=10.0)
+        if world == 1 and not args.no_cpu_baseline:
+            gf, threads, passes, med = cpu_baseline(r["m_local"], hx.numpy(), budget_s=10.0, reps_min=2, reps_max=5)
             line["cpu_baseline"] = {"value": gf, "unit": "GFLOP/s", "cores": threads, "kind": "port",
-                                    "sample": f"{passes} SpMV passes over rank 0's row block ({r['nnz_local']} nnz, median {med * 1e3:.1f} ms), OpenMP row-parallel CSR loop"}
-        print(json.dumps(line), flush=True)
+                                    "sample": f"{passes} SpMV passes over the whole matrix ({nnz} nnz, median {med * 1e3:.0f} ms each) out of the {iters} of a step; OpenMP row-parallel CSR loop"}
     # Tear down in dependency order: torch frees pinned blocks by recording an event on the stream
     # they were last used on, and that stream belongs to the context object.
     torch.cuda.synchronize()
-    del hx, hy, dev_x, scratch, xf, stream
-    for k in ("sharded", "x0", "group", "fmt", "m_local"):
+    ctx = r["ctx"]
+    del hx, hy, dev_x, xf, stream, xa, xb, sh
+    for g in r["group"]:
+        g.close()
+    for k in ("sharded", "x0", "group", "fmt", "m_local", "bufs"):
         r.pop(k, None)
     import gc
 
     gc.collect()
     torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and not args.no_configs:
+        # the single-GPU configurations, replayed with their committed graphs (not part of the timed region above)
+        line["configs"] = {}
+        for name in args.configs.split(","):
+            try:
+                out, keep = run_single(ctx, name, COMMITTED_GRAPHS[name], peak, log)
+                release(keep)
+            except Exception as e:  # a sub-configuration never takes the main line down
+                out = {"error": repr(e)[:300]}
+            line["configs"][name] = out
+            if time.perf_counter() - t_start > args.configs_budget_s:
+                line["configs"]["skipped"] = f"time budget of {args.configs_budget_s:.0f} s used"
+                break
+    if rank == 0:
+        line["wall_s"] = round(time.perf_counter() - t_start, 1)
+        print(json.dumps(line), flush=True)
     r.pop("ctx", None)
+    del ctx
     if dist:
         dist.barrier()
         dist.destroy_process_group()
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5"])
-    ap.add_argument("--scale", type=int, default=26, help="c5: R-MAT scale (2^scale rows)")
-    ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x by an unpadded exchange of the ranks' slices)")
-    ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank whose exchange overlaps the next chunk's kernels (0: 2 when sharded, else 1)")
-    ap.add_argument("--chunk-shape", default="equal", choices=["equal", "geometric"], help="c5: equal non-zeros per chunk, or chunk sizes halving towards the one published last")
-    ap.add_argument("--exchange", default="multicast", choices=["multicast", "allgather", "a2a"],
-                    help="c5: how a rank's slice of the next x reaches the others (multicast falls back to allgather where symmetric memory has no multicast address)")
-    ap.add_argument("--balance", default="nnz", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
-                    "or a number w (a row weighs w non-zeros; the CSR5-like kernel measures about 2.6)")
-    ap.add_argument("--search", action="store_true", help="c5: run the quick search instead of the default one-kernel graph")
-    ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--full-search", action="store_true", help="sweep the full node-parameter and launch grids (slow)")
-    ap.add_argument("--dense", default="dense compress", help="with --spec: dense-view nodes, '|'-separated")
-    ap.add_argument("--spec", default=None, help="run exactly this compressed-view graph (name from the candidate list)")
-    ap.add_argument("--threads", type=int, default=0, help="with --spec: thread_num_in_block")
-    ap.add_argument("--graph", default=None, help="skip the search: a bench JSON line file (its config.graph is used) or the graph JSON itself")
-    ap.add_argument("--prune-gbs", type=float, default=0.0, help="search: skip candidates whose format cannot be read in the best time so far at this bandwidth (GB/s, an upper bound such as 8000); 0 = time everything")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--verbose", action="store_true")
-    args = ap.parse_args()
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
-        run_reference(args, rank, world)
-        return
-
+def run_one_config(args, rank, world, local_rank, dist):
+    """--workload c1|c2|c3|c4|c4s as the main line (single GPU: with N > 1 every rank runs its own replica)."""
     import torch
 
     from alphasparse_b200 import capi, tuner
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
-    torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_
-
-        dist = dist_
-        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)  # the exchange must not queue behind SpMV kernels
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), pg_options=opts)
-
-    if args.workload == "c5":
-        run_c5(args, rank, world, local_rank, dist)
-        return
     W, K = max(args.warmup, 3), max(args.steps, 1)
-    desc, gen = WORKLOADS[args.workload]
-    if args.workload == "c2" and world > 1:
-        # weak scaling: this rank's row block of the 2048 x (2048*world) grid, x replicated
-        r0 = rank * 2048 * 2048
-        m, x = matrices.laplacian_2d(2048, 1, grid_y=2048 * world, rows=(r0, r0 + 2048 * 2048))
-    else:
-        m, x = gen()
     log = (lambda s: print(f"[rank {rank}] {s}", file=sys.stderr)) if args.verbose else None
-
+    peak, peak_kind = measured_peak_gbs()
     ctx = capi.Context(local_rank)
+    graph_desc = None
+    if args.graph:
+        graph_desc = json.load(open(args.graph))["config"]["graph"] if os.path.exists(args.graph) else json.loads(args.graph)
+    elif args.committed:
+        graph_desc = COMMITTED_GRAPHS[args.workload]
     t_s = time.perf_counter()
     if args.spec:
         # one fixed graph (profiling runs): candidate name from the whitelist table, dense view from --dense
         from alphasparse_b200.graph import Matrix
 
+        desc, gen = WORKLOADS[args.workload]
+        m, x = gen()
         hm = Matrix.from_csr(m)
         cm = hm.dense(args.dense.replace("|", "\n"))
         if cm.n_subs != 1:
@@ -327,65 +470,49 @@ def main():
         cand = [c for c in tuner.compressed_candidates(mn_, mx_, nnz_ / rows_, "sort" in args.dense, quick=False) if c.name == args.spec]
         if not cand:
             raise SystemExit(f"no candidate named {args.spec} applies to this matrix")
-        fmt = cm.execute(cand[0].lines(0))
-        group = fmt.upload(ctx)
         th, red = (args.threads or cand[0].launches[0][0]), cand[0].launches[0][1]
-        tuner.set_launch(fmt, group, 0, th, red)
-        trials = []
-        graph_desc = {"dense": args.dense, "subs": [{"graph": cand[0].name, "threads": th, "row_reduce": red}]}
+        graph_desc = {"dense": args.dense.replace("|", " | "), "subs": [{"graph": cand[0].name, "nodes": cand[0].nodes, "template": cand[0].template, "threads": th, "row_reduce": red}]}
         cm.close()
         hm.close()
-    elif args.graph:
-        graph_desc = json.load(open(args.graph))["config"]["graph"] if os.path.exists(args.graph) else json.loads(args.graph)
-        fmt, group = tuner.build(ctx, m, graph_desc)
-        trials = []
-    else:
-        fmt, group, trials, graph_desc = tuner.search(ctx, m, quick=not args.full_search, log=log, prune_gbs=args.prune_gbs)
+        del m, x
+    sampler = ClockSampler(local_rank)
+    out, keep = run_single(ctx, args.workload, graph_desc, peak, log)
     search_s = time.perf_counter() - t_s
-    padding_rate = max(fmt.padding_rate(i) for i in range(fmt.n_subs))
-
-    val_t = torch.float64 if m.values.dtype == np.float64 else torch.float32
-    dx = torch.from_numpy(np.ascontiguousarray(x)).cuda()
-    dy = torch.zeros(m.n_rows, dtype=val_t, device="cuda")
-    stream = torch.cuda.ExternalStream(ctx.stream)
-    zero_y = "auto" if int(m.row_lengths().min()) > 0 else True  # rows without non-zeros are never stored by a kernel
+    m, x, group, dx, dy, stream, zero_y = (keep[k] for k in ("m", "x", "group", "dx", "dy", "stream", "zero_y"))
+    if args.stage:
+        for i in range(group.n):
+            group.set_tuning(i, 0, 1)
 
     def step():
         group.spmv(dx.data_ptr(), dy.data_ptr(), zero_y)
 
-    torch.cuda.synchronize()
+    # the contract's bracket: W warm-up steps, then exactly K steps between two events, max over ranks
     for _ in range(W):
         step()
     ctx.synchronize()
     if dist:
         dist.barrier()
-    sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     torch.cuda.synchronize()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(K):
         step()
     e1.record(stream)
     e1.synchronize()
-    torch.cuda.synchronize()
     ms_total = e0.elapsed_time(e1)
+    # and the median of 5 batches of >= 0.2 s each, during which the clocks are sampled
+    ms_med, reps, batches = time_group(ctx, group, dx, dy, zero_y, stream, warmup=0)
+    sampler.stop_flag.set()
     if dist:
         t = torch.tensor([ms_total], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
     ms_step = ms_total / K
-    if rank == 0:
-        # keep the GPU busy (untimed) until the clock sampler has seen it under load
-        t_end = time.perf_counter() + 4.0
-        while len(sampler.samples) < 3 and time.perf_counter() < t_end:
-            for _ in range(200):
-                step()
-            ctx.synchronize()
 
     # end to end through the host-buffer entry point: pinned x in, y out, every step
+    val_t = torch.float64 if m.values.dtype == np.float64 else torch.float32
     hx = torch.from_numpy(np.ascontiguousarray(x)).pin_memory()
     hy = torch.empty(m.n_rows, dtype=val_t).pin_memory()
     plans = group._plans
@@ -402,7 +529,6 @@ def main():
         t = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-    sampler.stop_flag.set()
 
     # launch-bound case (c1: the matrix lives in L2 and a kernel runs for a few microseconds): the same
     # SpMV replayed from a CUDA graph of 100 launches, so that host launch latency is out of the number
@@ -427,31 +553,26 @@ def main():
         except Exception as e:  # diagnostic extra, never fatal
             graph_us = f"unavailable: {e!r}"[:120]
 
-    # parity of what was just timed, against the CPU oracle on rank 0 (bounded: c2-sized matrices take ~0.1 s)
-    parity = None
-    if rank == 0 and m.nnz <= 300_000_000:
-        rd = oracle_lib()
-        y_ref, scale = rd.csr_ref(m, x)
-        parity = rd.rel_err(hy.numpy(), y_ref, scale)
-
+    rd = oracle()
+    y_ref, scale = rd.csr_ref(m, x)
+    parity = rd.rel_err(hy.numpy(), y_ref, scale) if rank == 0 else None
     nnz_total = m.nnz * world
-    gflops = 2.0 * nnz_total / (ms_step * 1e-3) * 1e-9
     b_alg = m.algorithmic_bytes()
     achieved = b_alg / (ms_step * 1e-3) * 1e-9
-    peak, peak_kind = measured_peak_gbs()
     if rank == 0:
         es = m.values.dtype.itemsize
         line = {
-            "metric": "SpMV GFLOP/s", "value": gflops, "unit": "GFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
+            "metric": "SpMV GFLOP/s", "value": 2.0 * nnz_total / (ms_step * 1e-3) * 1e-9, "unit": "GFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f64" if es == 8 else "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "description": desc, "rows_per_gpu": m.n_rows, "nnz_per_gpu": m.nnz,
-                       "graph": graph_desc,
-                       "l2": "inputs larger than L2 (format arrays %.0f MB)" % (group.format_bytes() / 1e6),
-                       "search_s": round(search_s, 2), "trials": len(trials), "padding_rate": round(padding_rate, 4),
+            "config": {"workload": args.workload, "description": out["description"] + ("" if world == 1 else f"; {world} independent replicas, one per GPU (replicas only: no data-path collective)"),
+                       "rows": m.n_rows, "nnz": m.nnz, "graph": out["graph"], "l2": "inputs larger than L2 (format arrays %.0f MB)" % out["format_MB"],
+                       "search_s": round(search_s, 2), "trials": out["trials"], "padding_rate": out["padding_rate"],
+                       "ms_per_spmv_median_of_batches": ms_med, "reps_per_batch": reps, "batches_ms": [round(b, 5) for b in batches],
                        **({"us_per_spmv_from_a_cuda_graph_of_100": graph_us} if graph_us is not None else {})},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": profiled_traffic(args.workload, graph_desc, world), "peak_kind": peak_kind, "algorithmic_bytes": b_alg,
+                         "traffic": profiled_traffic(args.workload, out["graph"]), "peak_kind": peak_kind, "algorithmic_bytes": b_alg,
+                         "frac_median_of_batches": b_alg / (ms_med * 1e-3) * 1e-9 / peak,
                          "format_bytes": int(group.format_bytes() + es * (m.n_cols + m.n_rows))},
             "e2e": {"value": 2.0 * nnz_total / e2e_s * 1e-9, "unit": "GFLOP/s", "h2d_bytes_per_step": int(es * m.n_cols),
                     "d2h_bytes_per_step": int(es * m.n_rows), "ms_per_step": e2e_s * 1e3},
@@ -459,14 +580,77 @@ def main():
             "clocks": sampler.summary(),
             "parity_max_rel_err": parity,
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             gf, threads, passes, med = cpu_baseline(m, x)
             line["cpu_baseline"] = {"value": gf, "unit": "GFLOP/s", "cores": threads, "kind": "port",
                                     "sample": f"{passes} full SpMV passes of this matrix (median {med * 1e3:.2f} ms), OpenMP row-parallel CSR loop"}
         print(json.dumps(line))
+    del hx, hy
+    release(keep)
     if dist:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default: 5 for c5, where a step is 100 SpMVs; 200 otherwise)")
+    ap.add_argument("--warmup", type=int, default=None, help="untimed warm-up steps (default 3; at least 3 are always run)")
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["c5"])
+    ap.add_argument("--scale", type=int, default=26, help="c5: R-MAT scale (2^scale rows)")
+    ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x)")
+    ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank (0: 1 with the publishing kernels, 2 with a separate store pass)")
+    ap.add_argument("--exchange", default="publish", choices=["publish", "multicast", "allgather", "a2a"],
+                    help="c5: how a rank's slice of the next x reaches the others: from inside the SpMV kernel (publish), by a multicast store pass per "
+                         "chunk, or by NCCL (both multicast modes fall back to allgather where symmetric memory has no multicast address)")
+    ap.add_argument("--balance", default="nnz", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
+                    "or a number w (a row with non-zeros weighs w non-zeros)")
+    ap.add_argument("--tlb", type=int, default=0, help="c5: non-zeros per thread of the CSR5-like format (default 32)")
+    ap.add_argument("--stage", action="store_true", help="CSR5-like plans: row sums of a warp through shared memory, contiguous write-out")
+    ap.add_argument("--search", action="store_true", help="c5: run the quick search instead of the default one-kernel graph")
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--full-search", action="store_true", help="sweep the full node-parameter and launch grids (slow)")
+    ap.add_argument("--dense", default="dense compress", help="with --spec: dense-view nodes, '|'-separated")
+    ap.add_argument("--spec", default=None, help="run exactly this compressed-view graph (name from the candidate list)")
+    ap.add_argument("--threads", type=int, default=0, help="with --spec: thread_num_in_block")
+    ap.add_argument("--graph", default=None, help="skip the search: a bench JSON line file (its config.graph is used) or the graph JSON itself")
+    ap.add_argument("--committed", action="store_true", help="single-GPU workloads: replay the committed graph instead of searching")
+    ap.add_argument("--configs", default="c1,c2,c3,c4", help="c5 at N = 1: single-GPU configurations to attach to the line")
+    ap.add_argument("--no-configs", action="store_true")
+    ap.add_argument("--configs-budget-s", type=float, default=600.0, help="no further sub-configuration is started once the run has taken this long")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--verbose", action="store_true")
+    args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 5 if args.workload == "c5" else 200
+    if args.warmup is None:
+        args.warmup = 3
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    # the CPU legs (oracle checks, cpu_baseline) and the OpenMP host operators; the ranks of a node share its cores
+    use_all_host_cores(int(os.environ.get("LOCAL_WORLD_SIZE", str(world))))
+
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+
+        dist = dist_
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.workload == "c5":
+        run_c5(args, rank, world, local_rank, dist)
+    else:
+        run_one_config(args, rank, world, local_rank, dist)
 
 
 if __name__ == "__main__":

@@ -219,6 +219,31 @@ uint64_t asp_static_stage_bytes(void);
  * (code_builder.cc:1483-1489). */
 asp_status asp_multicast_store(const void *src, void *multicast_dst, size_t bytes, void *stream, int ctas);
 
+/* The sharded repeated SpMV (x <- A x over the GPUs of one NVLink domain, every rank owning a row block) as
+ * ONE kernel per plan that computes and publishes: like asp_spmv, but the rows a warp finishes leave the
+ * kernel through `d_y_multicast`, the NVLink multicast address of the buffer that `d_y` is this GPU's
+ * replica of (same offsets), so they land in every rank's copy of the next x while the other warps are
+ * still computing. Only the first and last row of each warp, which neighbouring warps may share, are
+ * accumulated locally (cleared before the kernel, sent by a small kernel after it). Every plan must be a
+ * CSR5-like template (TLB size 4, 8, 16 or 32; 16- or 32-bit columns; not forced to atomics), else
+ * ASP_ERR_UNSUPPORTED. Rows the plans never write (rows without non-zeros that the format dropped) are not
+ * touched in any replica: the caller clears the buffer once, when it creates it. Follow the call with
+ * asp_rank_barrier (or a collective) before any rank reads the result. No counterpart in the reference,
+ * which is single-GPU (code_builder.cc:1483-1489). */
+asp_status asp_spmv_publish(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *d_x, void *d_y, void *d_y_multicast);
+/* number of rows asp_spmv_publish sends after the kernel (at most two per warp) */
+uint64_t asp_plan_end_rows(const asp_plan *plan);
+
+/* Barrier of the `world` ranks of a multicast group as a one-warp kernel on `stream` (see asp_spmv_publish):
+ * `flags_local` / `flags_multicast` are this GPU's replica and the multicast address of a symmetric array of
+ * `world` 32-bit words, zero at first; `epoch` must grow by one per barrier, the same on every rank. Stores
+ * issued earlier on the stream are visible to a peer that passes the barrier. The wait is bounded
+ * (`max_polls` polls per slot, 0 = about a second): on expiry the kernel writes 1 + the slot it gave up on
+ * to *status_u32 (device memory, cleared by the caller) and returns. One rank per GPU only. No counterpart
+ * in the reference. */
+asp_status asp_rank_barrier(const void *flags_local, void *flags_multicast, int rank, int world, unsigned epoch, void *status_u32, unsigned max_polls,
+                            void *stream);
+
 /* replaces execute_binary + perf_result parsing (executor.cc:6-59): CUDA-event timing of
  * `reps` SpMVs after `warmup`, x and y internal (x = 100 everywhere, as the generated main()
  * does). gflops = 2*sum(true_nnz)*1e-6/ms. Returns ASP_ERR_IMPLAUSIBLE when gflops exceeds

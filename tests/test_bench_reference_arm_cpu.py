@@ -32,3 +32,10 @@ def test_other_ranks_of_the_reference_arm_do_nothing():
     e = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--workload", "c1", "--gpus", "2"], capture_output=True, text=True, env=e, timeout=120)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_reference_arm_of_the_sharded_workload_times_one_pass_per_step():
+    d = run("--workload", "c5", "--scale", "12", "--steps", "2", "--warmup", "1")
+    assert d["impl"] == "reference" and d["config"]["workload"] == "c5" and d["scaling"] == "strong"
+    assert d["config"]["rows"] == 4096 and "ONE SpMV pass" in d["cpu_baseline"]["sample"]
+    assert d["steps"] == 2 and d["value"] > 0

@@ -127,3 +127,24 @@ def test_format_loaded_from_its_file_runs_like_the_original(asp_ctx, mats, tmp_p
     assert np.array_equal(y0, y1) or refdump.rel_err(y1, y0.astype(np.float64), scale) <= 1e-6  # atomics may reorder sums
     for o in (g0, g1, fmt, back):
         o.close()
+
+
+@pytest.mark.parametrize("templ", ["K9", "K10"])
+@pytest.mark.parametrize("s", [4, 8, 16, 32, 5])
+@pytest.mark.parametrize("mat", ["rmat_f32", "mixed_f32", "laplace_f64", "fem_f64"])
+def test_csr5_like_kernels_for_every_tlb_size_direct_and_staged(asp_ctx, mats, mat, s, templ):
+    """The CSR5-like family is specialised on the TLB size (4, 8, 16, 32; any other size takes the generic
+    kernel). Both write-out forms -- one store per row, and the warp's rows through shared memory as one
+    contiguous run -- must give the oracle's y; rows spanning many warps (mixed_f32 has rows of up to
+    5000 non-zeros) and rows without non-zeros (rmat_f32) included."""
+    m, x = mats[mat]
+    fmt = Matrix.from_csr(m).execute(f"dense compress\nsub all tlb_nnz {s}\nsub all template {templ}")
+    g = fmt.upload(asp_ctx)
+    y_ref, scale = refdump.csr_ref(m, x)
+    for path in (0, 1):
+        g.set_tuning(0, 0, path)
+        for threads in (64, 256):
+            tuner.set_launch(fmt, g, 0, threads, 1)
+            refdump.assert_y(g.spmv_host(x), y_ref, scale, m.values.dtype, f"{mat} {templ} s={s} path={path} threads={threads}")
+    g.close()
+    fmt.close()

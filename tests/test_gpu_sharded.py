@@ -26,7 +26,10 @@ def _chunks(ctx, blk, n_chunks, keep):
         def fn(xt, yt, g=g):
             g.spmv(xt.data_ptr(), yt.data_ptr(), True)
 
-        out.append((fn, lo, hi))
+        def pub(xp, yp, mp, g=g):
+            g.spmv_publish(xp, yp, mp)
+
+        out.append((fn, lo, hi, pub))
     return out
 
 
@@ -47,7 +50,7 @@ def test_row_chunks_on_one_gpu_match_the_oracle(asp_ctx):
         sh = ShardedSpmv(None, [0, m.n_rows], 0, 1, torch.float32, "cuda", chunks=chunks)
         x0 = torch.from_numpy(x).cuda()
         y = sh.spmv_slice(x0).clone()
-        xf = sh.iterate(x0.clone(), 3, sh.new_vector())
+        xf = sh.iterate(x0, 3, sh.new_vector(), sh.new_vector())
         torch.cuda.synchronize()
     y_ref, scale = refdump.csr_ref(m, x)
     refdump.assert_y(y.cpu().numpy(), y_ref, scale, np.float32, "chunked slice")
@@ -96,17 +99,34 @@ def _worker(rank, world, port, mode, out_dir):
     blk = m.row_slice(int(bounds[rank]), int(bounds[rank + 1]))
     ctx = capi.Context(rank)
     keep = []
-    chunks = _chunks(ctx, blk, 2, keep)
+    # the multicast forms pair nothing across ranks: every rank cuts its block as it likes
+    n_chunks = 2 if mode in ("allgather", "a2a") else (1 if rank == 0 else 3)
+    chunks = _chunks(ctx, blk, n_chunks, keep)
     stream = torch.cuda.ExternalStream(ctx.stream)
+    timed_out = None
     with torch.cuda.stream(stream):
         sh = ShardedSpmv(None, bounds, rank, world, torch.float32, torch.device("cuda", rank), chunks=chunks, exchange=mode)
         a, b = sh.new_vector(), sh.new_vector()
-        a.copy_(torch.from_numpy(x).cuda())
-        xf = sh.iterate(a, 3, b)
+        x0 = torch.from_numpy(x).cuda()
+        xf = sh.iterate(x0, 3, a, b)  # x0 is only read; the results alternate between a and b
         torch.cuda.synchronize()
+        sh.check_barrier_status()
+        if mode == "publish" and sh._flags is not None:
+            # a barrier that one rank never joins runs out (bounded wait) and reports which rank was missing
+            dist.barrier()
+            if rank == 0:
+                sh._epoch += 1
+                capi.rank_barrier(sh._flags.data_ptr(), sh._flags_mc, rank, world, sh._epoch, sh._status.data_ptr(), stream.cuda_stream, max_polls=20000)
+                torch.cuda.synchronize()
+                try:
+                    sh.check_barrier_status()
+                    timed_out = "no"
+                except RuntimeError as e:
+                    timed_out = str(e)
+            dist.barrier()
     np.save(os.path.join(out_dir, f"final_{rank}.npy"), xf.cpu().numpy())
     with open(os.path.join(out_dir, f"mode_{rank}.txt"), "w") as fh:
-        fh.write(sh._mode)
+        fh.write(f"{sh._mode};{'flags' if sh._flags is not None else 'nccl'};{timed_out}")
     del sh, a, b, xf
     for f, g in keep:
         g.close()
@@ -116,7 +136,7 @@ def _worker(rank, world, port, mode, out_dir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["allgather", "a2a", "multicast"])
+@pytest.mark.parametrize("mode", ["allgather", "a2a", "multicast", "publish"])
 def test_two_ranks_agree_with_one(mode, tmp_path):
     import torch.multiprocessing as mp
 
@@ -127,3 +147,7 @@ def test_two_ranks_agree_with_one(mode, tmp_path):
     f0, f1 = np.load(tmp_path / "final_0.npy"), np.load(tmp_path / "final_1.npy")
     assert np.array_equal(f0.view(np.uint32), f1.view(np.uint32)), "the ranks' replicas of x differ"
     assert np.max(np.abs(f0.astype(np.float64) - ref)) <= 1e-4 * np.max(np.abs(ref))
+    used = [open(tmp_path / f"mode_{r}.txt").read().split(";") for r in range(2)]
+    assert used[0][0] == used[1][0], used
+    if mode == "publish" and used[0][0] == "publish" and used[0][1] == "flags":
+        assert "rank 1" in used[0][2], used  # rank 0 waited for rank 1 in vain, and said so
