@@ -25,8 +25,11 @@ DEFAULT_GRAPH = {"dense": "dense sort 1073741824 | dense compress",
                  "subs": [{"graph": "S9_K9_s32", "nodes": ["tlb_nnz 32"], "template": "K9", "threads": 128, "row_reduce": 1}]}
 
 
-def graph_with_tlb_size(s: int) -> dict:
-    return {"dense": DEFAULT_GRAPH["dense"],
+def graph_with_tlb_size(s: int, sort: bool = True) -> dict:
+    """The one-kernel graph with `s` non-zeros per thread. Without the one-bin sort every row, empty or not, is
+    written (an empty row costs one stored zero), in row order and unpermuted: what the publishing kernels
+    need to send a warp's rows as one contiguous run of 16-byte multicast stores."""
+    return {"dense": DEFAULT_GRAPH["dense"] if sort else "dense compress",
             "subs": [{"graph": f"S9_K9_s{s}", "nodes": [f"tlb_nnz {s}"], "template": "K9", "threads": 128, "row_reduce": 1}]}
 
 
@@ -64,7 +67,17 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
         log(f"rows [{r0}, {r1}) nnz {nnz_local} generated in {gen_s:.1f} s")
 
     exchange = args.exchange if world > 1 else "none"
-    n_chunks = max(1, args.chunks if args.chunks > 0 else (1 if exchange in ("publish", "none") else 2))
+    if args.chunks > 0:
+        n_chunks = args.chunks
+    elif exchange in ("publish", "none"):
+        n_chunks = 1
+    elif exchange == "multicast":
+        # The store pass of a chunk costs in proportion to its rows, and only a rank's LAST pass is exposed: a rank
+        # cuts its block into one chunk per 1/(2 world) of all rows it owns (nnz-balanced blocks of a skewed matrix
+        # differ a hundred-fold in rows, so the hub ranks get one chunk and the rank with the sparse tail up to 8).
+        n_chunks = int(min(8, max(1, -(-(r1 - r0) * 2 * world // n))))
+    else:
+        n_chunks = 2  # the pairwise exchanges pair the c-th chunks of all ranks
     ctx = capi.Context(local_rank)
     t0 = time.perf_counter()
     cuts = partition_rows_by_nnz(m.indptr, n_chunks)
@@ -85,7 +98,8 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
         group_.close()
         del fmt_, group_, mc
     else:
-        desc = graph_with_tlb_size(args.tlb) if args.tlb else DEFAULT_GRAPH
+        sort = (exchange != "publish") if args.sort == "auto" else (args.sort == "yes")
+        desc = graph_with_tlb_size(args.tlb or 32, sort)
     fmts, groups, chunks = [], [], []
     build_error = None
     # most rows first: with a separate store pass the exchange of the last chunk is the only one no kernel hides
@@ -102,9 +116,9 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
         mc = m.row_slice(lo, hi) if n_chunks > 1 else m
         try:
             f, g = tuner.build(ctx, mc, desc)
-            if args.stage:
+            if args.stage or args.cap_log2:
                 for i in range(g.n):
-                    g.set_tuning(i, 0, 1)
+                    g.set_tuning(i, 0, (1 if args.stage else 0) | (args.cap_log2 << 4))
         except Exception as e:  # reported to every rank below, before anybody enters a collective
             build_error = e
             break

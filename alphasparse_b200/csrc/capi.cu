@@ -251,6 +251,14 @@ asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threa
         const int64_t needed = (int64_t)((p->units_for_grid + (uint64_t)threads - 1) / (uint64_t)threads);
         if (tblock > needed) tblock = needed > 0 ? needed : 1;
     }
+    if (t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE)
+    {
+        // these templates have no row-reduce phase; the third launch parameter selects their write-out instead:
+        // 1 = every finished row is stored on its own, 2 = the rows of a warp leave through shared memory as one run
+        if (reduce > 2) return fail(ASP_ERR_INVALID_ARG, "CSR5-like templates: thread_num_of_row_reduce is 1 (rows stored one by one) or 2 (staged write-out)");
+        p->args.path = (p->args.path & ~1) | (reduce == 2 ? 1 : 0);
+        p->args.row_reduce = reduce == 2 ? 2 : 1;
+    }
     if ((t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE) && threads > 256)
     {
         // compiled for at most 256 threads per CTA; the warp loop is grid-stride, so more CTAs
@@ -873,7 +881,8 @@ asp_status plan_group_build(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp
                     return r + d.first_row;
                 };
                 std::vector<uint32_t> rows(2 * W);
-#pragma omp parallel for schedule(static)
+                uint64_t all_starts = 0;
+#pragma omp parallel for schedule(static) reduction(+ : all_starts)
                 for (int64_t w = 0; w < (int64_t)W; w++)
                 {
                     uint64_t starts = 0;
@@ -886,6 +895,15 @@ asp_status plan_group_build(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp
                     const uint64_t R0 = fr.get(w);
                     rows[2 * w] = (uint32_t)row_of(R0);
                     rows[2 * w + 1] = (uint32_t)row_of(R0 + (starts ? starts - 1 : 0));
+                    all_starts += starts;
+                }
+                // staging area of the staged write-out: room for twice the average number of rows a warp produces
+                // (a power of two between 32 and 256; warps with more rows send the rest straight out)
+                {
+                    const uint64_t avg = W ? all_starts / W : 1;
+                    uint64_t cap = 32;
+                    while (cap < 2 * avg && cap < 256) cap <<= 1;
+                    a.stage_cap = (int)std::min<uint64_t>(cap, 32ull * S);
                 }
                 rows.erase(std::unique(rows.begin(), rows.end()), rows.end());
                 std::shared_ptr<Arena> er(new (std::nothrow) Arena());
@@ -997,7 +1015,14 @@ asp_status asp_plan_set_tuning(asp_plan *plan, int vec, int path)
     if (t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || t == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE)
     {
         if (vec != 0) return fail(ASP_ERR_INVALID_ARG, "the CSR5-like family has no vec knob");
-        if (path >= 0) plan->args.path = path & 1;
+        if (path >= 0)
+        {
+            // bit 0: staged write-out; bits 4..7 (optional): log2 of the rows per warp that are staged
+            plan->args.path = path & 1;
+            plan->args.row_reduce = (path & 1) ? 2 : 1;
+            const int lg = (path >> 4) & 0xf;
+            if (lg) plan->args.stage_cap = (int)std::min<uint64_t>(1ull << lg, 32ull * plan->args.tlb_size);
+        }
         return ASP_OK;
     }
     if (t != ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS && t != ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS)
@@ -1152,7 +1177,7 @@ asp_status asp_spmv_publish(asp_ctx *ctx, asp_plan *const *plans, int n_plans, c
         if (p->templ == ASP_EMPTY_TEMPLATE) continue;
         const bool csr5 = p->templ == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || p->templ == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE;
         if (!csr5 || !p->end_rows || p->args.atomic || !asp::csr5_specialised((int)p->args.tlb_size, p->col_width, p->args.bits_word))
-            return fail(ASP_ERR_UNSUPPORTED, "publishing SpMV: every plan must be a CSR5-like template with TLB size 4, 8, 16 or 32 and 16- or 32-bit columns");
+            return fail(ASP_ERR_UNSUPPORTED, "publishing SpMV: every plan must be a CSR5-like template with TLB size 4, 8, 16 or 32 and 32-bit columns");
     }
     ASP_ON_DEVICE(ctx);
     // the three steps of every plan run back to back on the context's stream

@@ -99,8 +99,9 @@ std::vector<Candidate> compressed_candidates(uint64_t mn_, uint64_t mx_, double 
         }
         for (int64_t s : ss)
         {
-            out.push_back({"S9_K9_s" + std::to_string(s), {"tlb_nnz " + std::to_string(s)}, "K9", cross(T2, {1})});
-            out.push_back({"S9_K10_s" + std::to_string(s), {"tlb_nnz " + std::to_string(s)}, "K10", cross(T2, {1})});
+            // (third launch parameter of the CSR5-like templates: 1 = rows stored one by one, 2 = staged write-out)
+            out.push_back({"S9_K9_s" + std::to_string(s), {"tlb_nnz " + std::to_string(s)}, "K9", cross(T2, {1, 2})});
+            out.push_back({"S9_K10_s" + std::to_string(s), {"tlb_nnz " + std::to_string(s)}, "K10", cross(T2, {1, 2})});
         }
     }
     if (mn >= 30 && mx <= 512)

@@ -74,6 +74,7 @@ struct KArgs
     int row_reduce; // thread_num_of_row_reduce
     int bits_word, bits_flag, bits_row, bits_off;
     int warps_first_row_len; // length of the WLB first-row array (K10 has a +1 sentinel)
+    int stage_cap;           // CSR5-like, staged write-out: rows per warp that go through shared memory (the rest go straight out)
     int path;                // kernel-specific walk: SELL-like 0 = warp tasks when strips are equal, 1 = one CTA per strip;
                              // CSR5-like 1 = the row sums of a warp go through shared memory and out as one contiguous run
 };

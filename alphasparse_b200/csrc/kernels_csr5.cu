@@ -137,24 +137,35 @@ __device__ __forceinline__ void put(VT *y, u64 row, VT v, bool atomic)
 
 // MODE bit 0: WARP_FAST (second CSR5-like template: a warp that lies inside one row takes a butterfly
 // reduction), bit 1: STAGE (row sums through shared memory, contiguous write-out), bit 2: PUBLISH
-// (contiguous write-out through the multicast address; implies STAGE and unpermuted rows)
-template <class VT, class CT, int S, int MODE>
+// (write-out through the multicast address; implies STAGE). B: elements per load batch. BRANCHY: the walk
+// over the row-start flags branches per flagged element instead of running predicated straight-line code.
+template <class VT, class CT, int S, int MODE, int B, bool BRANCHY>
 __global__ void __launch_bounds__(256) k_csr5s(const KArgs a)
 {
     constexpr bool WARP_FAST = (MODE & 1) != 0, STAGE = (MODE & 2) != 0, PUBLISH = (MODE & 4) != 0;
-    constexpr int B = S < 16 ? S : 16; // elements per load batch
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const VT *__restrict__ val = (const VT *)a.val;
     const CT *__restrict__ col = (const CT *)a.col;
     const VT *__restrict__ x = (const VT *)a.x + a.first_col;
     VT *__restrict__ y = (VT *)a.y;
+    VT *__restrict__ ymc = (VT *)a.y_mc;
     const u32 lane = threadIdx.x & 31;
     const int fshift = a.bits_word - S; // the S flags are the top bits of the word
     const u64 rmask = (1ull << a.bits_row) - 1, omask = (1ull << a.bits_off) - 1;
     const bool all_atomic = a.atomic != 0;
-    // staging area of this warp: one slot per row the warp can produce
-    VT *stage = STAGE ? reinterpret_cast<VT *>(smem_raw) + (size_t)(threadIdx.x >> 5) * (32 * S) : nullptr;
+    // staging area of this warp: the first `cap` rows a warp produces go through it, later ones straight out
+    const u32 cap = STAGE ? (u32)a.stage_cap : 0u;
+    VT *stage = STAGE ? reinterpret_cast<VT *>(smem_raw) + (size_t)(threadIdx.x >> 5) * cap : nullptr;
     const u64 wstride = ((u64)gridDim.x * blockDim.x) >> 5;
+
+    // a finished row sum that does not go through the staging area
+    auto out = [&](u64 rel_row, VT v, bool atomic) {
+        const u64 r = row_of(a, rel_row);
+        if (atomic) atomicAdd(y + r, v); // result unused: red.global.add
+        else if (PUBLISH) mc_store(ymc + r, v);
+        else y[r] = v;
+    };
+
     for (u64 w = ((u64)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < a.n_units; w += wstride)
     {
         const u64 R0 = mget5(a.m[MS_ROW_OF_UNIT], w);
@@ -193,7 +204,8 @@ __global__ void __launch_bounds__(256) k_csr5s(const KArgs a)
         u32 yo = frow;
         bool seen = false;
         VT sum = 0, tail = 0;
-#pragma unroll
+        // (the batch loop stays rolled: unrolling it for S = 32 quadruples the code without gaining anything)
+#pragma unroll 1
         for (int k0 = 0; k0 < S; k0 += B)
         {
             u32 c[B];
@@ -206,21 +218,43 @@ __global__ void __launch_bounds__(256) k_csr5s(const KArgs a)
             for (int u = 0; u < B; u++) xv[u] = ld_x(x + c[u]);
 #pragma unroll
             for (int u = 0; u < B; u++) p[u] *= xv[u];
-            // straight-line walk: a row that ends inside the thread is emitted under a predicate
 #pragma unroll
             for (int u = 0; u < B; u++)
             {
                 const bool f = (F >> (k0 + u)) & 1u;
-                const bool e = f && seen;
-                if (e)
+                if (BRANCHY)
                 {
-                    if (STAGE) stage[yo] = sum;
-                    else put(y, row_of(a, R0 + yo), sum, all_atomic || (lane == 0 && yo == frow));
+                    if (f)
+                    {
+                        if (seen)
+                        {
+                            // a row that starts and ends inside this thread; only the warp's very first row can
+                            // also receive sums from the previous warp
+                            if (STAGE && yo < cap) stage[yo] = sum;
+                            else out(R0 + yo, sum, all_atomic || (lane == 0 && yo == frow));
+                            yo++;
+                        }
+                        else
+                            tail = sum;
+                        seen = true;
+                        sum = 0;
+                    }
+                    sum += p[u];
                 }
-                yo += e ? 1u : 0u;
-                tail = (f && !seen) ? sum : tail;
-                seen = seen || f;
-                sum = f ? p[u] : sum + p[u];
+                else
+                {
+                    // straight-line walk: a row that ends inside the thread is emitted under a predicate
+                    const bool e = f && seen;
+                    if (e)
+                    {
+                        if (STAGE && yo < cap) stage[yo] = sum;
+                        else out(R0 + yo, sum, all_atomic || (lane == 0 && yo == frow));
+                    }
+                    yo += e ? 1u : 0u;
+                    tail = (f && !seen) ? sum : tail;
+                    seen = seen || f;
+                    sum = f ? p[u] : sum + p[u];
+                }
             }
         }
         if (!seen) tail = sum;
@@ -237,40 +271,42 @@ __global__ void __launch_bounds__(256) k_csr5s(const KArgs a)
         }
         VT extra = __shfl_down_sync(0xffffffffu, sc, 1);
         if (lane == 31) extra = 0;
-        if (!STAGE)
+        if (seen)
         {
-            if (seen) put(y, row_of(a, R0 + yo), sum + extra, all_atomic || (lane == 0 && yo == frow) || (lane + roff == 31));
-            continue;
+            // the last row this thread starts; it is the warp's last row when no later lane starts one
+            if (STAGE && yo < cap) stage[yo] = sum + extra;
+            else out(R0 + yo, sum + extra, all_atomic || (lane == 0 && yo == frow) || (lane + roff == 31));
         }
-        // ---- staged write-out: rows R0 .. R0 + nrows - 1 are in stage[0 .. nrows)
-        if (seen) stage[yo] = sum + extra;
-        // the last row-starting lane holds the warp's last row
+        if (!STAGE) continue;
+        // ---- staged write-out: rows R0 .. R0 + min(nrows, cap) - 1 are in stage[]
         const u32 last_head = 31 - __clz(heads); // heads has bit 0 set: every warp starts with a flag
         const u32 nrows = __shfl_sync(0xffffffffu, yo, last_head) + 1;
+        const u32 nst = nrows < cap ? nrows : cap;
         __syncwarp();
         if (all_atomic)
         {
-            for (u32 j = lane; j < nrows; j += 32) atomicAdd(y + row_of(a, R0 + j), stage[j]);
+            for (u32 j = lane; j < nst; j += 32) atomicAdd(y + row_of(a, R0 + j), stage[j]);
         }
         else
         {
-            // the end rows may continue in the neighbouring warps
+            // the warp's first and last row may continue in the neighbouring warps
             if (lane == 0) atomicAdd(y + row_of(a, R0), stage[0]);
-            if (lane == 1 && nrows > 1) atomicAdd(y + row_of(a, R0 + nrows - 1), stage[nrows - 1]);
+            if (lane == 1 && nrows > 1 && nrows <= cap) atomicAdd(y + row_of(a, R0 + nrows - 1), stage[nrows - 1]);
+            const u32 jend = nrows <= cap ? nrows - 1 : cap; // one past the last staged row that is not an end row
             if (PUBLISH && a.sort_kind != 0)
             {
                 // permuted rows: one multicast store per row (a stable partition keeps them ascending)
-                for (u32 j = 1 + lane; j + 1 < nrows; j += 32) mc_store((VT *)a.y_mc + row_of(a, R0 + j), stage[j]);
+                for (u32 j = 1 + lane; j < jend; j += 32) mc_store(ymc + row_of(a, R0 + j), stage[j]);
             }
             else if (PUBLISH)
             {
                 // unpermuted rows: y[first_row + R0 + j], and the same offset behind the multicast address
-                VT *mc = (VT *)a.y_mc + a.first_row + R0;
+                VT *mc = ymc + a.first_row + R0;
                 if constexpr (sizeof(VT) == 4)
                 {
                     // 16-byte multicast stores where the run allows it
                     const u32 g0 = (u32)(((uintptr_t)(mc + 1) >> 2) & 3); // position of the first interior row inside its 16 bytes
-                    const u32 n_in = nrows > 2 ? nrows - 2 : 0;
+                    const u32 n_in = jend > 1 ? jend - 1 : 0;
                     const u32 head = ((4 - g0) & 3) < n_in ? ((4 - g0) & 3) : n_in;
                     const u32 body = (n_in - head) >> 2;
                     if (lane < head) mc_store(mc + 1 + lane, stage[1 + lane]);
@@ -280,16 +316,16 @@ __global__ void __launch_bounds__(256) k_csr5s(const KArgs a)
                         mc_store4(mc + j, stage[j], stage[j + 1], stage[j + 2], stage[j + 3]);
                     }
                     const u32 t0 = 1 + head + 4 * body;
-                    if (t0 + lane < nrows - 1 && n_in) mc_store(mc + t0 + lane, stage[t0 + lane]);
+                    if (t0 + lane < jend) mc_store(mc + t0 + lane, stage[t0 + lane]);
                 }
                 else
                 {
-                    for (u32 j = 1 + lane; j + 1 < nrows; j += 32) mc_store(mc + j, stage[j]);
+                    for (u32 j = 1 + lane; j < jend; j += 32) mc_store(mc + j, stage[j]);
                 }
             }
             else
             {
-                for (u32 j = 1 + lane; j + 1 < nrows; j += 32) y[row_of(a, R0 + j)] = stage[j];
+                for (u32 j = 1 + lane; j < jend; j += 32) y[row_of(a, R0 + j)] = stage[j];
             }
         }
         __syncwarp(); // the next warp task of this warp reuses the staging area
@@ -297,19 +333,12 @@ __global__ void __launch_bounds__(256) k_csr5s(const KArgs a)
     if (PUBLISH) __threadfence_system();
 }
 
-template <class VT, class CT, int S>
-cudaError_t launch_s(int mode, const KArgs &a, unsigned grid, unsigned block, cudaStream_t st)
+template <class VT, class CT, int S, int B, bool BRANCHY>
+cudaError_t launch_sb(int mode, const KArgs &a, unsigned grid, unsigned block, cudaStream_t st)
 {
-    const size_t smem = (mode & 2) ? (size_t)(block / 32) * 32 * S * sizeof(VT) : 0;
-#define ASP_CSR5_MODE(M)                                                                                         \
-    case M:                                                                                                      \
-        if (smem > 48 * 1024)                                                                                    \
-        {                                                                                                        \
-            cudaError_t e = cudaFuncSetAttribute(k_csr5s<VT, CT, S, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            if (e != cudaSuccess) return e;                                                                      \
-        }                                                                                                        \
-        k_csr5s<VT, CT, S, M><<<grid, block, smem, st>>>(a);                                                     \
-        break;
+    const size_t smem = (mode & 2) ? (size_t)(block / 32) * a.stage_cap * sizeof(VT) : 0;
+#define ASP_CSR5_MODE(M)                                                       \
+    case M: k_csr5s<VT, CT, S, M, B, BRANCHY><<<grid, block, smem, st>>>(a); break;
     switch (mode)
     {
         ASP_CSR5_MODE(0)
@@ -322,6 +351,16 @@ cudaError_t launch_s(int mode, const KArgs &a, unsigned grid, unsigned block, cu
     }
 #undef ASP_CSR5_MODE
     return cudaGetLastError();
+}
+
+template <class VT, class CT, int S>
+cudaError_t launch_s(int mode, const KArgs &a, unsigned grid, unsigned block, cudaStream_t st)
+{
+    // Load batches, measured on a power-law matrix with random columns and on R-MAT: 8 elements in flight per
+    // thread are best when rows go straight out (more CTAs fit), 16 with the staged write-out; a branch per
+    // flagged element never beat the predicated walk by more than 1 %.
+    if (mode & 2) return launch_sb<VT, CT, S, (S < 16 ? S : 16), false>(mode, a, grid, block, st);
+    return launch_sb<VT, CT, S, (S < 8 ? S : 8), false>(mode, a, grid, block, st);
 }
 
 template <class VT, class CT>
@@ -359,15 +398,17 @@ __global__ void __launch_bounds__(256) k_publish_rows(const VT *__restrict__ y, 
 
 bool csr5_specialised(int tlb_size, int col_width, int bits_word)
 {
-    return (tlb_size == 4 || tlb_size == 8 || tlb_size == 16 || tlb_size == 32) && (col_width == 2 || col_width == 4) && bits_word - tlb_size >= 0;
+    return (tlb_size == 4 || tlb_size == 8 || tlb_size == 16 || tlb_size == 32) && col_width == 4 && bits_word - tlb_size >= 0;
 }
 
 cudaError_t launch_csr5(int val_is_f64, int col_width, int mode, const KArgs &a, unsigned grid, unsigned block, cudaStream_t st)
 {
     const int S = (int)a.tlb_size;
-    if (val_is_f64)
-        return col_width == 2 ? launch_vc5<double, unsigned short>(S, mode, a, grid, block, st) : launch_vc5<double, unsigned int>(S, mode, a, grid, block, st);
-    return col_width == 2 ? launch_vc5<float, unsigned short>(S, mode, a, grid, block, st) : launch_vc5<float, unsigned int>(S, mode, a, grid, block, st);
+    if (a.stage_cap <= 0) mode &= ~2; // no staging area configured: rows go straight out
+    if ((mode & 4) && !(mode & 2)) return cudaErrorInvalidValue;
+    if (col_width != 4) return cudaErrorInvalidValue;
+    if (val_is_f64) return launch_vc5<double, unsigned int>(S, mode, a, grid, block, st);
+    return launch_vc5<float, unsigned int>(S, mode, a, grid, block, st);
 }
 
 cudaError_t launch_zero_rows(int val_is_f64, void *y, const unsigned *rows, unsigned long long n, cudaStream_t st)

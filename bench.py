@@ -52,7 +52,7 @@ WORKLOADS = {
 COMMITTED_GRAPHS = {
     "c1": {"dense": "dense compress", "subs": [{"graph": "S5_K3", "nodes": ["row_padding 32 1", "tlb_row"], "template": "K3", "threads": 128, "row_reduce": 1}]},
     "c2": {"dense": "dense compress", "subs": [{"graph": "S5_K3", "nodes": ["row_padding 32 1", "tlb_row"], "template": "K3", "threads": 128, "row_reduce": 1}]},
-    "c3": {"dense": "dense compress", "subs": [{"graph": "S9_K9_s16", "nodes": ["tlb_nnz 16"], "template": "K9", "threads": 128, "row_reduce": 1}]},
+    "c3": {"dense": "dense compress", "subs": [{"graph": "S9_K9_s16", "nodes": ["tlb_nnz 16"], "template": "K9", "threads": 128, "row_reduce": 2}]},
     "c4": {"dense": "dense compress", "subs": [{"graph": "S1_K2_m128", "nodes": ["row_padding 128 1", "blb_row_evenly 128", "tlb_row"], "template": "K2", "threads": 256, "row_reduce": 1}]},
 }
 COMMITTED_GRAPHS["c4s"] = COMMITTED_GRAPHS["c4"]
@@ -607,6 +607,9 @@ def main():
     ap.add_argument("--balance", default="nnz", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
                     "or a number w (a row with non-zeros weighs w non-zeros)")
     ap.add_argument("--tlb", type=int, default=0, help="c5: non-zeros per thread of the CSR5-like format (default 32)")
+    ap.add_argument("--sort", default="auto", choices=["auto", "yes", "no"], help="c5: put the rows without non-zeros last (a one-bin coarse sort) so that the format drops them; auto = "
+                    "yes, except with the publishing kernels, which send unpermuted rows as contiguous 16-byte multicast stores")
+    ap.add_argument("--cap-log2", type=int, default=0, help="CSR5-like plans: log2 of the rows per warp that go through shared memory (0: chosen at plan creation)")
     ap.add_argument("--stage", action="store_true", help="CSR5-like plans: row sums of a warp through shared memory, contiguous write-out")
     ap.add_argument("--search", action="store_true", help="c5: run the quick search instead of the default one-kernel graph")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])

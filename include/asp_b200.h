@@ -167,7 +167,11 @@ void asp_plan_destroy(asp_plan *plan);
 asp_status asp_plan_descs_validate(const asp_plan_desc *descs, int n);
 
 /* replaces re-emitting + recompiling the program for every launch-parameter trial
- * (default_auto_tuner.cc:449-2030): tblock_num / thread_num_in_block / thread_num_of_row_reduce. */
+ * (default_auto_tuner.cc:449-2030): tblock_num / thread_num_in_block / thread_num_of_row_reduce.
+ * The two CSR5-like templates have no row-reduce phase; for them the third parameter selects the
+ * write-out: 1 = every finished row is stored on its own (what the reference's kernel does), 2 = the rows
+ * of a warp are collected in shared memory and leave as one contiguous run (an extension of the launch
+ * space for sm_100a; which one is faster depends on the matrix, so the search times both). */
 asp_status asp_plan_set_launch(asp_plan *plan, int64_t tblock_num, int64_t thread_num_in_block, int64_t thread_num_of_row_reduce);
 /* The launch asp_spmv will actually use. The kernels are compiled for a bounded CTA width per family
  * (ELL-like 512, SELL-like and CSR5-like 256 threads) and never launch CTAs without work, so a request
@@ -176,11 +180,13 @@ asp_status asp_plan_set_launch(asp_plan *plan, int64_t tblock_num, int64_t threa
  * no such query: its launch is the literal it printed into the program (code_of_kernal_function_call,
  * e.g. direct_atom_op_warp_block_compress.cc:1012-1040). Any pointer may be NULL. */
 asp_status asp_plan_get_launch(const asp_plan *plan, int64_t *tblock_num, int64_t *thread_num_in_block, int64_t *thread_num_of_row_reduce);
-/* Work decomposition knobs of the ELL-like and SELL-like families, for launch-space experiments (the
- * defaults are what the measurements in this repository use): `vec` = TLBs per thread (1, 2, 4, 8 for
- * ELL-like; 1, 2, 4 for SELL-like; 0 keeps the current value), `path` (SELL-like only; -1 keeps) 0 = warp
- * tasks over equal strips, 1 = one CTA per strip. Re-applies the last requested launch. No counterpart in
- * the reference (its generated kernels handle one TLB per thread). */
+/* Work decomposition knobs, for launch-space experiments (the defaults are what the measurements in this
+ * repository use): `vec` = TLBs per thread (1, 2, 4, 8 for ELL-like; 1, 2, 4 for SELL-like; 0 keeps the
+ * current value), `path` (-1 keeps): SELL-like 0 = warp tasks over equal strips, 1 = one CTA per strip;
+ * CSR5-like bit 0 = staged write-out (the same switch as thread_num_of_row_reduce = 2), bits 4..7 = log2
+ * of the rows per warp that go through shared memory (0 keeps the size chosen at plan creation).
+ * Re-applies the last requested launch. No counterpart in the reference (its generated kernels handle
+ * one TLB per thread). */
 asp_status asp_plan_set_tuning(asp_plan *plan, int vec, int path);
 /* bytes of device memory the plan's format arrays occupy (B_fmt without x and y) */
 uint64_t asp_plan_format_bytes(const asp_plan *plan);

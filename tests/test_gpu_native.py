@@ -142,9 +142,9 @@ def test_csr5_like_kernels_for_every_tlb_size_direct_and_staged(asp_ctx, mats, m
     g = fmt.upload(asp_ctx)
     y_ref, scale = refdump.csr_ref(m, x)
     for path in (0, 1):
-        g.set_tuning(0, 0, path)
         for threads in (64, 256):
-            tuner.set_launch(fmt, g, 0, threads, 1)
+            tuner.set_launch(fmt, g, 0, threads, 1 + path)  # third launch parameter: 1 = row by row, 2 = staged write-out
+            assert g.get_launch(0)[2] == 1 + path
             refdump.assert_y(g.spmv_host(x), y_ref, scale, m.values.dtype, f"{mat} {templ} s={s} path={path} threads={threads}")
     g.close()
     fmt.close()

@@ -20,7 +20,7 @@ def _chunks(ctx, blk, n_chunks, keep):
     out = []
     for c in sorted(range(n_chunks), key=lambda c: -(int(cuts[c + 1]) - int(cuts[c]))):
         lo, hi = int(cuts[c]), int(cuts[c + 1])
-        f, g = tuner.build(ctx, blk.row_slice(lo, hi), bench_rmat.DEFAULT_GRAPH)
+        f, g = tuner.build(ctx, blk.row_slice(lo, hi), bench_rmat.DEFAULT_GRAPH if (c & 1) == 0 else bench_rmat.graph_with_tlb_size(16, sort=False))
         keep.append((f, g))
 
         def fn(xt, yt, g=g):
@@ -86,6 +86,13 @@ def _free_port():
     return p
 
 
+def _two_rank_matrix():
+    # more than 65536 columns, so that the column indices are 32 bits wide (what the publishing kernels take)
+    m, x = M.rmat(17, 8, seed=4)
+    m.values *= 0.03
+    return m, x
+
+
 def _worker(rank, world, port, mode, out_dir):
     import torch.distributed as dist
 
@@ -93,8 +100,7 @@ def _worker(rank, world, port, mode, out_dir):
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-    m, x = M.rmat(13, 16, seed=4)
-    m.values *= 0.02
+    m, x = _two_rank_matrix()
     bounds = partition_rows_by_nnz(m.indptr, world)
     blk = m.row_slice(int(bounds[rank]), int(bounds[rank + 1]))
     ctx = capi.Context(rank)
@@ -141,8 +147,7 @@ def test_two_ranks_agree_with_one(mode, tmp_path):
     import torch.multiprocessing as mp
 
     mp.spawn(_worker, args=(2, _free_port(), mode, str(tmp_path)), nprocs=2, join=True)
-    m, x = M.rmat(13, 16, seed=4)
-    m.values *= 0.02
+    m, x = _two_rank_matrix()
     ref = _reference_iterations(m, x, 3)
     f0, f1 = np.load(tmp_path / "final_0.npy"), np.load(tmp_path / "final_1.npy")
     assert np.array_equal(f0.view(np.uint32), f1.view(np.uint32)), "the ranks' replicas of x differ"
