@@ -180,6 +180,8 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
         c1.record(stream)
         c1.synchronize()
         ms_compute = c0.elapsed_time(c1) / iters
+        if log:
+            log(f"rows {r1 - r0} nnz {nnz_local} chunks {n_chunks} compute-only {ms_compute:.4f} ms per SpMV; timed {ms_total / K / iters:.4f} ms per SpMV")
     nnz_total = torch.tensor([nnz_local], dtype=torch.int64, device=dev)
     t = torch.tensor([ms_total, ms_compute, float(np.median(per_step))], device=dev)
     if dist:

@@ -55,6 +55,98 @@ std::vector<Launch> cross(const std::vector<int64_t> &threads, const std::vector
     return l;
 }
 
+// ---- the reference's node-parameter grids (whilte_list_path_impl.cc), one function per strategy ------------
+// `mode`: 1 = quick (one or two points per strategy, short launch sweeps), 0 = the reference's grids plus the
+// extensions of this build (marked below), 2 = the reference's grids exactly (what the enumeration test compares
+// with the reference's own tuner). In modes 0 and 2 the launch sweep of a point is derived from the lowered
+// format (reference_launches), as default_auto_tuner.cc does; Candidate::launches is then only the fallback.
+std::vector<Candidate> reference_candidates(int64_t mn, int64_t mx, uint64_t rows, uint64_t nnz, bool is_sorted, bool extensions)
+{
+    std::vector<Candidate> out;
+    const std::vector<Launch> none;
+    auto S = [](int64_t v) { return std::to_string(v); };
+    if (mn >= 128)
+    {
+        // strategy 8 (:2838-2867): BLB_COL_DIV(c), c = 128, 256, ... <= min(4096, ceil32(max))
+        int64_t hi = std::min<int64_t>(4096, ceil32(mx));
+        hi = std::max<int64_t>(hi, 128);
+        for (int64_t c = 128; c <= hi; c *= 2) out.push_back({"S8_K7_c" + S(c), {"blb_col_fixed " + S(c)}, "K7", none});
+    }
+    if (mx <= 512)
+    {
+        // strategy 1 (:228): ROW_PADDING(m, 1) -> BLB_ROW_DIV(evenly m) -> TLB_ROW_DIV, m = 64 .. 256 step 64
+        for (int64_t mm : integer_range(64, 256, 64))
+            out.push_back({"S1_K2_m" + S(mm), {"row_padding " + S(mm) + " 1", "blb_row_evenly " + S(mm), "tlb_row"}, "K2", none});
+        // strategy 5 (:1806-1813): ROW_PADDING(32, 1) -> TLB_ROW_DIV
+        out.push_back({"S5_K3", {"row_padding 32 1", "tlb_row"}, "K3", none});
+    }
+    if (!is_sorted)
+    {
+        // strategy 9 (:3119-3176): TLB_NNZ_DIV(s), s = 2 .. clamp(floor(nnz / rows), 2, 32) in steps of a quarter of the range
+        int64_t avg = rows ? (int64_t)(nnz / rows) : 2;
+        avg = std::min<int64_t>(32, std::max<int64_t>(2, avg));
+        const int64_t step = std::max<int64_t>(1, (avg - 2) / 4);
+        std::set<int64_t> ss;
+        for (int64_t v : integer_range(2, avg, step)) ss.insert(v);
+        if (extensions)
+        {
+            // (extension) long rows make the 2..avg range too narrow for the loads of a thread to cover the memory latency
+            if (mx > 512) ss.insert(8), ss.insert(16);
+            ss.insert(32);
+        }
+        for (int64_t v : ss)
+        {
+            out.push_back({"S9_K9_s" + S(v), {"tlb_nnz " + S(v)}, "K9", none});
+            out.push_back({"S9_K10_s" + S(v), {"tlb_nnz " + S(v)}, "K10", none});
+        }
+    }
+    if (mn >= 30 && mx <= 512)
+    {
+        // strategy 4 (:1483-1520): WLB_COL_DIV(c), c = 32 .. (first grid point >= max) in steps of ceil32((max - min) / 3)
+        int64_t step = (mx - mn) / 3;
+        if (step % 32) step = (step / 32 + 1) * 32;
+        step = std::max<int64_t>(32, step);
+        int64_t up = 32;
+        while (up < mx) up += step;
+        for (int64_t c : integer_range(32, up, step)) out.push_back({"S4_K4_c" + S(c), {"wlb_col_fixed " + S(c)}, "K4", none});
+    }
+    if (mn >= 32 && mx <= 1024)
+    {
+        // strategy 6 (:2093-2127): ROW_PADDING(m, min row nnz) -> BLB_ROW_DIV(evenly m) -> WLB_COL_DIV(c), m = 2, 4 (fastest), c = 32 .. F step 32
+        int64_t F = mx / 2;
+        if (F % 32) F = (F / 32 + 1) * 32;
+        F = std::max<int64_t>(32, std::min<int64_t>(128, F));
+        for (int64_t c : integer_range(32, F, 32))
+            for (int64_t mm : {2, 4})
+                out.push_back({"S6_K8_m" + S(mm) + "_c" + S(c), {"row_padding " + S(mm) + " " + S(mn), "blb_row_evenly " + S(mm), "wlb_col_fixed " + S(c)}, "K8", none});
+        // strategy 7 (:2481-2530): BLB_ROW_DIV(nnz >= b) -> WLB_COL_DIV(c), b = 128, 512, 896; c = 32 .. ceil32(min(b / 2, max / 2, 128)) step 32
+        for (int64_t bb : integer_range(128, 1024, 384))
+        {
+            int64_t U = std::min<int64_t>(std::min<int64_t>(bb / 2, mx / 2), 128);
+            if (U % 32) U = (U / 32 + 1) * 32;
+            for (int64_t c = 32; c <= U; c += 32)
+                out.push_back({"S7_K8_b" + S(bb) + "_c" + S(c), {"blb_row_nnz " + S(bb), "wlb_col_fixed " + S(c)}, "K8", none});
+        }
+    }
+    if (mx <= 1024)
+    {
+        // strategy 2 (:613-643): ROW_PADDING(m, min row nnz) -> BLB_ROW_DIV(evenly m) -> TLB_COL_DIV(c), m = 32, 64 (fastest), c = 1 .. min(16, ceil(max / 2)) step 3
+        const int64_t F = std::min<int64_t>(16, (mx + 1) / 2);
+        for (int64_t c : integer_range(1, F, 3))
+            for (int64_t mm : {32, 64})
+                out.push_back({"S2_K6_m" + S(mm) + "_c" + S(c), {"row_padding " + S(mm) + " " + S(std::max<int64_t>(1, mn)), "blb_row_evenly " + S(mm), "tlb_col_fixed " + S(c)}, "K6", none});
+        // strategy 3 (:1072-1110): BLB_ROW_DIV(nnz >= b) -> TLB_COL_DIV(c), b = 128, 512, 896; c = 1, 1 + max(1, b / 192), ... <= min(max(1, b / 64), max / 2 (+1 when max is even))
+        const int64_t maxcol = mx / 2 + ((mx % 2 == 0) ? 1 : 0);
+        for (int64_t bb : integer_range(128, 1024, 384))
+        {
+            const int64_t up = std::max<int64_t>(1, bb / 64), st = std::max<int64_t>(1, bb / 192);
+            for (int64_t c = 1; c <= up && c <= maxcol; c += st)
+                out.push_back({"S3_K6_b" + S(bb) + "_c" + S(c), {"blb_row_nnz " + S(bb), "tlb_col_fixed " + S(c)}, "K6", none});
+        }
+    }
+    return out;
+}
+
 std::vector<Candidate> compressed_candidates(uint64_t mn_, uint64_t mx_, double avg, bool is_sorted, bool quick)
 {
     const int64_t mn = (int64_t)mn_, mx = (int64_t)mx_;
@@ -142,6 +234,135 @@ std::vector<Candidate> compressed_candidates(uint64_t mn_, uint64_t mx_, double 
                     out.push_back({"S3_K6_b" + std::to_string(bb) + "_c" + std::to_string(c), {"blb_row_nnz " + std::to_string(bb), "tlb_col_fixed " + std::to_string(c)}, "K6", cross(T2, {1, 4, 16})});
     }
     return out;
+}
+
+// ---- the reference's launch sweeps (default_auto_tuner.cc), derived from the lowered format ----------------
+struct ArrView
+{
+    const asp_array_desc *d = nullptr;
+    uint64_t len() const { return d ? d->len : 0; }
+    uint64_t get(uint64_t i) const
+    {
+        switch (d->compress)
+        {
+        case ASP_COMPRESS_NONE:
+            switch (d->dtype)
+            {
+            case ASP_U8: return ((const uint8_t *)d->host_ptr)[i];
+            case ASP_U16: return ((const uint16_t *)d->host_ptr)[i];
+            case ASP_U32: return ((const uint32_t *)d->host_ptr)[i];
+            default: return ((const uint64_t *)d->host_ptr)[i];
+            }
+        case ASP_COMPRESS_LINEAR: return i * d->coef + d->icpt;
+        case ASP_COMPRESS_CONSTANT: return d->icpt;
+        case ASP_COMPRESS_CYCLE_LINEAR: return (i % d->cycle) * d->coef + d->icpt;
+        case ASP_COMPRESS_CYCLE_INCREASE: return i / d->cycle + d->icpt;
+        default:
+        {
+            uint64_t v = d->branch_val[0];
+            for (int b = 1; b < d->n_branch; b++)
+                if (i > d->branch_hi[b - 1]) v = d->branch_val[b];
+            return v;
+        }
+        }
+    }
+};
+ArrView role_of(const asp_plan_desc &d, int role)
+{
+    ArrView v;
+    for (int i = 0; i < d.n_arrays; i++)
+        if (d.arrays[i].role == role) v.d = &d.arrays[i];
+    return v;
+}
+// smallest and largest difference of consecutive entries of a CSR-like offset array
+void min_max_diff(const ArrView &a, uint64_t init_min, uint64_t &mn, uint64_t &mx)
+{
+    mn = init_min;
+    mx = 0;
+    for (uint64_t i = 0; i + 1 < a.len(); i++)
+    {
+        const uint64_t d = a.get(i + 1) - a.get(i);
+        mn = std::min(mn, d);
+        mx = std::max(mx, d);
+    }
+}
+// thread_num_in_block from `lo` to `hi` in at most `parts` steps that are multiples of 32
+std::vector<int64_t> thread_range(uint64_t lo, uint64_t hi, uint64_t parts)
+{
+    uint64_t step = (hi - lo) / parts;
+    if (step % 32) step = (step / 32 + 1) * 32;
+    step = std::max<uint64_t>(32, step);
+    return integer_range((int64_t)lo, (int64_t)hi, (int64_t)step);
+}
+uint64_t floor32_clamped(uint64_t v) { return std::min<uint64_t>(1024, std::max<uint64_t>(32, v / 32 * 32)); }
+
+// false: the reference skips the template on this format altogether
+bool reference_launches(int templ, const asp_plan_desc &d, const asp_sub_info &info, uint64_t max_tblock, std::vector<Launch> &out)
+{
+    out.clear();
+    uint64_t mn = 0, mx = 0;
+    switch (templ)
+    {
+    case ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS: // :465
+        out = cross(integer_range(32, 256, 32), {1});
+        return true;
+    case ASP_DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE: // :849
+        out = cross(integer_range(32, 512, 64), {1});
+        return true;
+    case ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE: // :1911-1925 registers (0, 256, 64) and skips 0
+        out = cross(integer_range(64, 256, 64), {1});
+        return true;
+    case ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE: // :1749-1798
+    {
+        uint64_t lo = std::max<uint64_t>(32, info.n_tlb / (max_tblock - 1));
+        if (lo % 32) lo = (lo / 32 + 1) * 32;
+        if (lo > 512) return false;
+        out = cross(thread_range(lo, 512, 4), {1});
+        return true;
+    }
+    case ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS: // :587-700: from the TLBs per BLB
+    {
+        min_max_diff(role_of(d, ASP_ARR_BLOCK_BEGIN_THREAD_INDEX_OFFSET), 9999999, mn, mx);
+        const uint64_t hi = std::min<uint64_t>(1024, (mx + 31) / 32 * 32), lo = floor32_clamped(mn);
+        if (lo > hi) return false;
+        out = cross(thread_range(lo, hi, 8), {1});
+        return true;
+    }
+    case ASP_SHARED_MEMORY_LONG_ROW_TEMPLATE: // :970-1110: from the non-zeros per BLB (the upper end is rounded DOWN there)
+    {
+        min_max_diff(role_of(d, ASP_ARR_BLOCK_NZ_BEGIN_OFFSET), 9999999999999999ull, mn, mx);
+        const uint64_t hi = floor32_clamped(mx), lo = floor32_clamped(mn);
+        if (lo > hi) return false;
+        out = cross(thread_range(lo, hi, 8), {1});
+        return true;
+    }
+    case ASP_SHARED_MEMORY_TEMPLATE_WARP_COMPRESS: // :1215-1360: TLBs per BLB in 4 steps; row reduce 1, 4, 16 up to the most partials of a row
+    {
+        min_max_diff(role_of(d, ASP_ARR_BLOCK_BEGIN_THREAD_INDEX_OFFSET), 4096, mn, mx);
+        if (mx > 1024) return false; // "too many (> 1024) TLB in BLB" (whilte_list_path_impl.cc:798, 1220): strategies 2 and 3 drop the point
+        uint64_t rmn = 0, rmx = 0;
+        min_max_diff(role_of(d, ASP_ARR_ROW_OFFSET_IN_THREAD_TMP_RESULT), ~0ull, rmn, rmx);
+        const uint64_t hi = std::min<uint64_t>(1024, (mx + 31) / 32 * 32), lo = floor32_clamped(mn);
+        if (lo > hi) return false;
+        std::vector<int64_t> red;
+        for (uint64_t r = 1; r <= 32 && r <= rmx; r *= 4) red.push_back((int64_t)r);
+        out = cross(thread_range(lo, hi, 4), red);
+        return true;
+    }
+    case ASP_SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE: // :1495-1625: WLBs per BLB x 32 in 8 steps; row reduce 1, 2, 4, ... up to the most partials of a row
+    {
+        min_max_diff(role_of(d, ASP_ARR_BLOCK_BEGIN_WARP_INDEX_OFFSET), 1024, mn, mx);
+        uint64_t rmn = 0, rmx = 0;
+        min_max_diff(role_of(d, ASP_ARR_ROW_OFFSET_IN_WARP_TMP_RESULT), ~0ull, rmn, rmx);
+        const uint64_t hi = std::min<uint64_t>(1024, mx * 32), lo = std::min<uint64_t>(1024, std::max<uint64_t>(32, mn * 32));
+        if (lo > hi) return false;
+        std::vector<int64_t> red;
+        for (uint64_t r = 1; r <= 32 && r <= rmx; r *= 2) red.push_back((int64_t)r);
+        out = cross(thread_range(lo, hi, 8), red);
+        return true;
+    }
+    default: return false; // the two 3-level templates are not reachable from the whitelist strategies
+    }
 }
 
 std::vector<std::string> dense_strategies(bool quick)
@@ -241,7 +462,11 @@ extern "C" {
 const char *asp_search_candidates(uint64_t mn, uint64_t mx, double avg, int is_sorted, int quick)
 {
     g_text.clear();
-    for (const Candidate &c : compressed_candidates(mn, mx, avg, is_sorted != 0, quick != 0))
+    // quick: 1 = the short table, 0 = the long table of this build (both carry their own launch lists), 2 = the
+    // reference's node grids exactly (launches are derived from the lowered format, so none are listed)
+    const std::vector<Candidate> cands = quick == 2 ? reference_candidates((int64_t)mn, (int64_t)mx, 1000, (uint64_t)(avg * 1000.0 + 0.5), is_sorted != 0, false)
+                                                    : compressed_candidates(mn, mx, avg, is_sorted != 0, quick != 0);
+    for (const Candidate &c : cands)
     {
         g_text += c.name + " ; " + c.templ + " ; ";
         for (size_t i = 0; i < c.nodes.size(); i++) g_text += (i ? "|" : "") + c.nodes[i];
@@ -279,7 +504,7 @@ asp_status asp_search(const asp_matrix *m, const asp_search_options *opt_, asp_t
 
     std::unique_ptr<asp_search_result> best;
     std::vector<std::string> trials;
-    for (const std::string &dense : dense_strategies(opt.quick != 0))
+    for (const std::string &dense : dense_strategies(opt.quick == 1))
     {
         asp_matrix *cm_raw = nullptr;
         if (asp_dense_execute(m, dense.c_str(), &cm_raw) != ASP_OK) continue;
@@ -306,8 +531,12 @@ asp_status asp_search(const asp_matrix *m, const asp_search_options *opt_, asp_t
             if (opt.struggle_step_num >= 0) rule.reset(new StopRule((uint64_t)opt.struggle_step_num, opt.time_limit_s));
             bool have = false, stop = false;
             Pick bestp{};
-            for (const Candidate &cand : compressed_candidates(mn, mx, rows ? (double)nnz / (double)rows : 0.0, is_sorted, opt.quick != 0))
+            const std::vector<Candidate> cands = opt.quick == 1 ? compressed_candidates(mn, mx, rows ? (double)nnz / (double)rows : 0.0, is_sorted, true)
+                                                                : reference_candidates((int64_t)mn, (int64_t)mx, rows, nnz, is_sorted, opt.quick == 0);
+            for (const Candidate &cand : cands)
             {
+                // names start with "S<k>_": the whitelist strategy the point belongs to
+                if (opt.strategy_mask && !(opt.strategy_mask & (1u << (cand.name[1] - '0')))) continue;
                 asp_format *f_raw = nullptr;
                 if (asp_graph_execute(cm.get(), (cand.lines(sub) + others).c_str(), &f_raw) != ASP_OK)
                 {
@@ -320,6 +549,22 @@ asp_status asp_search(const asp_matrix *m, const asp_search_options *opt_, asp_t
                 asp_sub_info info;
                 if (asp_format_sub_info(f.get(), sub, &info) != ASP_OK) continue;
                 const int tid = template_id(cand.templ);
+                std::vector<Launch> launches = cand.launches;
+                if (opt.quick != 1)
+                {
+                    // the launch sweep the reference derives from the lowered format (default_auto_tuner.cc:449-2030);
+                    // its 65535-CTA grid cap only survives in the exact mode
+                    std::vector<asp_plan_desc> descs(n);
+                    if (asp_format_plan_descs(f.get(), descs.data()) != ASP_OK) continue;
+                    if (!reference_launches(tid, descs[sub], info, opt.quick == 2 ? 65535 : 2147483647ull, launches)) continue;
+                    if (opt.quick == 0 && (tid == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || tid == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE))
+                    {
+                        // (extension) the staged write-out of the CSR5-like kernels, as the third launch parameter
+                        const size_t n0 = launches.size();
+                        for (size_t q = 0; q < n0; q++)
+                            if (launches[q].threads <= 256) launches.push_back({launches[q].threads, 2});
+                    }
+                }
                 if (opt.prune_gbs > 0 && have)
                 {
                     // sound pruning: the kernel has to read every byte of the format at least once
@@ -343,7 +588,7 @@ asp_status asp_search(const asp_matrix *m, const asp_search_options *opt_, asp_t
                         continue;
                     }
                 }
-                for (const Launch &l : cand.launches)
+                for (const Launch &l : launches)
                 {
                     std::vector<int64_t> tb(n, 1), th(n, 32), rd(n, 1);
                     tb[sub] = derive_tblock(tid, info.n_tlb, info.n_wlb, info.n_blb, l.threads);

@@ -62,11 +62,11 @@ def compressed_candidates(mn: int, mx: int, avg: float, is_sorted: bool, quick: 
     """Strategies that apply to a sub-matrix with row nnz in [mn, mx] (mean avg): what the C++ loop
     sweeps (asp_search_candidates). `quick` keeps one or two node-parameter points per strategy and
     a short launch sweep."""
-    text = graph._lib().asp_search_candidates(int(mn), int(mx), float(avg), int(bool(is_sorted)), int(bool(quick))).decode()
+    text = graph._lib().asp_search_candidates(int(mn), int(mx), float(avg), int(bool(is_sorted)), int(quick)).decode()
     out = []
     for line in text.splitlines():
         name, templ, nodes, launches = [f.strip() for f in line.split(";")]
-        out.append(Candidate(name, nodes.split("|") if nodes else [], templ, [tuple(int(v) for v in l.split(":")) for l in launches.split(",")]))
+        out.append(Candidate(name, nodes.split("|") if nodes else [], templ, [tuple(int(v) for v in l.split(":")) for l in launches.split(",") if l]))
     return out
 
 
@@ -84,14 +84,15 @@ def set_launch(fmt: Format, group: capi.PlanGroup, sub: int, threads: int, reduc
     group.set_launch(sub, derive_tblock(t, info.n_tlb, info.n_wlb, info.n_blb, threads), threads, reduce)
 
 
-def _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs=0.0, prune_min_bytes=0):
+def _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs=0.0, prune_min_bytes=0, strategies=None):
     opt = graph.SearchOptions()
-    opt.quick = int(bool(quick))
+    opt.quick = int(quick)  # 1 quick, 0 the reference's space plus extensions, 2 the reference's space exactly
     opt.warmup, opt.reps, opt.max_subs = int(warmup), int(reps), int(max_subs)
     opt.struggle_step_num = -1 if struggle_step_num is None else int(struggle_step_num)
     opt.time_limit_s = 0.0 if time_limit_s is None else float(time_limit_s)
     opt.padding_rate_up_bound = PADDING_RATE_UP_BOUND
     opt.prune_gbs, opt.prune_min_bytes = float(prune_gbs), int(prune_min_bytes)
+    opt.strategy_mask = sum(1 << int(k) for k in strategies) if strategies else 0
     cb = graph.LOG_FN(lambda user, line: log(line.decode())) if log else graph.LOG_FN()
     opt.log_fn = cb
     return opt, cb  # the callback object must outlive the call
@@ -138,12 +139,12 @@ def search(ctx: capi.Context, m: CsrMatrix, quick: bool = True, warmup: int = 2,
 
 
 def search_with_timer(m: CsrMatrix, time_fn, quick: bool = True, warmup: int = 2, reps: int = 10, log=None, max_subs: int = 5,
-                      struggle_step_num: int | None = None, time_limit_s: float | None = None, prune_gbs: float = 0.0, prune_min_bytes: int = 0):
+                      struggle_step_num: int | None = None, time_limit_s: float | None = None, prune_gbs: float = 0.0, prune_min_bytes: int = 0, strategies=None):
     """asp_search with a caller-supplied timer `time_fn(fmt: Format, tblock, threads, reduce) -> ms or
     None` (None: the point cannot run). No GPU involved: used to test the loop against a model.
     Returns (description, trials, ms of the winner)."""
     hm = Matrix.from_csr(m)
-    opt, keep = _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs, prune_min_bytes)
+    opt, keep = _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs, prune_min_bytes, strategies)
 
     def cb(user, fmt_handle, tb, th, rd, w, r, ms_out):
         view = Format.borrowed(fmt_handle)

@@ -109,7 +109,12 @@ asp_status asp_partition_rows_by_nnz(uint64_t n_rows, const int64_t *indptr, int
  * and one call of `time_fn` instead of an nvcc compile and a run of a generated program. */
 typedef struct asp_search_options
 {
-    int32_t quick;              /* 1: one or two node-parameter points per strategy and a short launch sweep */
+    int32_t quick;              /* 1: one or two node-parameter points per strategy and a short launch sweep; 0: the reference's
+                                 * node-parameter grids (whilte_list_path_impl.cc:228, 613-643, 1072-1110, 1483-1520, 2093-2127,
+                                 * 2481-2530, 2838-2867, 3119-3176) and its launch sweeps derived from the lowered format
+                                 * (default_auto_tuner.cc:465-498, 587-700, 849-883, 970-1110, 1215-1360, 1495-1625, 1749-1798,
+                                 * 1911-1933), plus this build's extensions (TLB sizes 8 / 16 / 32 for the CSR5-like templates on
+                                 * long rows, their staged write-out, no 65535-CTA grid cap); 2: the reference's space exactly */
     int32_t warmup, reps;       /* handed to time_fn */
     int32_t max_subs;           /* row divisions that give more strips are abandoned (reference: 5) */
     int32_t struggle_step_num;  /* < 0: time every candidate; else the stop rule of search_strategy.cc per strip */
@@ -121,6 +126,8 @@ typedef struct asp_search_options
     uint64_t prune_min_bytes;   /* 0: 256 MiB */
     void (*log_fn)(void *user, const char *line); /* may be NULL */
     void *log_user;
+    uint32_t strategy_mask;     /* 0: every whitelist strategy the row statistics admit; else bit k set = enumerate strategy k
+                                 * (1..9, find_best_path_of_white_list_strategy<k> of the reference) */
 } asp_search_options;
 
 /* Times one SpMV over `fmt` (sub-matrices with the EMPTY template are skipped) with the given launch
@@ -146,7 +153,9 @@ int asp_search_result_num_trials(const asp_search_result *r);
 const char *asp_search_result_trial(const asp_search_result *r, int i);
 
 /* The strategies that apply to a sub-matrix with row non-zeros in [min, max] (mean avg), as text: one line
- * per candidate, "<name> ; <template> ; <node>|<node>... ; <threads>:<reduce>,..." (what asp_search sweeps). */
+ * per candidate, "<name> ; <template> ; <node>|<node>... ; <threads>:<reduce>,..." (what asp_search sweeps).
+ * quick = 1: the short table; 0: the long table with fixed launch lists; 2: the reference's node grids exactly,
+ * without launch lists (asp_search derives them from the lowered format, as the reference does). */
 const char *asp_search_candidates(uint64_t min_row_nnz, uint64_t max_row_nnz, double avg_row_nnz, int is_sorted, int quick);
 /* launch shapes the reference derives instead of searching (default_auto_tuner.cc:465-498, 688-693) */
 int64_t asp_search_derive_tblock(int template_type, uint64_t n_tlb, uint64_t n_wlb, uint64_t n_blb, int64_t thread_num_in_block);
