@@ -228,7 +228,7 @@ asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threa
     p->asked_threads = threads;
     p->asked_reduce = reduce;
     const int t = p->templ;
-    const bool warp_based = t != ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS && t != ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS;
+    const bool warp_based = t != ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS && t != ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS && t != ASP_BLOCK_ELL_TEMPLATE;
     if (warp_based && (threads % 32) != 0) return fail(ASP_ERR_INVALID_ARG, "thread_num_in_block must be a multiple of 32 for this template");
     if (is_smem_family(t))
     {
@@ -239,6 +239,12 @@ asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threa
     }
     if (tblock <= 0) tblock = 1;
     if (tblock > 2147483647LL) tblock = 2147483647LL;
+    if (t == ASP_BLOCK_ELL_TEMPLATE)
+    {
+        // one thread per pair of block rows, CTAs of at most 128 threads, never more CTAs than work
+        threads = std::min<int64_t>(128, (threads + 31) / 32 * 32);
+        tblock = (int64_t)std::max<uint64_t>(1, (p->units_for_grid + (uint64_t)threads - 1) / (uint64_t)threads);
+    }
     if (t == ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS)
     {
         // the ELL-like kernel handles `vec` TLBs per thread and is compiled for at most 512 threads
@@ -359,6 +365,12 @@ bool validate_contents(const asp_plan_desc &d, const std::vector<HostMeta> &hm, 
         c.p = col->host_ptr;
         c.dtype = col->dtype;
         c.kind = ASP_COMPRESS_NONE;
+        if (d.template_type == ASP_BLOCK_ELL_TEMPLATE)
+        {
+            // a block column covers bits_off columns of x
+            if ((max_of(c, col->len) + 1) * (uint64_t)d.bits_off + d.first_col > d.n_cols) return why = "col_index_arr names a column outside x", false;
+            return true;
+        }
         if (max_of(c, col->len) + d.first_col >= d.n_cols) return why = "col_index_arr names a column outside x", false;
     }
     const uint64_t radd = (d.sort_kind == ASP_SORT_GLOBAL) ? 0 : d.first_row;
@@ -570,7 +582,7 @@ asp_status plan_group_build(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp
     for (int i = 0; i < n; i++)
     {
         const asp_plan_desc &d = descs[i];
-        if (d.template_type < 0 || d.template_type > ASP_EMPTY_TEMPLATE) return fail(ASP_ERR_INVALID_ARG, "unknown template_type");
+        if (d.template_type < 0 || d.template_type > ASP_BLOCK_ELL_TEMPLATE) return fail(ASP_ERR_INVALID_ARG, "unknown template_type");
         // (also for EMPTY plans: the host-buffer entry points size x and y from the value type)
         if (d.val_dtype != ASP_F32 && d.val_dtype != ASP_F64) return fail(ASP_ERR_UNSUPPORTED, "val_dtype must be f32 or f64");
         if (d.n_rows == 0 || d.n_cols == 0) return fail(ASP_ERR_INVALID_ARG, "matrix without rows or columns");
@@ -631,7 +643,7 @@ asp_status plan_group_build(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp
             }
         }
         if (!vals[i] || !cols[i]) return fail(ASP_ERR_INVALID_ARG, "val_arr or col_index_arr missing");
-        if (vals[i]->len != cols[i]->len) return fail(ASP_ERR_INVALID_ARG, "val_arr and col_index_arr differ in length");
+        if (d.template_type != ASP_BLOCK_ELL_TEMPLATE && vals[i]->len != cols[i]->len) return fail(ASP_ERR_INVALID_ARG, "val_arr and col_index_arr differ in length");
         for (int s : required_slots(d.template_type))
             if (!metas[i][s].present) return fail(ASP_ERR_INVALID_ARG, "a metadata array this template needs is missing");
         if (perm_on_device(d.template_type) && d.sort_kind != ASP_SORT_NONE && !perms[i].present)
@@ -923,6 +935,23 @@ asp_status plan_group_build(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp
                 p->end_rows = er;
                 p->n_end_rows = rows.size();
             }
+            break;
+        }
+        case ASP_BLOCK_ELL_TEMPLATE:
+        {
+            const uint64_t W = d.tlb_size, r = (uint64_t)d.bits_row, c = (uint64_t)d.bits_off;
+            const uint64_t NB = W ? cols[i]->len / W : 0;
+            a.n_tlb = NB;
+            a.n_units = NB;
+            a.effective = d.effective_num;
+            if (!asp::block_ell_supported((int)r, (int)c)) st = ASP_ERR_UNSUPPORTED, why = "block-value template: blocks must be 2 x 2, 3 x 3 or 4 x 4";
+            else if (cols[i]->dtype != ASP_U32) st = ASP_ERR_UNSUPPORTED, why = "block-value template: block-column indices must be u32";
+            else if (W == 0 || NB == 0 || NB * W != cols[i]->len || (NB & 1) || nnz_pad != cols[i]->len * r * c)
+                st = ASP_ERR_BOUNDS, why = "block-value template: arrays do not match slots x padded block rows x r x c";
+            else if (d.effective_num == 0 || d.effective_num > NB * r || d.first_row + d.effective_num > d.n_rows)
+                st = ASP_ERR_BOUNDS, why = "block-value template: rows of the sub-matrix outside y or the block rows";
+            else if (d.sort_kind != ASP_SORT_NONE || d.is_atom_add) st = ASP_ERR_UNSUPPORTED, why = "block-value template: neither sorted nor column-sliced matrices";
+            p->units_for_grid = NB / 2;
             break;
         }
         default: st = ASP_ERR_UNSUPPORTED; why = "template not implemented"; break;

@@ -113,6 +113,7 @@ int template_of_name(const std::string &k)
         {"K9", ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE},
         {"K10", ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE},
         {"EMPTY", ASP_EMPTY_TEMPLATE},
+        {"B1", ASP_BLOCK_ELL_TEMPLATE}, // block-value template of this build (not one of the reference's ten)
     };
     auto it = tab.find(k);
     return it == tab.end() ? -1 : it->second;
@@ -179,6 +180,13 @@ bool apply_sub_node(CompressedBlock &b, const std::vector<std::string> &tok, std
         if (L(1) == 0 || b.blb.built || b.wlb.built || b.tlb.built) return err = "tlb_nnz needs an untiled sub-matrix", false;
         need_wlb();
         sep_thread_level_acc_to_nnz(b, L(1));
+    }
+    else if (op == "block_value")
+    {
+        // not a node of the reference: marks the sub-matrix for storage as dense <r> x <c> blocks (template B1)
+        if (L(1) == 0 || L(2) == 0 || b.blb.built || b.wlb.built || b.tlb.built || b.block_r) return err = "block_value needs <r> <c> and an untiled sub-matrix", false;
+        b.block_r = L(1);
+        b.block_c = L(2);
     }
     else
         return err = "unknown compressed-view node " + op, false;
@@ -483,8 +491,9 @@ asp_status asp_graph_execute(const asp_matrix *in, const char *spec, asp_format 
             std::string err;
             for (const std::vector<std::string> &tok : s->nodes)
                 if (!apply_sub_node(b, tok, err)) return hfail(ASP_ERR_INVALID_ARG, err);
-            complete_each_level_blocking(b);
             const int type = template_of_name(s->templ);
+            if ((b.block_r != 0) != (type == ASP_BLOCK_ELL_TEMPLATE)) return hfail(ASP_ERR_INVALID_ARG, "the block_value node and the template B1 go together");
+            if (!b.block_r) complete_each_level_blocking(b);
             if (type < 0) return hfail(ASP_ERR_INVALID_ARG, "unknown template " + s->templ);
             if (type == ASP_EMPTY_TEMPLATE)
             {

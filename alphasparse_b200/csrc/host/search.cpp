@@ -65,6 +65,13 @@ std::vector<Candidate> reference_candidates(int64_t mn, int64_t mx, uint64_t row
     std::vector<Candidate> out;
     const std::vector<Launch> none;
     auto S = [](int64_t v) { return std::to_string(v); };
+    if (extensions && !is_sorted)
+    {
+        // (extension, "strategy 0") the block-value operator: dense r x c blocks with one block-column index each.
+        // Matrices that are not made of such blocks fail the lowering or the padding gate.
+        for (int64_t rc : {3, 2, 4})
+            out.push_back({"S0_B1_" + S(rc) + "x" + S(rc), {"block_value " + S(rc) + " " + S(rc)}, "B1", cross({128}, {1})});
+    }
     if (mn >= 128)
     {
         // strategy 8 (:2838-2867): BLB_COL_DIV(c), c = 128, 256, ... <= min(4096, ceil32(max))
@@ -153,6 +160,9 @@ std::vector<Candidate> compressed_candidates(uint64_t mn_, uint64_t mx_, double 
     std::vector<Candidate> out;
     const std::vector<int64_t> T3 = quick ? std::vector<int64_t>{128, 256} : integer_range(32, 256, 32);
     const std::vector<int64_t> T2 = {128, 256};
+    if (!is_sorted)
+        for (int64_t rc : {3, 2, 4}) // the block-value operator of this build (see reference_candidates)
+            out.push_back({"S0_B1_" + std::to_string(rc) + "x" + std::to_string(rc), {"block_value " + std::to_string(rc) + " " + std::to_string(rc)}, "B1", cross({128}, {1})});
     if (mn >= 128)
     {
         // strategy 8: BLB_COL_DIV(c) -> long-row template; c = 128 .. min(4096, ceil32(max)), doubling
@@ -361,6 +371,9 @@ bool reference_launches(int templ, const asp_plan_desc &d, const asp_sub_info &i
         out = cross(thread_range(lo, hi, 8), red);
         return true;
     }
+    case ASP_BLOCK_ELL_TEMPLATE:
+        out = cross({128}, {1});
+        return true;
     default: return false; // the two 3-level templates are not reachable from the whitelist strategies
     }
 }
@@ -382,6 +395,7 @@ int template_id(const std::string &k)
     static const char *names[] = {"K1", "K2", "K3", "K5", "K6", "K7", "K8", "K4", "K9", "K10"}; // asp_template_type order
     for (int i = 0; i < 10; i++)
         if (k == names[i]) return i;
+    if (k == "B1") return ASP_BLOCK_ELL_TEMPLATE;
     return -1;
 }
 
@@ -393,6 +407,7 @@ int64_t derive_tblock(int templ, uint64_t n_tlb, uint64_t n_wlb, uint64_t n_blb,
     {
     case 0: case 1: case 3: case 4: case 5: case 6: n = n_blb; break; // K1 K2 K5 K6 K7 K8
     case 7: n = (32 * n_wlb + (uint64_t)threads - 1) / (uint64_t)threads; break; // K4
+    case ASP_BLOCK_ELL_TEMPLATE: n = (n_tlb / 2 + (uint64_t)threads - 1) / (uint64_t)threads; break; // a thread owns two block rows
     default: n = (n_tlb + (uint64_t)threads - 1) / (uint64_t)threads; break;      // K3 K9 K10
     }
     return (int64_t)std::max<uint64_t>(1, std::min<uint64_t>(n, 2147483647ull));

@@ -799,6 +799,106 @@ bool init_k9(const Matrix &m, const CompressedBlock &b, bool with_warp_reduce, T
 }
 } // namespace
 
+// ---- block-value template (this build's; no counterpart in the reference) --------------------------------
+// Blocked ELL over dense r x c blocks: block rows of r consecutive rows, block columns of c consecutive columns
+// (relative to the sub-matrix's first column); every block that holds a non-zero is stored in full, block rows
+// are padded with zero blocks to the width of the widest one, and the block rows to an even count.
+bool init_block_ell(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::string &err)
+{
+    const u64 r = b.block_r, c = b.block_c;
+    if (m.is_sorted) return err = "block_value: not for sorted matrices (a block row must be r consecutive rows of y)", false;
+    if (!((r == 2 && c == 2) || (r == 3 && c == 3) || (r == 4 && c == 4))) return err = "block_value: blocks of 2 x 2, 3 x 3 or 4 x 4", false;
+    const u64 width = b.max_col - b.min_col + 1;
+    if (width % c) return err = "block_value: the columns of the sub-matrix are not a multiple of the block width", false;
+    const u64 NBR = (b.n_rows + r - 1) / r, NB = (NBR + 1) / 2 * 2;
+    // pass 1: block columns per block row (merged over its r rows), and how full the blocks are
+    std::vector<u64> bptr(NBR + 1, 0);
+    std::vector<u32> bcol;
+    {
+        std::vector<u64> cnt(NBR, 0);
+#pragma omp parallel
+        {
+            std::vector<u32> tmp;
+#pragma omp for schedule(static)
+            for (int64_t br = 0; br < (int64_t)NBR; br++)
+            {
+                tmp.clear();
+                for (u64 row = (u64)br * r; row < std::min<u64>(b.n_rows, ((u64)br + 1) * r); row++)
+                    for (u64 k = b.rowptr[row]; k < b.rowptr[row + 1]; k++) tmp.push_back((u32)(b.col[k] / c));
+                std::sort(tmp.begin(), tmp.end());
+                cnt[br] = (u64)(std::unique(tmp.begin(), tmp.end()) - tmp.begin());
+            }
+        }
+        for (u64 br = 0; br < NBR; br++) bptr[br + 1] = bptr[br] + cnt[br];
+        bcol.resize(bptr[NBR]);
+#pragma omp parallel
+        {
+            std::vector<u32> tmp;
+#pragma omp for schedule(static)
+            for (int64_t br = 0; br < (int64_t)NBR; br++)
+            {
+                tmp.clear();
+                for (u64 row = (u64)br * r; row < std::min<u64>(b.n_rows, ((u64)br + 1) * r); row++)
+                    for (u64 k = b.rowptr[row]; k < b.rowptr[row + 1]; k++) tmp.push_back((u32)(b.col[k] / c));
+                std::sort(tmp.begin(), tmp.end());
+                tmp.erase(std::unique(tmp.begin(), tmp.end()), tmp.end());
+                std::copy(tmp.begin(), tmp.end(), bcol.begin() + bptr[br]);
+            }
+        }
+    }
+    u64 W = 0;
+    for (u64 br = 0; br < NBR; br++) W = std::max(W, bptr[br + 1] - bptr[br]);
+    if (W == 0) return err = "block_value: sub-matrix without non-zeros", false;
+    const u64 stored = NB * W * r * c;
+    if (b.nnz() == 0 || (double)stored / (double)b.nnz() > 8.0) return err = "block_value: the matrix is not made of dense blocks of this size (more than 8 stored values per non-zero)", false;
+    // pass 2: the arrays
+    const int es = b.val.es;
+    std::vector<uint8_t> idx(NB * W * 4, 0), val(stored * (u64)es, 0);
+    u32 *ip = (u32 *)idx.data();
+#pragma omp parallel for schedule(static)
+    for (int64_t br = 0; br < (int64_t)NBR; br++)
+    {
+        const u64 n = bptr[br + 1] - bptr[br];
+        const u32 *bc = bcol.data() + bptr[br];
+        for (u64 k = 0; k < W; k++) ip[k * NB + br] = k < n ? bc[k] : (n ? bc[n - 1] : 0); // zero blocks repeat the last block column
+        for (u64 row = (u64)br * r; row < std::min<u64>(b.n_rows, ((u64)br + 1) * r); row++)
+        {
+            const u64 i = row - (u64)br * r;
+            u64 k = 0; // the columns of a row ascend, so do its block slots
+            for (u64 q = b.rowptr[row]; q < b.rowptr[row + 1]; q++)
+            {
+                const u32 cb = b.col[q] / (u32)c;
+                while (bc[k] != cb) k++;
+                const u64 j = b.col[q] - (u64)cb * c;
+                memcpy(&val[(((k * r + i) * c + j) * NB + (u64)br) * es], &b.val.b[q * es], es);
+            }
+        }
+    }
+    common_head(m, b, ASP_BLOCK_ELL_TEMPLATE, t);
+    t.tlb_size = W;
+    t.bits_row = (int)r;
+    t.bits_off = (int)c;
+    t.effective_num = b.n_rows;
+    t.n_blb = NBR;
+    t.n_wlb = NBR;
+    t.n_tlb = NB;
+    t.thread_num_in_block = 128;
+    t.tblock_num = (long)std::max<u64>(1, (NB / 2 + 127) / 128);
+    t.arrays.emplace_back();
+    TemplateArray &v = t.arrays.back();
+    v.role = ASP_ARR_VAL;
+    v.dt = t.val_dt;
+    v.len = stored;
+    v.bytes.swap(val);
+    t.arrays.emplace_back();
+    TemplateArray &ci = t.arrays.back();
+    ci.role = ASP_ARR_COL_INDEX;
+    ci.dt = ASP_U32;
+    ci.len = NB * W;
+    ci.bytes.swap(idx);
+    return true;
+}
+
 bool init_template(const Matrix &m, size_t sub, int type, TemplateData &out, std::string &err)
 {
     if (sub >= m.blocks.size())
@@ -807,6 +907,11 @@ bool init_template(const Matrix &m, size_t sub, int type, TemplateData &out, std
         return false;
     }
     const CompressedBlock &b = m.blocks[sub];
+    if (type == ASP_BLOCK_ELL_TEMPLATE)
+    {
+        if (!b.block_r) return err = "the template B1 needs the block_value node", false;
+        return init_block_ell(m, b, out, err);
+    }
     const bool csr5 = type == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE || type == ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE;
     if (!csr5 && b.tlb_is_nnz_div)
     {

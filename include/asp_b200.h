@@ -67,7 +67,14 @@ typedef enum asp_template_type
     ASP_DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE = 7,
     ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE = 8,
     ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE = 9,
-    ASP_EMPTY_TEMPLATE = 10
+    ASP_EMPTY_TEMPLATE = 10,
+    /* Not one of the reference's templates: blocked ELL over dense r x c blocks, built by the `block_value r c`
+     * operator of asp_b200_host.h (2 x 2, 3 x 3, 4 x 4). One block-column index per block instead of one column
+     * index per non-zero, and the c values of x are gathered once per block. Arrays: ASP_ARR_COL_INDEX = block
+     * column of slot k of block row b at [k * NB + b] (u32), ASP_ARR_VAL = element (i, j) of that block at
+     * [((k * r + i) * c + j) * NB + b]. Scalars of asp_plan_desc: tlb_size = block slots per block row,
+     * effective_num = rows of the sub-matrix, bits_row = r, bits_off = c; NB = len(col) / tlb_size (even). */
+    ASP_BLOCK_ELL_TEMPLATE = 11
 } asp_template_type;
 
 /* role of an array inside a template; names are the reference's struct field names
