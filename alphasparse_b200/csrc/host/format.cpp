@@ -3,6 +3,9 @@
 
 #include <string.h>
 
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <algorithm>
 #include <stdexcept>
 #include <fstream>
@@ -60,66 +63,161 @@ std::unique_ptr<Matrix> matrix_from_csr(u64 n_rows, u64 n_cols, const int64_t *i
     return m;
 }
 
+// The `.mtx.coo` grammar of the reference (struct.cc:92-174): the first line that does not start with white space
+// is "rows cols ..."; every other such line is "row col value", 1-based, rows non-decreasing. The reference reads it
+// with getline + split + atol / stof, one line at a time; here the file is read in one piece, cut at line ends into
+// one slice per thread, and the slices are parsed in parallel with strtoull / strtod.
 std::unique_ptr<Matrix> matrix_from_coo_file(const std::string &path, int val_dt, std::string &err)
 {
-    std::ifstream f(path);
-    if (!f)
+    FILE *fp = fopen(path.c_str(), "rb");
+    if (!fp)
     {
         err = "cannot open " + path;
         return nullptr;
     }
-    std::string line;
-    u64 n_rows = 0, n_cols = 0;
-    bool have_head = false;
-    std::vector<u64> rows;
-    std::vector<u32> cols;
-    std::vector<double> vals;
-    u64 last_row = 0;
-    while (std::getline(f, line))
+    std::vector<char> buf;
     {
-        if (line.empty() || line[0] == ' ' || line[0] == '\t' || line[0] == '\r') continue; // lines that start with white space are skipped
-        std::istringstream is(line);
-        if (!have_head)
+        fseek(fp, 0, SEEK_END);
+        const long sz = ftell(fp);
+        fseek(fp, 0, SEEK_SET);
+        buf.resize((size_t)std::max<long>(sz, 0) + 1);
+        const size_t got = sz > 0 ? fread(buf.data(), 1, (size_t)sz, fp) : 0;
+        fclose(fp);
+        buf.resize(got + 1);
+        buf[got] = '\n'; // a last line without a line end still terminates (the numbers are parsed up to it)
+    }
+    const char *base = buf.data(), *end = base + buf.size();
+    auto skipped = [](const char *p) { return *p == '\n' || *p == ' ' || *p == '\t' || *p == '\r'; }; // empty, or starting with white space
+    auto next_line = [&](const char *p) {
+        while (p < end && *p != '\n') p++;
+        return p < end ? p + 1 : end;
+    };
+    // header
+    const char *p = base;
+    while (p < end && skipped(p)) p = next_line(p);
+    u64 n_rows = 0, n_cols = 0;
+    {
+        char *q = nullptr;
+        if (p >= end || !(*p >= '0' && *p <= '9'))
         {
-            if (!(is >> n_rows >> n_cols))
+            err = "bad header line";
+            return nullptr;
+        }
+        n_rows = strtoull(p, &q, 10);
+        const char *q2 = q;
+        while (*q2 == ' ' || *q2 == '\t') q2++;
+        if (!(*q2 >= '0' && *q2 <= '9'))
+        {
+            err = "bad header line";
+            return nullptr;
+        }
+        n_cols = strtoull(q2, &q, 10);
+        p = next_line(p);
+    }
+    // slices of whole lines, one per thread
+    int nt = 1;
+#ifdef _OPENMP
+    nt = omp_get_max_threads();
+#endif
+    const size_t body = (size_t)(end - p);
+    nt = (int)std::max<size_t>(1, std::min<size_t>((size_t)nt, body / (1u << 16) + 1));
+    std::vector<const char *> cut(nt + 1);
+    cut[0] = p;
+    cut[nt] = end;
+    for (int t = 1; t < nt; t++)
+    {
+        const char *c = p + body / nt * t;
+        cut[t] = (c <= cut[t - 1]) ? cut[t - 1] : next_line(c - 1);
+    }
+    struct Part
+    {
+        std::vector<u64> rows;
+        std::vector<u32> cols;
+        std::vector<double> vals;
+        std::string err;
+    };
+    std::vector<Part> parts(nt);
+#pragma omp parallel for schedule(static, 1) num_threads(nt)
+    for (int t = 0; t < nt; t++)
+    {
+        Part &pt = parts[t];
+        const char *s = cut[t], *e = cut[t + 1];
+        pt.rows.reserve((size_t)(e - s) / 12 + 16);
+        pt.cols.reserve((size_t)(e - s) / 12 + 16);
+        pt.vals.reserve((size_t)(e - s) / 12 + 16);
+        u64 last = 0;
+        while (s < e)
+        {
+            if (skipped(s))
             {
-                err = "bad header line";
-                return nullptr;
+                s = next_line(s);
+                continue;
             }
-            have_head = true;
-            continue;
+            char *q = nullptr;
+            const u64 r = strtoull(s, &q, 10);
+            const char *a1 = q;
+            const u64 c = strtoull(a1, &q, 10);
+            const char *a2 = q;
+            const double v = strtod(a2, &q);
+            if (a1 == s || a2 == a1 || q == a2 || r == 0 || c == 0 || r > n_rows || c > n_cols)
+            {
+                pt.err = "bad entry: " + std::string(s, (size_t)(next_line(s) - s - 1));
+                break;
+            }
+            if (r < last)
+            {
+                pt.err = "rows are not non-decreasing";
+                break;
+            }
+            last = r;
+            pt.rows.push_back(r - 1);
+            pt.cols.push_back((u32)(c - 1));
+            pt.vals.push_back(v);
+            s = next_line(q);
         }
-        u64 r, c;
-        double v;
-        if (!(is >> r >> c >> v) || r == 0 || c == 0 || r > n_rows || c > n_cols)
+    }
+    u64 nnz = 0;
+    for (int t = 0; t < nt; t++)
+    {
+        if (!parts[t].err.empty())
         {
-            err = "bad entry: " + line;
+            err = parts[t].err;
             return nullptr;
         }
-        if (r < last_row)
-        {
-            err = "rows are not non-decreasing";
-            return nullptr;
-        }
-        last_row = r;
-        rows.push_back(r - 1);
-        cols.push_back((u32)(c - 1));
-        vals.push_back(v);
+        if (t > 0 && !parts[t].rows.empty())
+            for (int u = t - 1; u >= 0; u--)
+                if (!parts[u].rows.empty())
+                {
+                    if (parts[t].rows.front() < parts[u].rows.back())
+                    {
+                        err = "rows are not non-decreasing";
+                        return nullptr;
+                    }
+                    break;
+                }
+        nnz += parts[t].rows.size();
     }
     std::unique_ptr<Matrix> m(new Matrix());
     m->n_rows = n_rows;
     m->n_cols = n_cols;
-    m->nnz = rows.size();
+    m->nnz = nnz;
     m->val_dt = val_dt;
     m->rowptr.assign(n_rows + 1, 0);
-    for (u64 r : rows) m->rowptr[r + 1]++;
-    for (u64 i = 0; i < n_rows; i++) m->rowptr[i + 1] += m->rowptr[i];
-    m->col.swap(cols);
+    m->col.resize(nnz);
     m->val.es = dtype_bytes(val_dt);
-    m->val.resize(m->nnz);
-    if (val_dt == ASP_F64) memcpy(m->val.b.data(), vals.data(), m->nnz * 8);
-    else
-        for (u64 i = 0; i < m->nnz; i++) ((float *)m->val.b.data())[i] = (float)vals[i];
+    m->val.resize(nnz);
+    u64 off = 0;
+    for (int t = 0; t < nt; t++)
+    {
+        const Part &pt = parts[t];
+        for (u64 r : pt.rows) m->rowptr[r + 1]++;
+        std::copy(pt.cols.begin(), pt.cols.end(), m->col.begin() + off);
+        if (val_dt == ASP_F64) memcpy(m->val.b.data() + off * 8, pt.vals.data(), pt.vals.size() * 8);
+        else
+            for (u64 i = 0; i < pt.vals.size(); i++) ((float *)m->val.b.data())[off + i] = (float)pt.vals[i];
+        off += pt.rows.size();
+    }
+    for (u64 i = 0; i < n_rows; i++) m->rowptr[i + 1] += m->rowptr[i];
     return m;
 }
 

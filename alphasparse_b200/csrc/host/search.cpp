@@ -6,6 +6,7 @@
 #include <chrono>
 #include <cmath>
 #include <cstdio>
+#include <map>
 #include <memory>
 #include <set>
 #include <string>
@@ -516,6 +517,45 @@ asp_status asp_search(const asp_matrix *m, const asp_search_options *opt_, asp_t
         if (opt.log_fn) opt.log_fn(opt.log_user, s.c_str());
     };
     const uint64_t total_nnz = asp_matrix_nnz(m);
+    // checkpoint: points timed by an earlier, interrupted run of the same search (key: the trial line without its time)
+    std::map<std::string, float> done;
+    FILE *ckpt = nullptr;
+    struct CloseFile
+    {
+        FILE *&f;
+        ~CloseFile()
+        {
+            if (f) fclose(f);
+        }
+    } close_ckpt{ckpt};
+    if (opt.checkpoint_path && opt.checkpoint_path[0])
+    {
+        if (FILE *in = fopen(opt.checkpoint_path, "r"))
+        {
+            char line[1024];
+            while (fgets(line, sizeof line, in))
+            {
+                // "<dense> ; sub <i> ; <name> ; threads ; reduce ; ms ; padding"
+                std::string s(line);
+                size_t p5 = std::string::npos, pos = 0;
+                int semis = 0;
+                size_t p6 = std::string::npos;
+                while ((pos = s.find(" ; ", pos)) != std::string::npos)
+                {
+                    semis++;
+                    if (semis == 5) p5 = pos;
+                    if (semis == 6) p6 = pos;
+                    pos += 3;
+                }
+                if (semis != 6) continue; // a line cut off by the interruption
+                const float ms = (float)atof(s.substr(p5 + 3, p6 - p5 - 3).c_str());
+                if (ms > 0) done[s.substr(0, p5)] = ms;
+            }
+            fclose(in);
+            log("checkpoint: " + std::to_string(done.size()) + " timed points taken from " + opt.checkpoint_path);
+        }
+        ckpt = fopen(opt.checkpoint_path, "a");
+    }
 
     std::unique_ptr<asp_search_result> best;
     std::vector<std::string> trials;
@@ -610,7 +650,11 @@ asp_status asp_search(const asp_matrix *m, const asp_search_options *opt_, asp_t
                     th[sub] = l.threads;
                     rd[sub] = l.reduce;
                     float ms = 0;
-                    if (time_fn(time_user, f.get(), tb.data(), th.data(), rd.data(), opt.warmup, opt.reps, &ms) != 0 || !(ms > 0))
+                    char key[512];
+                    snprintf(key, sizeof key, "%s ; sub %d ; %s ; %lld ; %lld", one_line(dense).c_str(), sub, cand.name.c_str(), (long long)l.threads, (long long)l.reduce);
+                    const auto was = done.find(key);
+                    if (was != done.end()) ms = was->second;
+                    else if (time_fn(time_user, f.get(), tb.data(), th.data(), rd.data(), opt.warmup, opt.reps, &ms) != 0 || !(ms > 0))
                     {
                         log("  sub " + std::to_string(sub) + " " + cand.name + " threads=" + std::to_string(l.threads) + ": cannot run");
                         continue;
@@ -619,6 +663,11 @@ asp_status asp_search(const asp_matrix *m, const asp_search_options *opt_, asp_t
                     snprintf(buf, sizeof buf, "%s ; sub %d ; %s ; %lld ; %lld ; %.6f ; %.4f", one_line(dense).c_str(), sub, cand.name.c_str(), (long long)l.threads,
                              (long long)l.reduce, ms, rate);
                     trials.push_back(buf);
+                    if (ckpt && was == done.end())
+                    {
+                        fprintf(ckpt, "%s\n", buf);
+                        fflush(ckpt);
+                    }
                     snprintf(buf, sizeof buf, "  sub %d [%llu rows, nnz/row %llu..%llu] %s threads=%lld reduce=%lld: %.1f us", sub, (unsigned long long)rows, (unsigned long long)mn,
                              (unsigned long long)mx, cand.name.c_str(), (long long)l.threads, (long long)l.reduce, ms * 1e3);
                     log(buf);

@@ -37,7 +37,7 @@ class SearchOptions(C.Structure):
     """asp_search_options"""
     _fields_ = [("quick", C.c_int32), ("warmup", C.c_int32), ("reps", C.c_int32), ("max_subs", C.c_int32), ("struggle_step_num", C.c_int32),
                 ("time_limit_s", C.c_double), ("padding_rate_up_bound", C.c_double), ("prune_gbs", C.c_double), ("prune_min_bytes", C.c_uint64),
-                ("log_fn", LOG_FN), ("log_user", C.c_void_p), ("strategy_mask", C.c_uint32)]
+                ("log_fn", LOG_FN), ("log_user", C.c_void_p), ("strategy_mask", C.c_uint32), ("checkpoint_path", C.c_char_p)]
 
 _bound = False
 

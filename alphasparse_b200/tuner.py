@@ -84,7 +84,7 @@ def set_launch(fmt: Format, group: capi.PlanGroup, sub: int, threads: int, reduc
     group.set_launch(sub, derive_tblock(t, info.n_tlb, info.n_wlb, info.n_blb, threads), threads, reduce)
 
 
-def _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs=0.0, prune_min_bytes=0, strategies=None):
+def _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs=0.0, prune_min_bytes=0, strategies=None, checkpoint=None):
     opt = graph.SearchOptions()
     opt.quick = int(quick)  # 1 quick, 0 the reference's space plus extensions, 2 the reference's space exactly
     opt.warmup, opt.reps, opt.max_subs = int(warmup), int(reps), int(max_subs)
@@ -93,6 +93,7 @@ def _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log
     opt.padding_rate_up_bound = PADDING_RATE_UP_BOUND
     opt.prune_gbs, opt.prune_min_bytes = float(prune_gbs), int(prune_min_bytes)
     opt.strategy_mask = sum(1 << int(k) for k in strategies) if strategies else 0
+    opt.checkpoint_path = checkpoint.encode() if checkpoint else None
     cb = graph.LOG_FN(lambda user, line: log(line.decode())) if log else graph.LOG_FN()
     opt.log_fn = cb
     return opt, cb  # the callback object must outlive the call
@@ -121,14 +122,14 @@ def _result(res_handle):
 
 
 def search(ctx: capi.Context, m: CsrMatrix, quick: bool = True, warmup: int = 2, reps: int = 10, log=None, max_subs: int = 5,
-           struggle_step_num: int | None = None, time_limit_s: float | None = None, prune_gbs: float = 0.0):
+           struggle_step_num: int | None = None, time_limit_s: float | None = None, prune_gbs: float = 0.0, checkpoint: str | None = None):
     """Full search on the GPU of `ctx` (asp_search_gpu). Returns (Format, PlanGroup, trials,
     description of the winning graph). With `struggle_step_num` and / or `time_limit_s` every
     sub-matrix sweep runs under the reference's stop rule; by default every candidate is timed.
     `prune_gbs` > 0 (an upper bound of the memory bandwidth in GB/s) skips candidates whose format
     cannot be read in the best time found so far."""
     hm = Matrix.from_csr(m)
-    opt, keep = _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs)
+    opt, keep = _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs, checkpoint=checkpoint)
     res = C.c_void_p()
     graph._check(graph._lib().asp_search_gpu(ctx.handle, hm._h, C.byref(opt), C.byref(res)))
     del keep
@@ -139,12 +140,12 @@ def search(ctx: capi.Context, m: CsrMatrix, quick: bool = True, warmup: int = 2,
 
 
 def search_with_timer(m: CsrMatrix, time_fn, quick: bool = True, warmup: int = 2, reps: int = 10, log=None, max_subs: int = 5,
-                      struggle_step_num: int | None = None, time_limit_s: float | None = None, prune_gbs: float = 0.0, prune_min_bytes: int = 0, strategies=None):
+                      struggle_step_num: int | None = None, time_limit_s: float | None = None, prune_gbs: float = 0.0, prune_min_bytes: int = 0, strategies=None, checkpoint: str | None = None):
     """asp_search with a caller-supplied timer `time_fn(fmt: Format, tblock, threads, reduce) -> ms or
     None` (None: the point cannot run). No GPU involved: used to test the loop against a model.
     Returns (description, trials, ms of the winner)."""
     hm = Matrix.from_csr(m)
-    opt, keep = _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs, prune_min_bytes, strategies)
+    opt, keep = _options(quick, warmup, reps, max_subs, struggle_step_num, time_limit_s, log, prune_gbs, prune_min_bytes, strategies, checkpoint)
 
     def cb(user, fmt_handle, tb, th, rd, w, r, ms_out):
         view = Format.borrowed(fmt_handle)

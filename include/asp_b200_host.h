@@ -130,6 +130,11 @@ typedef struct asp_search_options
     void *log_user;
     uint32_t strategy_mask;     /* 0: every whitelist strategy the row statistics admit; else bit k set = enumerate strategy k
                                  * (1..9, find_best_path_of_white_list_strategy<k> of the reference) */
+    const char *checkpoint_path; /* NULL: none. Else a text file that receives every timed point as soon as it is timed (one
+                                 * trial line each, flushed); a search started with the same file, matrix and options takes the
+                                 * recorded times of those points instead of timing them again, so an interrupted search picks
+                                 * up where it stopped. The reference keeps only the best graph of a finished strategy
+                                 * (whilte_list_path_impl.cc:5395-5412). */
 } asp_search_options;
 
 /* Times one SpMV over `fmt` (sub-matrices with the EMPTY template are skipped) with the given launch

@@ -130,3 +130,30 @@ def test_bandwidth_bound_pruning_skips_only_points_that_cannot_win():
     # formats below the size threshold are never pruned (cache-resident kernels beat the memory bound)
     d4, t4, _ = tuner.search_with_timer(m, timer, prune_gbs=6.0)
     assert len(t4) == len(trials) and d4 == desc
+
+
+def test_interrupted_search_resumes_from_its_checkpoint(tmp_path):
+    """Every timed point goes to the checkpoint file at once; a second run with the same file re-times none of them
+    (and one cut off half-way re-times only what is missing), and both pick the same winner."""
+    m, _ = M.uniform_random(600, 8, seed=11)
+    ck = str(tmp_path / "search.ckpt")
+    calls = []
+
+    def model(fmt, tb, th, rd):
+        calls.append((fmt.sub_info(0).template_type, th[0], rd[0]))
+        return 1.0 + 0.001 * (th[0] % 97) + 0.01 * fmt.sub_info(0).template_type
+
+    d1, t1, ms1 = tuner.search_with_timer(m, model, quick=True, checkpoint=ck)
+    n_first = len(calls)
+    lines = open(ck).read().splitlines()
+    assert n_first > 10 and len(lines) == len(t1)
+    calls.clear()
+    d2, t2, ms2 = tuner.search_with_timer(m, model, quick=True, checkpoint=ck)
+    # only the final whole-matrix timings (one per dense strategy) are not checkpointed points
+    assert len(calls) < n_first // 3 and d1 == d2 and abs(ms1 - ms2) < 1e-6 and len(t2) == len(t1)
+    # cut the file in the middle of a line, as an interruption would
+    text = open(ck).read()
+    open(ck, "w").write(text[: len(text) // 2])
+    calls.clear()
+    d3, t3, _ = tuner.search_with_timer(m, model, quick=True, checkpoint=ck)
+    assert 0 < len(calls) < n_first and d3 == d1 and len(t3) == len(t1)
