@@ -116,9 +116,9 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
         mc = m.row_slice(lo, hi) if n_chunks > 1 else m
         try:
             f, g = tuner.build(ctx, mc, desc)
-            if args.stage or args.cap_log2:
+            if args.stage or args.cap_log2 or args.generic_csr5:
                 for i in range(g.n):
-                    g.set_tuning(i, 0, (1 if args.stage else 0) | (args.cap_log2 << 4))
+                    g.set_tuning(i, 0, (1 if args.stage else 0) | (2 if args.generic_csr5 else 0) | (args.cap_log2 << 4))
         except Exception as e:  # reported to every rank below, before anybody enters a collective
             build_error = e
             break
@@ -149,6 +149,11 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
         if check_fn is not None:
             parity = check_fn(m, x0.cpu().numpy(), y1.cpu().numpy())
         del y1
+        if getattr(args, "profile_launches", 0):
+            for _ in range(args.profile_launches):
+                sh.spmv_slice(x0)
+            torch.cuda.synchronize()
+            return {"profile_only": True, "nnz": nnz_local, "rows": n, "graph": desc, "format_bytes": int(sum(g.format_bytes() for g in groups))}
         W, K = max(args.warmup, 3), max(args.steps, 1)
         for _ in range(W):
             sh.iterate(x0, 2, xa, xb)

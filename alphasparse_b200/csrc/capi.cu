@@ -1047,7 +1047,8 @@ asp_status asp_plan_set_tuning(asp_plan *plan, int vec, int path)
         if (path >= 0)
         {
             // bit 0: staged write-out; bits 4..7 (optional): log2 of the rows per warp that are staged
-            plan->args.path = path & 1;
+            // bit 1: rows stored one by one by the kernel that takes any TLB size at run time (for comparisons)
+            plan->args.path = path & 3;
             plan->args.row_reduce = (path & 1) ? 2 : 1;
             const int lg = (path >> 4) & 0xf;
             if (lg) plan->args.stage_cap = (int)std::min<uint64_t>(1ull << lg, 32ull * plan->args.tlb_size);

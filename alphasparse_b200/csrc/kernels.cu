@@ -981,7 +981,7 @@ static cudaError_t launch_vc(int templ, const KArgs &a, dim3 grid, dim3 block, s
     case 8:
     case 9:
         // TLB sizes 4 / 8 / 16 / 32 with 32-bit columns run the specialised kernels; everything else the generic one
-        if (csr5_specialised((int)a.tlb_size, (int)sizeof(CT), a.bits_word))
+        if (csr5_specialised((int)a.tlb_size, (int)sizeof(CT), a.bits_word) && ((a.path & 2) == 0 || (a.path & 1) || a.y_mc))
             return launch_csr5(sizeof(VT) == 8, (int)sizeof(CT), (templ == 9 ? 1 : 0) | ((a.path & 1) ? 2 : 0) | (a.y_mc ? 6 : 0), a, grid.x, block.x, st);
         if (a.y_mc) return cudaErrorInvalidValue;
         if (templ == 8) k_csr5<VT, CT, false><<<grid, block, 0, st>>>(a);

@@ -53,9 +53,13 @@ COMMITTED_GRAPHS = {
     "c1": {"dense": "dense compress", "subs": [{"graph": "S5_K3", "nodes": ["row_padding 32 1", "tlb_row"], "template": "K3", "threads": 128, "row_reduce": 1}]},
     "c2": {"dense": "dense compress", "subs": [{"graph": "S5_K3", "nodes": ["row_padding 32 1", "tlb_row"], "template": "K3", "threads": 128, "row_reduce": 1}]},
     "c3": {"dense": "dense compress", "subs": [{"graph": "S9_K9_s16", "nodes": ["tlb_nnz 16"], "template": "K9", "threads": 128, "row_reduce": 2}]},
-    "c4": {"dense": "dense compress", "subs": [{"graph": "S1_K2_m128", "nodes": ["row_padding 128 1", "blb_row_evenly 128", "tlb_row"], "template": "K2", "threads": 256, "row_reduce": 1}]},
+    # c4: the block-value operator of this build (one block-column index per 3 x 3 block); the best graph over the
+    # reference's own operators is kept beside it, and the default run reports both
+    "c4": {"dense": "dense compress", "subs": [{"graph": "S0_B1_3x3", "nodes": ["block_value 3 3"], "template": "B1", "threads": 128, "row_reduce": 1}]},
+    "c4_reference_operators": {"dense": "dense compress", "subs": [{"graph": "S1_K2_m128", "nodes": ["row_padding 128 1", "blb_row_evenly 128", "tlb_row"], "template": "K2", "threads": 256, "row_reduce": 1}]},
 }
 COMMITTED_GRAPHS["c4s"] = COMMITTED_GRAPHS["c4"]
+WORKLOADS["c4_reference_operators"] = WORKLOADS["c4"]
 
 
 def profiled_traffic(workload: str, graph_desc) -> float | None:
@@ -67,6 +71,7 @@ def profiled_traffic(workload: str, graph_desc) -> float | None:
     p = os.path.join(ROOT, "profiles", "dram_traffic.md")
     if not os.path.exists(p):
         return None
+    workload = workload.split("_")[0]  # "c4_reference_operators" is c4 with another graph
     for line in open(p):
         f = [c.strip() for c in line.strip().strip("|").split("|")]
         if len(f) >= 3 and f[0] == workload and f[1] == subs[0].get("graph"):
@@ -327,9 +332,14 @@ def run_c5(args, rank, world, local_rank, dist):
     if rank == 0:
         sampler.start()  # stopped right after the timed region: its samples cover set-up (idle) and the timed steps
     t_start = time.perf_counter()
-    r = bench_rmat.run(args, rank, world, local_rank, dist, log, check_fn=check_against_oracle)
-    n_before = len(sampler.samples)
+    r = bench_rmat.run(args, rank, world, local_rank, dist, log, check_fn=None if args.profile_launches else check_against_oracle)
     sampler.stop_flag.set()
+    if r.get("profile_only"):
+        if rank == 0:
+            n_, nnz_ = r["rows"], r["nnz"]
+            print(json.dumps({"profile_launches": args.profile_launches, "workload": "c5", "scale": args.scale, "nnz": nnz_, "rows": n_,
+                              "algorithmic_bytes": nnz_ * 8 + 4 * (n_ + 1) + 8 * n_, "format_bytes": r["format_bytes"], "graph": r["graph"]}))
+        return
     n, nnz, iters = r["rows"], r["nnz"], r["iters"]
     K, W = max(args.steps, 1), max(args.warmup, 3)
     b_alg = nnz * 8 + 4 * (n + 1) + 4 * (n + n)
@@ -475,6 +485,20 @@ def run_one_config(args, rank, world, local_rank, dist):
         cm.close()
         hm.close()
         del m, x
+    if args.profile_launches:
+        desc_, gen_ = WORKLOADS[args.workload]
+        m_, x_ = gen_()
+        fmt_, group_ = tuner.build(ctx, m_, graph_desc) if graph_desc is not None else tuner.search(ctx, m_, quick=True)[:2]
+        dx_ = torch.from_numpy(np.ascontiguousarray(x_)).cuda()
+        dy_ = torch.zeros(m_.n_rows, dtype=dx_.dtype, device="cuda")
+        for _ in range(args.profile_launches):
+            group_.spmv(dx_.data_ptr(), dy_.data_ptr(), "auto" if int(m_.row_lengths().min()) > 0 else True)
+        ctx.synchronize()
+        print(json.dumps({"profile_launches": args.profile_launches, "workload": args.workload, "nnz": m_.nnz, "rows": m_.n_rows,
+                          "algorithmic_bytes": m_.algorithmic_bytes(), "format_bytes": group_.format_bytes()}))
+        group_.close()
+        fmt_.close()
+        return
     sampler = ClockSampler(local_rank)
     out, keep = run_single(ctx, args.workload, graph_desc, peak, log)
     search_s = time.perf_counter() - t_s
@@ -597,7 +621,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None, help="timed steps (default: 5 for c5, where a step is 100 SpMVs; 200 otherwise)")
     ap.add_argument("--warmup", type=int, default=None, help="untimed warm-up steps (default 3; at least 3 are always run)")
-    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["c5"])
+    ap.add_argument("--workload", default="c5", choices=sorted(k for k in WORKLOADS if "_" not in k) + ["c5"])
     ap.add_argument("--scale", type=int, default=26, help="c5: R-MAT scale (2^scale rows)")
     ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x)")
     ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank (0: 1 with the publishing kernels, 2 with a separate store pass)")
@@ -610,6 +634,7 @@ def main():
     ap.add_argument("--sort", default="auto", choices=["auto", "yes", "no"], help="c5: put the rows without non-zeros last (a one-bin coarse sort) so that the format drops them; auto = "
                     "yes, except with the publishing kernels, which send unpermuted rows as contiguous 16-byte multicast stores")
     ap.add_argument("--cap-log2", type=int, default=0, help="CSR5-like plans: log2 of the rows per warp that go through shared memory (0: chosen at plan creation)")
+    ap.add_argument("--generic-csr5", action="store_true", help="CSR5-like plans: the kernel that takes the TLB size at run time instead of the specialised one (comparison runs)")
     ap.add_argument("--stage", action="store_true", help="CSR5-like plans: row sums of a warp through shared memory, contiguous write-out")
     ap.add_argument("--search", action="store_true", help="c5: run the quick search instead of the default one-kernel graph")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
@@ -619,9 +644,10 @@ def main():
     ap.add_argument("--threads", type=int, default=0, help="with --spec: thread_num_in_block")
     ap.add_argument("--graph", default=None, help="skip the search: a bench JSON line file (its config.graph is used) or the graph JSON itself")
     ap.add_argument("--committed", action="store_true", help="single-GPU workloads: replay the committed graph instead of searching")
-    ap.add_argument("--configs", default="c1,c2,c3,c4", help="c5 at N = 1: single-GPU configurations to attach to the line")
+    ap.add_argument("--configs", default="c1,c2,c3,c4,c4_reference_operators", help="c5 at N = 1: single-GPU configurations to attach to the line")
     ap.add_argument("--no-configs", action="store_true")
     ap.add_argument("--configs-budget-s", type=float, default=600.0, help="no further sub-configuration is started once the run has taken this long")
+    ap.add_argument("--profile-launches", type=int, default=0, help="for ncu captures: build the plan, run this many SpMVs and exit (no timing, one short JSON line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
