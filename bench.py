@@ -625,7 +625,7 @@ def main():
     ap.add_argument("--scale", type=int, default=26, help="c5: R-MAT scale (2^scale rows)")
     ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x)")
     ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank (0: 1 with the publishing kernels, 2 with a separate store pass)")
-    ap.add_argument("--exchange", default="publish", choices=["publish", "multicast", "allgather", "a2a"],
+    ap.add_argument("--exchange", default="multicast", choices=["multicast", "publish", "allgather", "a2a"],
                     help="c5: how a rank's slice of the next x reaches the others: from inside the SpMV kernel (publish), by a multicast store pass per "
                          "chunk, or by NCCL (both multicast modes fall back to allgather where symmetric memory has no multicast address)")
     ap.add_argument("--balance", default="nnz", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
