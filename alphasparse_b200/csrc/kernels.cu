@@ -709,19 +709,70 @@ __global__ void __launch_bounds__(1024) k_smem_tlb(const KArgs a)
         const u64 n = t1 - t0;
         const u64 g0 = mget(a.m[MS_ROW_OFF], r0);
         __syncthreads(); // the previous strip's phase 2 has finished reading part[]
-        for (u64 i = threadIdx.x; i < n; i += blockDim.x)
+        constexpr int V = 4;
+        if ((n % V) == 0 && (nz0 % V) == 0)
         {
-            VT acc = 0;
-            const VT *vp = val + nz0 + i;
-            const CT *cp = col + nz0 + i;
-#pragma unroll 4
-            for (u32 k = 0; k < S; k++)
+            // the strip's TLB count is padded to a multiple of 32 by the TLB operator: a thread takes V adjacent TLBs,
+            // so every value / index load is one 16-byte (fp32) or two 16-byte (fp64) vectors, batches of 4 steps in flight
+            for (u64 i = (u64)threadIdx.x * V; i < n; i += (u64)blockDim.x * V)
             {
-                acc += __ldcs(vp) * __ldg(x + __ldcs(cp));
-                vp += n;
-                cp += n;
+                VT acc[V];
+#pragma unroll
+                for (int j = 0; j < V; j++) acc[j] = 0;
+                const VT *vp = val + nz0 + i;
+                const CT *cp = col + nz0 + i;
+                constexpr int U = 4;
+                u32 k = 0;
+                for (; k + U <= S; k += U)
+                {
+                    VT v[U][V], xv[U][V];
+                    CT c[U][V];
+#pragma unroll
+                    for (int u = 0; u < U; u++) ld_stream_pinned<CT, V>(cp + (u64)u * n, c[u]);
+#pragma unroll
+                    for (int u = 0; u < U; u++) ld_stream_pinned<VT, V>(vp + (u64)u * n, v[u]);
+#pragma unroll
+                    for (int u = 0; u < U; u++)
+#pragma unroll
+                        for (int j = 0; j < V; j++) xv[u][j] = ld_x_pinned(x + c[u][j]);
+#pragma unroll
+                    for (int u = 0; u < U; u++)
+#pragma unroll
+                        for (int j = 0; j < V; j++) acc[j] += v[u][j] * xv[u][j];
+                    vp += (u64)U * n;
+                    cp += (u64)U * n;
+                }
+                for (; k < S; k++)
+                {
+                    VT v[V];
+                    CT c[V];
+                    ld_stream_n<VT, V>(vp, v);
+                    ld_stream_n<CT, V>(cp, c);
+#pragma unroll
+                    for (int j = 0; j < V; j++) acc[j] += v[j] * __ldg(x + c[j]);
+                    vp += n;
+                    cp += n;
+                }
+#pragma unroll
+                for (int j = 0; j < V; j++) part[i + j] = acc[j];
             }
-            part[i] = acc;
+        }
+        else
+        {
+            for (u64 i = threadIdx.x; i < n; i += blockDim.x)
+            {
+                VT acc = 0;
+                const VT *vp = val + nz0 + i;
+                const CT *cp = col + nz0 + i;
+#pragma unroll 4
+                for (u32 k = 0; k < S; k++)
+                {
+                    acc += __ldcs(vp) * __ldg(x + __ldcs(cp));
+                    vp += n;
+                    cp += n;
+                }
+                part[i] = acc;
+            }
         }
         __syncthreads();
         smem_row_reduce<VT>(a, part, y, r0, r1, g0);

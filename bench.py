@@ -628,8 +628,9 @@ def main():
     ap.add_argument("--exchange", default="multicast", choices=["multicast", "publish", "allgather", "a2a"],
                     help="c5: how a rank's slice of the next x reaches the others: from inside the SpMV kernel (publish), by a multicast store pass per "
                          "chunk, or by NCCL (both multicast modes fall back to allgather where symmetric memory has no multicast address)")
-    ap.add_argument("--balance", default="nnz", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
-                    "or a number w (a row with non-zeros weighs w non-zeros)")
+    ap.add_argument("--balance", default="6", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
+                    "or a number w (a row with non-zeros weighs w non-zeros; measured at 4 GPUs: 6 evens out the ranks' kernel times to 3 %%, "
+                    "nnz leaves the rank with the sparse tail 10 %% behind)")
     ap.add_argument("--tlb", type=int, default=0, help="c5: non-zeros per thread of the CSR5-like format (default 32)")
     ap.add_argument("--sort", default="auto", choices=["auto", "yes", "no"], help="c5: put the rows without non-zeros last (a one-bin coarse sort) so that the format drops them; auto = "
                     "yes, except with the publishing kernels, which send unpermuted rows as contiguous 16-byte multicast stores")
