@@ -47,6 +47,16 @@ WORKLOADS = {
     "c4s": ("3x3-block FEM-like fp64, 1048576 block rows x 9 blocks, seed 3", lambda: matrices.block_fem(1_048_576, 9, 4096, 3)),
 }
 
+# Two more matrices, only for profiling the kernel families that none of the five configurations ends up on
+# (warp / CTA per row chunk, the shared-memory row reduce): medium rows and long rows, columns uniformly random.
+def _rows_between(lo, hi, n_rows, n_cols, seed):
+    rng = np.random.default_rng(seed)
+    return matrices.from_row_lengths(rng.integers(lo, hi + 1, size=n_rows), n_cols, seed=seed)
+
+
+WORKLOADS["pmid"] = ("profiling matrix: 1,000,000 rows of 40..120 non-zeros, fp32, random columns", lambda: _rows_between(40, 120, 1_000_000, 1_000_000, 21))
+WORKLOADS["plong"] = ("profiling matrix: 60,000 rows of 1000..3000 non-zeros, fp32, random columns", lambda: _rows_between(1000, 3000, 60_000, 1_000_000, 22))
+
 # The graphs the GPU search (`bench.py --workload cK`) picked for the single-GPU configurations; the default
 # run replays them after its own timed region instead of searching again.
 COMMITTED_GRAPHS = {
@@ -485,6 +495,37 @@ def run_one_config(args, rank, world, local_rank, dist):
         cm.close()
         hm.close()
         del m, x
+    if args.profile_launches and args.profile_specs:
+        # several graphs over one matrix, a few launches each (one process for one ncu capture of several kernel families)
+        from alphasparse_b200.graph import Matrix
+
+        desc_, gen_ = WORKLOADS[args.workload]
+        m_, x_ = gen_()
+        hm = Matrix.from_csr(m_)
+        cm = hm.dense("dense compress")
+        rows_, nnz_, mn_, mx_ = cm.sub_rows(0)
+        table = {c.name: c for c in tuner.compressed_candidates(mn_, mx_, nnz_ / rows_, False, quick=False)}
+        dx_ = torch.from_numpy(np.ascontiguousarray(x_)).cuda()
+        dy_ = torch.zeros(m_.n_rows, dtype=dx_.dtype, device="cuda")
+        done = {}
+        for name in args.profile_specs.split(","):
+            cand = table[name]
+            fmt_ = cm.execute(cand.lines(0))
+            group_ = fmt_.upload(ctx)
+            th, red = cand.launches[0]
+            tuner.set_launch(fmt_, group_, 0, th, red)
+            for _ in range(args.profile_launches):
+                group_.spmv(dx_.data_ptr(), dy_.data_ptr(), True)
+            ctx.synchronize()
+            ms, gf = group_.time(2, 10, True)
+            done[name] = {"threads": th, "row_reduce": red, "launch": group_.get_launch(0), "format_bytes": group_.format_bytes(), "padding_rate": round(fmt_.padding_rate(0), 4), "ms": ms, "gflops": gf}
+            group_.close()
+            fmt_.close()
+        print(json.dumps({"profile_launches": args.profile_launches, "workload": args.workload, "nnz": m_.nnz, "rows": m_.n_rows,
+                          "algorithmic_bytes": m_.algorithmic_bytes(), "graphs": done}))
+        cm.close()
+        hm.close()
+        return
     if args.profile_launches:
         desc_, gen_ = WORKLOADS[args.workload]
         m_, x_ = gen_()
@@ -649,6 +690,7 @@ def main():
     ap.add_argument("--no-configs", action="store_true")
     ap.add_argument("--configs-budget-s", type=float, default=600.0, help="no further sub-configuration is started once the run has taken this long")
     ap.add_argument("--profile-launches", type=int, default=0, help="for ncu captures: build the plan, run this many SpMVs and exit (no timing, one short JSON line)")
+    ap.add_argument("--profile-specs", default=None, help="with --profile-launches: comma-separated graph names (candidate table) to run one after the other over the workload's matrix")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
