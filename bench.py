@@ -5,8 +5,9 @@
 Default workload (every N, N = 1 included): the sharded graph configuration, R-MAT scale 26
 (67,108,864 rows, ~1.06e9 non-zeros, fp32) generated on the GPUs, nnz-balanced row blocks, x
 replicated, ONE STEP = 100 repeated SpMVs (x <- A x). Strong scaling: the matrix is the same at every
-N. With N > 1 every rank's rows of the next x reach all ranks from inside the SpMV kernel (NVLink
-multicast stores, --exchange publish) and one bounded-wait barrier kernel per SpMV orders the ranks.
+N. With N > 1 every rank cuts its block into row chunks and stores each finished chunk once through an
+NVLink multicast address (NVSwitch replicates it) on a second stream, under the next chunk's kernel; one
+bounded-wait barrier kernel per SpMV orders the ranks (--exchange: the other forms that were measured).
 At N = 1 the line also carries `configs`: the four single-GPU configurations (c1..c4) replayed with the
 graphs the search picked for them, each with its own time, roofline fraction and parity.
 
@@ -26,7 +27,6 @@ import argparse
 import ctypes as C
 import json
 import os
-import re
 import subprocess
 import sys
 import threading
@@ -665,7 +665,7 @@ def main():
     ap.add_argument("--workload", default="c5", choices=sorted(k for k in WORKLOADS if "_" not in k) + ["c5"])
     ap.add_argument("--scale", type=int, default=26, help="c5: R-MAT scale (2^scale rows)")
     ap.add_argument("--iters", type=int, default=100, help="c5: repeated SpMVs per step (y -> x)")
-    ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank (0: 1 with the publishing kernels, 2 with a separate store pass)")
+    ap.add_argument("--chunks", type=int, default=0, help="c5: row chunks per rank (0: with the multicast store pass one per 1/(2N) of all rows the rank owns, at most 8; 1 with the publishing kernels; 2 with the NCCL forms)")
     ap.add_argument("--exchange", default="multicast", choices=["multicast", "publish", "allgather", "a2a"],
                     help="c5: how a rank's slice of the next x reaches the others: from inside the SpMV kernel (publish), by a multicast store pass per "
                          "chunk, or by NCCL (both multicast modes fall back to allgather where symmetric memory has no multicast address)")
@@ -673,8 +673,8 @@ def main():
                     "or a number w (a row with non-zeros weighs w non-zeros; measured at 4 GPUs: 6 evens out the ranks' kernel times to 3 %%, "
                     "nnz leaves the rank with the sparse tail 10 %% behind)")
     ap.add_argument("--tlb", type=int, default=0, help="c5: non-zeros per thread of the CSR5-like format (default 32)")
-    ap.add_argument("--sort", default="auto", choices=["auto", "yes", "no"], help="c5: put the rows without non-zeros last (a one-bin coarse sort) so that the format drops them; auto = "
-                    "yes, except with the publishing kernels, which send unpermuted rows as contiguous 16-byte multicast stores")
+    ap.add_argument("--sort", default="auto", choices=["auto", "yes", "no"], help="c5: put the rows without non-zeros last (a one-bin coarse sort) so that the format drops them (auto = yes); "
+                    "no = every row is stored, unpermuted, which lets the publishing kernels send 16-byte multicast stores (measured slower)")
     ap.add_argument("--cap-log2", type=int, default=0, help="CSR5-like plans: log2 of the rows per warp that go through shared memory (0: chosen at plan creation)")
     ap.add_argument("--generic-csr5", action="store_true", help="CSR5-like plans: the kernel that takes the TLB size at run time instead of the specialised one (comparison runs)")
     ap.add_argument("--stage", action="store_true", help="CSR5-like plans: row sums of a warp through shared memory, contiguous write-out")
