@@ -536,14 +536,37 @@ __global__ void __launch_bounds__(1024) k_direct3(const KArgs a)
             const u32 S = (u32)mget(a.m[MS_TLB_SIZE], w);
             const u64 t0 = mget(a.m[MS_WARP_THR], w), t1 = mget(a.m[MS_WARP_THR], w + 1);
             const u64 groups = (t1 - t0) >> 5;
-            for (u64 g = 0; g < groups; g++)
+            if ((wnz & 3) == 0)
             {
-                double acc = 0;
-                u64 nz = wnz + g * 32 * S + lane;
-                for (u32 k = 0; k < S; k++, nz += 32) acc += (double)(__ldcs(val + nz) * __ldg(x + __ldcs(col + nz)));
-                const u64 t = t0 + g * 32 + lane;
-                out_add(y, mget(a.m[MS_ROW_OF_TLB], t) + radd, (VT)acc, a.atomic != 0);
+                // a lane takes 4 adjacent TLBs of a group (one 16-byte load of values and of indices per step), so a
+                // warp walks 4 groups per trip: lane l -> group g0 + l / 8, TLBs 4 (l % 8) .. + 3
+                for (u64 g = lane >> 3; g < groups; g += 4)
+                {
+                    double acc[4] = {0, 0, 0, 0};
+                    u64 nz = wnz + g * 32 * S + 4 * (lane & 7);
+                    for (u32 k = 0; k < S; k++, nz += 32)
+                    {
+                        VT v[4];
+                        CT c[4];
+                        ld_stream_n<VT, 4>(val + nz, v);
+                        ld_stream_n<CT, 4>(col + nz, c);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) acc[j] += (double)(v[j] * __ldg(x + c[j]));
+                    }
+                    const u64 t = t0 + g * 32 + 4 * (lane & 7);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) out_add(y, mget(a.m[MS_ROW_OF_TLB], t + j) + radd, (VT)acc[j], a.atomic != 0);
+                }
             }
+            else
+                for (u64 g = 0; g < groups; g++)
+                {
+                    double acc = 0;
+                    u64 nz = wnz + g * 32 * S + lane;
+                    for (u32 k = 0; k < S; k++, nz += 32) acc += (double)(__ldcs(val + nz) * __ldg(x + __ldcs(col + nz)));
+                    const u64 t = t0 + g * 32 + lane;
+                    out_add(y, mget(a.m[MS_ROW_OF_TLB], t) + radd, (VT)acc, a.atomic != 0);
+                }
         }
     }
 }
@@ -805,13 +828,34 @@ __global__ void __launch_bounds__(1024) k_smem3(const KArgs a)
             const u32 S = (u32)mget(a.m[MS_TLB_SIZE], w);
             const u64 t0 = mget(a.m[MS_WARP_THR], w), t1 = mget(a.m[MS_WARP_THR], w + 1);
             const u64 n = t1 - t0;
-            for (u64 i = lane; i < n; i += 32)
+            if ((n & 3) == 0 && (wnz & 3) == 0)
             {
-                VT acc = 0;
-                u64 nz = wnz + i;
-                for (u32 k = 0; k < S; k++, nz += n) acc += __ldcs(val + nz) * __ldg(x + __ldcs(col + nz));
-                part[t0 + i - tb0] = acc;
+                // the WLB's TLB count is padded to a multiple of 32: a lane takes 4 adjacent TLBs, 16-byte loads per step
+                for (u64 i = (u64)lane * 4; i < n; i += 128)
+                {
+                    VT acc[4] = {0, 0, 0, 0};
+                    u64 nz = wnz + i;
+                    for (u32 k = 0; k < S; k++, nz += n)
+                    {
+                        VT v[4];
+                        CT c[4];
+                        ld_stream_n<VT, 4>(val + nz, v);
+                        ld_stream_n<CT, 4>(col + nz, c);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) acc[j] += v[j] * __ldg(x + c[j]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++) part[t0 + i + j - tb0] = acc[j];
+                }
             }
+            else
+                for (u64 i = lane; i < n; i += 32)
+                {
+                    VT acc = 0;
+                    u64 nz = wnz + i;
+                    for (u32 k = 0; k < S; k++, nz += n) acc += __ldcs(val + nz) * __ldg(x + __ldcs(col + nz));
+                    part[t0 + i - tb0] = acc;
+                }
         }
         __syncthreads();
         smem_row_reduce<VT>(a, part, y, r0, r1, g0);

@@ -507,16 +507,22 @@ def run_one_config(args, rank, world, local_rank, dist):
         table = {c.name: c for c in tuner.compressed_candidates(mn_, mx_, nnz_ / rows_, False, quick=False)}
         dx_ = torch.from_numpy(np.ascontiguousarray(x_)).cuda()
         dy_ = torch.zeros(m_.n_rows, dtype=dx_.dtype, device="cuda")
-        done = {}
+        done, built = {}, []
         for name in args.profile_specs.split(","):
+            # "<candidate>[@threads[:row_reduce]]"; the launches of all graphs come first (what a capture counts), the timings after
+            name, _, launch = name.partition("@")
             cand = table[name]
             fmt_ = cm.execute(cand.lines(0))
             group_ = fmt_.upload(ctx)
             th, red = cand.launches[0]
+            if launch:
+                th, red = int(launch.split(":")[0]), (int(launch.split(":")[1]) if ":" in launch else red)
             tuner.set_launch(fmt_, group_, 0, th, red)
             for _ in range(args.profile_launches):
                 group_.spmv(dx_.data_ptr(), dy_.data_ptr(), True)
             ctx.synchronize()
+            built.append((name, th, red, fmt_, group_))
+        for name, th, red, fmt_, group_ in built:
             ms, gf = group_.time(2, 10, True)
             done[name] = {"threads": th, "row_reduce": red, "launch": group_.get_launch(0), "format_bytes": group_.format_bytes(), "padding_rate": round(fmt_.padding_rate(0), 4), "ms": ms, "gflops": gf}
             group_.close()
