@@ -60,7 +60,7 @@ WORKLOADS["plong"] = ("profiling matrix: 60,000 rows of 1000..3000 non-zeros, fp
 # The graphs the GPU search (`bench.py --workload cK`) picked for the single-GPU configurations; the default
 # run replays them after its own timed region instead of searching again.
 COMMITTED_GRAPHS = {
-    "c1": {"dense": "dense compress", "subs": [{"graph": "S5_K3", "nodes": ["row_padding 32 1", "tlb_row"], "template": "K3", "threads": 128, "row_reduce": 1}]},
+    "c1": {"dense": "dense compress", "subs": [{"graph": "S2_K6_m64_c4", "nodes": ["row_padding 64 1", "blb_row_evenly 64", "tlb_col_fixed 4"], "template": "K6", "threads": 128, "row_reduce": 1}]},
     "c2": {"dense": "dense compress", "subs": [{"graph": "S5_K3", "nodes": ["row_padding 32 1", "tlb_row"], "template": "K3", "threads": 128, "row_reduce": 1}]},
     "c3": {"dense": "dense compress", "subs": [{"graph": "S9_K9_s16", "nodes": ["tlb_nnz 16"], "template": "K9", "threads": 128, "row_reduce": 2}]},
     # c4: the block-value operator of this build (one block-column index per 3 x 3 block); the best graph over the

@@ -43,3 +43,20 @@ def test_status_strings():
     L = capi.lib()
     assert L.asp_status_str(0) == b"ok"
     assert L.asp_status_str(5) == b"format array out of bounds"
+
+
+def test_argument_errors_of_the_multi_gpu_entry_points_need_no_device():
+    """Bad arguments are refused before anything is launched: more ranks than the barrier has lanes for, a rank
+    outside the group, NULL buffers."""
+    import ctypes as C
+
+    L = capi.lib()
+    buf = (C.c_uint32 * 64)()
+    p = C.cast(buf, C.c_void_p)
+    assert L.asp_rank_barrier(p, p, 0, 33, 1, p, 0, None) == 1   # world > 32
+    assert L.asp_rank_barrier(p, p, 2, 2, 1, p, 0, None) == 1    # rank outside the group
+    assert L.asp_rank_barrier(None, p, 0, 2, 1, p, 0, None) == 1
+    assert L.asp_spmv_publish(None, None, 0, None, None, None) == 1
+    assert L.asp_multicast_store(None, None, 16, None, 0) == 1
+    assert L.asp_multicast_store(p, p, 0, None, 0) == 0          # nothing to store
+    assert L.asp_plan_descs_validate(None, 0) == 1
