@@ -19,13 +19,13 @@ DTYPE_OF_NP = {np.dtype(np.uint8): U8, np.dtype(np.uint16): U16, np.dtype(np.uin
                np.dtype(np.float32): F32, np.dtype(np.float64): F64}
 NP_OF_NAME = {"u8": np.uint8, "u16": np.uint16, "u32": np.uint32, "u64": np.uint64, "f32": np.float32, "f64": np.float64}
 COMPRESS = {"none": 0, "linear": 1, "constant": 2, "branch": 3, "cycle_linear": 4, "cycle_increase": 5}
-TEMPLATE = {"K1": 0, "K2": 1, "K3": 2, "K5": 3, "K6": 4, "K7": 5, "K8": 6, "K4": 7, "K9": 8, "K10": 9, "EMPTY": 10, "B1": 11}
+TEMPLATE = {"K1": 0, "K2": 1, "K3": 2, "K5": 3, "K6": 4, "K7": 5, "K8": 6, "K4": 7, "K9": 8, "K10": 9, "EMPTY": 10, "B1": 11, "D1": 12}
 TEMPLATE_NAME = {
     0: "DIRECT_ATOM_TEMPLATE", 1: "DIRECT_ATOM_TEMPLATE_WARP_COMPRESS", 2: "DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS",
     3: "SHARED_MEMORY_TEMPLATE", 4: "SHARED_MEMORY_TEMPLATE_WARP_COMPRESS", 5: "SHARED_MEMORY_LONG_ROW_TEMPLATE",
     6: "SHARED_MEMORY_TOTAL_WARP_REDUCE_TEMPLATE", 7: "DIRECT_ATOM_TOTAL_WARP_REDUCE_TEMPLATE",
     8: "UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE", 9: "UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE",
-    10: "EMPTY_TEMPLATE", 11: "BLOCK_ELL_TEMPLATE",
+    10: "EMPTY_TEMPLATE", 11: "BLOCK_ELL_TEMPLATE", 12: "DIAG_TEMPLATE",
 }
 ROLE = {
     "val_arr": 0, "col_index_arr": 1, "row_index_before_sort": 2, "global_row_index_of_thread_level_block": 3,

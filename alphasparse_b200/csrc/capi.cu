@@ -228,7 +228,7 @@ asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threa
     p->asked_threads = threads;
     p->asked_reduce = reduce;
     const int t = p->templ;
-    const bool warp_based = t != ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS && t != ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS && t != ASP_BLOCK_ELL_TEMPLATE;
+    const bool warp_based = t != ASP_DIRECT_ATOM_TEMPLATE_WARP_BLOCK_COMPRESS && t != ASP_DIRECT_ATOM_TEMPLATE_WARP_COMPRESS && t != ASP_BLOCK_ELL_TEMPLATE && t != ASP_DIAG_TEMPLATE;
     if (warp_based && (threads % 32) != 0) return fail(ASP_ERR_INVALID_ARG, "thread_num_in_block must be a multiple of 32 for this template");
     if (is_smem_family(t))
     {
@@ -239,6 +239,11 @@ asp_status apply_launch(asp_ctx *ctx, asp_plan *p, int64_t tblock, int64_t threa
     }
     if (tblock <= 0) tblock = 1;
     if (tblock > 2147483647LL) tblock = 2147483647LL;
+    if (t == ASP_DIAG_TEMPLATE)
+    {
+        threads = std::min<int64_t>(256, (threads + 31) / 32 * 32);
+        tblock = (int64_t)std::max<uint64_t>(1, (p->units_for_grid + (uint64_t)threads - 1) / (uint64_t)threads);
+    }
     if (t == ASP_BLOCK_ELL_TEMPLATE)
     {
         // one thread per pair of block rows, CTAs of at most 128 threads, never more CTAs than work
@@ -365,6 +370,14 @@ bool validate_contents(const asp_plan_desc &d, const std::vector<HostMeta> &hm, 
         c.p = col->host_ptr;
         c.dtype = col->dtype;
         c.kind = ASP_COMPRESS_NONE;
+        if (d.template_type == ASP_DIAG_TEMPLATE)
+        {
+            // offsets are biased by the column count; |offset| beyond the matrix is harmless (the kernel masks every x index)
+            // but a bias that does not match makes no sense
+            c.dtype = ASP_U64;
+            if (max_of(c, col->len) >= 2 * (d.n_cols - d.first_col) + d.n_rows) return why = "a diagonal offset lies outside the matrix", false;
+            return true;
+        }
         if (d.template_type == ASP_BLOCK_ELL_TEMPLATE)
         {
             // a block column covers bits_off columns of x
@@ -582,7 +595,7 @@ asp_status plan_group_build(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp
     for (int i = 0; i < n; i++)
     {
         const asp_plan_desc &d = descs[i];
-        if (d.template_type < 0 || d.template_type > ASP_BLOCK_ELL_TEMPLATE) return fail(ASP_ERR_INVALID_ARG, "unknown template_type");
+        if (d.template_type < 0 || d.template_type > ASP_DIAG_TEMPLATE) return fail(ASP_ERR_INVALID_ARG, "unknown template_type");
         // (also for EMPTY plans: the host-buffer entry points size x and y from the value type)
         if (d.val_dtype != ASP_F32 && d.val_dtype != ASP_F64) return fail(ASP_ERR_UNSUPPORTED, "val_dtype must be f32 or f64");
         if (d.n_rows == 0 || d.n_cols == 0) return fail(ASP_ERR_INVALID_ARG, "matrix without rows or columns");
@@ -606,7 +619,8 @@ asp_status plan_group_build(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp
             }
             else if (ad.role == ASP_ARR_COL_INDEX)
             {
-                if (ad.dtype != ASP_U8 && ad.dtype != ASP_U16 && ad.dtype != ASP_U32) return fail(ASP_ERR_UNSUPPORTED, "col_index_arr must be u8/u16/u32");
+                if (d.template_type == ASP_DIAG_TEMPLATE ? ad.dtype != ASP_U64 : (ad.dtype != ASP_U8 && ad.dtype != ASP_U16 && ad.dtype != ASP_U32))
+                    return fail(ASP_ERR_UNSUPPORTED, "col_index_arr must be u8/u16/u32 (u64 diagonal offsets for the diagonal-value template)");
                 cols[i] = &ad;
             }
             else
@@ -643,7 +657,7 @@ asp_status plan_group_build(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp
             }
         }
         if (!vals[i] || !cols[i]) return fail(ASP_ERR_INVALID_ARG, "val_arr or col_index_arr missing");
-        if (d.template_type != ASP_BLOCK_ELL_TEMPLATE && vals[i]->len != cols[i]->len) return fail(ASP_ERR_INVALID_ARG, "val_arr and col_index_arr differ in length");
+        if (d.template_type != ASP_BLOCK_ELL_TEMPLATE && d.template_type != ASP_DIAG_TEMPLATE && vals[i]->len != cols[i]->len) return fail(ASP_ERR_INVALID_ARG, "val_arr and col_index_arr differ in length");
         for (int s : required_slots(d.template_type))
             if (!metas[i][s].present) return fail(ASP_ERR_INVALID_ARG, "a metadata array this template needs is missing");
         if (perm_on_device(d.template_type) && d.sort_kind != ASP_SORT_NONE && !perms[i].present)
@@ -952,6 +966,19 @@ asp_status plan_group_build(asp_ctx *ctx, const asp_plan_desc *descs, int n, asp
                 st = ASP_ERR_BOUNDS, why = "block-value template: rows of the sub-matrix outside y or the block rows";
             else if (d.sort_kind != ASP_SORT_NONE || d.is_atom_add) st = ASP_ERR_UNSUPPORTED, why = "block-value template: neither sorted nor column-sliced matrices";
             p->units_for_grid = NB / 2;
+            break;
+        }
+        case ASP_DIAG_TEMPLATE:
+        {
+            const uint64_t D = d.tlb_size, V = p->val_is_f64 ? 2 : 4;
+            const uint64_t NR = D ? nnz_pad / D : 0;
+            a.n_tlb = NR;
+            a.n_units = d.n_cols - d.first_col; // the offsets are biased by this
+            a.effective = d.effective_num;
+            if (D == 0 || D != cols[i]->len || NR * D != nnz_pad || NR == 0 || (NR % V) != 0) st = ASP_ERR_BOUNDS, why = "diagonal-value template: values do not match diagonals x padded rows";
+            else if (d.effective_num == 0 || d.effective_num > NR || d.first_row + d.effective_num > d.n_rows) st = ASP_ERR_BOUNDS, why = "diagonal-value template: rows of the sub-matrix outside y or the padded rows";
+            else if (d.sort_kind != ASP_SORT_NONE || d.is_atom_add) st = ASP_ERR_UNSUPPORTED, why = "diagonal-value template: neither sorted nor column-sliced matrices";
+            p->units_for_grid = NR / V;
             break;
         }
         default: st = ASP_ERR_UNSUPPORTED; why = "template not implemented"; break;

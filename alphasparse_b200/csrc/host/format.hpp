@@ -122,6 +122,8 @@ struct CompressedBlock
     bool padded = false;
     // block_value operator (not one of the reference's): the sub-matrix is to be stored as dense block_r x block_c blocks
     u64 block_r = 0, block_c = 0;
+    // diag_value operator (not one of the reference's): DIA storage; the most diagonals it may take
+    u64 diag_max = 0;
 
     int n_index() const { return 2 + (blb.built ? 1 : 0) + (wlb.built ? 1 : 0) + (tlb.built ? 3 : 0); }
     u64 nnz() const { return col.size(); }

@@ -114,6 +114,7 @@ int template_of_name(const std::string &k)
         {"K10", ASP_UNALIGNED_WARP_REDUCE_SAME_TLB_SIZE_TEMPLATE_WITH_WARP_REDUCE},
         {"EMPTY", ASP_EMPTY_TEMPLATE},
         {"B1", ASP_BLOCK_ELL_TEMPLATE}, // block-value template of this build (not one of the reference's ten)
+        {"D1", ASP_DIAG_TEMPLATE},      // diagonal-value template of this build
     };
     auto it = tab.find(k);
     return it == tab.end() ? -1 : it->second;
@@ -180,6 +181,12 @@ bool apply_sub_node(CompressedBlock &b, const std::vector<std::string> &tok, std
         if (L(1) == 0 || b.blb.built || b.wlb.built || b.tlb.built) return err = "tlb_nnz needs an untiled sub-matrix", false;
         need_wlb();
         sep_thread_level_acc_to_nnz(b, L(1));
+    }
+    else if (op == "diag_value")
+    {
+        // not a node of the reference: marks the sub-matrix for DIA storage (template D1); optional <max diagonals>, default 64
+        if (b.blb.built || b.wlb.built || b.tlb.built || b.block_r || b.diag_max) return err = "diag_value needs an untiled sub-matrix", false;
+        b.diag_max = L(1) ? L(1) : 64;
     }
     else if (op == "block_value")
     {
@@ -493,7 +500,8 @@ asp_status asp_graph_execute(const asp_matrix *in, const char *spec, asp_format 
                 if (!apply_sub_node(b, tok, err)) return hfail(ASP_ERR_INVALID_ARG, err);
             const int type = template_of_name(s->templ);
             if ((b.block_r != 0) != (type == ASP_BLOCK_ELL_TEMPLATE)) return hfail(ASP_ERR_INVALID_ARG, "the block_value node and the template B1 go together");
-            if (!b.block_r) complete_each_level_blocking(b);
+            if ((b.diag_max != 0) != (type == ASP_DIAG_TEMPLATE)) return hfail(ASP_ERR_INVALID_ARG, "the diag_value node and the template D1 go together");
+            if (!b.block_r && !b.diag_max) complete_each_level_blocking(b);
             if (type < 0) return hfail(ASP_ERR_INVALID_ARG, "unknown template " + s->templ);
             if (type == ASP_EMPTY_TEMPLATE)
             {

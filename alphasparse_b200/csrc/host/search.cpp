@@ -72,6 +72,8 @@ std::vector<Candidate> reference_candidates(int64_t mn, int64_t mx, uint64_t row
         // Matrices that are not made of such blocks fail the lowering or the padding gate.
         for (int64_t rc : {3, 2, 4})
             out.push_back({"S0_B1_" + S(rc) + "x" + S(rc), {"block_value " + S(rc) + " " + S(rc)}, "B1", cross({128}, {1})});
+        // (extension) DIA storage for matrices on a few diagonals
+        if (mx <= 64) out.push_back({"S0_D1", {"diag_value 64"}, "D1", cross({128, 256}, {1})});
     }
     if (mn >= 128)
     {
@@ -164,6 +166,7 @@ std::vector<Candidate> compressed_candidates(uint64_t mn_, uint64_t mx_, double 
     if (!is_sorted)
         for (int64_t rc : {3, 2, 4}) // the block-value operator of this build (see reference_candidates)
             out.push_back({"S0_B1_" + std::to_string(rc) + "x" + std::to_string(rc), {"block_value " + std::to_string(rc) + " " + std::to_string(rc)}, "B1", cross({128}, {1})});
+    if (!is_sorted && mx <= 64) out.push_back({"S0_D1", {"diag_value 64"}, "D1", cross({128, 256}, {1})}); // DIA storage (see reference_candidates)
     if (mn >= 128)
     {
         // strategy 8: BLB_COL_DIV(c) -> long-row template; c = 128 .. min(4096, ceil32(max)), doubling
@@ -375,6 +378,9 @@ bool reference_launches(int templ, const asp_plan_desc &d, const asp_sub_info &i
     case ASP_BLOCK_ELL_TEMPLATE:
         out = cross({128}, {1});
         return true;
+    case ASP_DIAG_TEMPLATE:
+        out = cross({128, 256}, {1});
+        return true;
     default: return false; // the two 3-level templates are not reachable from the whitelist strategies
     }
 }
@@ -397,6 +403,7 @@ int template_id(const std::string &k)
     for (int i = 0; i < 10; i++)
         if (k == names[i]) return i;
     if (k == "B1") return ASP_BLOCK_ELL_TEMPLATE;
+    if (k == "D1") return ASP_DIAG_TEMPLATE;
     return -1;
 }
 
@@ -409,6 +416,7 @@ int64_t derive_tblock(int templ, uint64_t n_tlb, uint64_t n_wlb, uint64_t n_blb,
     case 0: case 1: case 3: case 4: case 5: case 6: n = n_blb; break; // K1 K2 K5 K6 K7 K8
     case 7: n = (32 * n_wlb + (uint64_t)threads - 1) / (uint64_t)threads; break; // K4
     case ASP_BLOCK_ELL_TEMPLATE: n = (n_tlb / 2 + (uint64_t)threads - 1) / (uint64_t)threads; break; // a thread owns two block rows
+    case ASP_DIAG_TEMPLATE: n = (n_tlb + (uint64_t)threads - 1) / (uint64_t)threads; break;            // n_tlb counts the threads' row groups
     default: n = (n_tlb + (uint64_t)threads - 1) / (uint64_t)threads; break;      // K3 K9 K10
     }
     return (int64_t)std::max<uint64_t>(1, std::min<uint64_t>(n, 2147483647ull));

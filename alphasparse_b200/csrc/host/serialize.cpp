@@ -132,7 +132,7 @@ asp_status asp_format_load(const char *path, asp_format **out)
             uint64_t n_arrays = 0;
             ok = get(in.f, s) && get(in.f, F->infos[i]) && get(in.f, n_arrays);
             if (!ok || n_arrays > 64) return asp_host_fail(ASP_ERR_INVALID_ARG, "corrupt sub-matrix record");
-            if (s.template_type < 0 || s.template_type > ASP_BLOCK_ELL_TEMPLATE || (s.template_type != ASP_EMPTY_TEMPLATE && s.val_dt != val_dt) || s.sort_kind < ASP_SORT_NONE || s.sort_kind > ASP_SORT_LOCAL)
+            if (s.template_type < 0 || s.template_type > ASP_DIAG_TEMPLATE || (s.template_type != ASP_EMPTY_TEMPLATE && s.val_dt != val_dt) || s.sort_kind < ASP_SORT_NONE || s.sort_kind > ASP_SORT_LOCAL)
                 return asp_host_fail(ASP_ERR_INVALID_ARG, "corrupt sub-matrix record: template, value type or sort kind out of range");
             if (s.first_row >= F->n_rows || s.first_col >= F->n_cols) return asp_host_fail(ASP_ERR_INVALID_ARG, "corrupt sub-matrix record: first row / column outside the matrix");
             TemplateData &t = F->subs[i];

@@ -8,6 +8,8 @@
 
 #include "format.hpp"
 
+#include <set>
+
 namespace asp
 {
 namespace host
@@ -899,6 +901,53 @@ bool init_block_ell(const Matrix &m, const CompressedBlock &b, TemplateData &t, 
     return true;
 }
 
+// ---- diagonal-value template (this build's; no counterpart in the reference) ------------------------------
+// DIA storage: the distinct offsets col - row of the sub-matrix (at most b.diag_max of them), values diagonal-major.
+bool init_diag(const Matrix &m, const CompressedBlock &b, TemplateData &t, std::string &err)
+{
+    if (m.is_sorted) return err = "diag_value: not for sorted matrices (the diagonals are those of the original row order)", false;
+    if (!(b.min_col == 0 && b.max_col == m.n_cols - 1)) return err = "diag_value: not for column-sliced sub-matrices", false;
+    const int es = b.val.es;
+    const u64 V = 16 / (u64)es, NR = (b.n_rows + V - 1) / V * V;
+    const int64_t ncols = (int64_t)(b.max_col - b.min_col + 1);
+    // distinct offsets; a scattered matrix leaves after a few rows
+    std::set<int64_t> offs;
+    for (u64 r = 0; r < b.n_rows; r++)
+    {
+        for (u64 k = b.rowptr[r]; k < b.rowptr[r + 1]; k++) offs.insert((int64_t)b.col[k] - (int64_t)r);
+        if (offs.size() > b.diag_max) return err = "diag_value: more than " + std::to_string(b.diag_max) + " diagonals hold non-zeros", false;
+    }
+    if (offs.empty()) return err = "diag_value: sub-matrix without non-zeros", false;
+    const std::vector<int64_t> off(offs.begin(), offs.end());
+    const u64 D = off.size();
+    std::vector<uint8_t> val(D * NR * (u64)es, 0);
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < (int64_t)b.n_rows; r++)
+        for (u64 k = b.rowptr[r]; k < b.rowptr[r + 1]; k++)
+        {
+            const u64 d = (u64)(std::lower_bound(off.begin(), off.end(), (int64_t)b.col[k] - r) - off.begin());
+            memcpy(&val[(d * NR + (u64)r) * es], &b.val.b[k * es], es);
+        }
+    common_head(m, b, ASP_DIAG_TEMPLATE, t);
+    t.tlb_size = D;
+    t.effective_num = b.n_rows;
+    t.n_blb = 1;
+    t.n_wlb = 1;
+    t.n_tlb = NR / V;
+    t.thread_num_in_block = 256;
+    t.tblock_num = (long)std::max<u64>(1, (NR / V + 255) / 256);
+    t.arrays.emplace_back();
+    TemplateArray &v = t.arrays.back();
+    v.role = ASP_ARR_VAL;
+    v.dt = t.val_dt;
+    v.len = D * NR;
+    v.bytes.swap(val);
+    std::vector<u64> biased(D);
+    for (u64 d = 0; d < D; d++) biased[d] = (u64)(off[d] + ncols);
+    add_meta(t, ASP_ARR_COL_INDEX, biased, ASP_U64);
+    return true;
+}
+
 bool init_template(const Matrix &m, size_t sub, int type, TemplateData &out, std::string &err)
 {
     if (sub >= m.blocks.size())
@@ -907,6 +956,11 @@ bool init_template(const Matrix &m, size_t sub, int type, TemplateData &out, std
         return false;
     }
     const CompressedBlock &b = m.blocks[sub];
+    if (type == ASP_DIAG_TEMPLATE)
+    {
+        if (!b.diag_max) return err = "the template D1 needs the diag_value node", false;
+        return init_diag(m, b, out, err);
+    }
     if (type == ASP_BLOCK_ELL_TEMPLATE)
     {
         if (!b.block_r) return err = "the template B1 needs the block_value node", false;

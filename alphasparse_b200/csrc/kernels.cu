@@ -1101,6 +1101,7 @@ static cudaError_t launch_v(int templ, int col_width, const KArgs &a, dim3 grid,
 
 cudaError_t launch_template(int templ, int val_is_f64, int col_width, const KArgs &a, unsigned grid, unsigned block, size_t smem, cudaStream_t st, int vec)
 {
+    if (templ == 12) return col_width == 8 ? launch_diag(val_is_f64, a, grid, block, st) : cudaErrorInvalidValue; // diagonal-value template
     if (templ == 11) // block-value template: r and c travel in the two bit-count fields the CSR5-like templates use
         return col_width == 4 ? launch_block_ell(val_is_f64, a.bits_row, a.bits_off, a, grid, block, st) : cudaErrorInvalidValue;
     if (val_is_f64) return launch_v<double>(templ, col_width, a, dim3(grid), dim3(block), smem, st, vec);

@@ -16,6 +16,9 @@ cudaError_t launch_csr5(int val_is_f64, int col_width, int mode, const KArgs &a,
 // tlb_size = block slots per block row, effective = rows of the sub-matrix
 bool block_ell_supported(int r, int c);
 cudaError_t launch_block_ell(int val_is_f64, int r, int c, const KArgs &a, unsigned grid, unsigned block, cudaStream_t st);
+// diagonal-value template (kernels_diag.cu): KArgs::col = u64 offsets biased by the column count, n_tlb = padded rows,
+// tlb_size = diagonals, effective = rows, n_units = columns of the sub-matrix
+cudaError_t launch_diag(int val_is_f64, const KArgs &a, unsigned grid, unsigned block, cudaStream_t st);
 // end rows of the warps (the rows the CSR5-like kernel accumulates with `red`): cleared before, published after
 cudaError_t launch_zero_rows(int val_is_f64, void *y, const unsigned *rows, unsigned long long n, cudaStream_t st);
 cudaError_t launch_publish_rows(int val_is_f64, const void *y, void *y_mc, const unsigned *rows, unsigned long long n, cudaStream_t st);

@@ -74,7 +74,14 @@ typedef enum asp_template_type
      * column of slot k of block row b at [k * NB + b] (u32), ASP_ARR_VAL = element (i, j) of that block at
      * [((k * r + i) * c + j) * NB + b]. Scalars of asp_plan_desc: tlb_size = block slots per block row,
      * effective_num = rows of the sub-matrix, bits_row = r, bits_off = c; NB = len(col) / tlb_size (even). */
-    ASP_BLOCK_ELL_TEMPLATE = 11
+    ASP_BLOCK_ELL_TEMPLATE = 11,
+    /* Not one of the reference's templates either: DIA storage, built by the `diag_value` operator, for matrices
+     * whose non-zeros lie on a few diagonals (banded stencils). One offset per diagonal instead of one column index
+     * per non-zero; x is read as shifted contiguous runs. Arrays: ASP_ARR_COL_INDEX = the D offsets as u64, biased by
+     * (n_cols - first_col) so that they are unsigned; ASP_ARR_VAL = A[r, r + off[d]] at [d * NR + r] (zero where the
+     * diagonal leaves the matrix). Scalars: tlb_size = D, effective_num = rows of the sub-matrix; NR = len(val) / D,
+     * a multiple of 16 / sizeof(value). */
+    ASP_DIAG_TEMPLATE = 12
 } asp_template_type;
 
 /* role of an array inside a template; names are the reference's struct field names

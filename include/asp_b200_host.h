@@ -42,7 +42,9 @@ uint64_t asp_matrix_nnz(const asp_matrix *m);
  *   sub <id|all> tlb_row | tlb_col_fixed <nnz> | tlb_nnz <nnz>
  *   sub <id|all> block_value <r> <c>        (no node of the reference) store the sub-matrix as dense r x c blocks:
  *                                            2 x 2, 3 x 3 or 4 x 4; alone in its sub-graph, followed by `template B1`
- *   sub <id|all> template K1..K10 | B1 [tblock threads [row_reduce]]
+ *   sub <id|all> diag_value [<max diagonals>] (no node of the reference) DIA storage for matrices whose non-zeros lie on at
+ *                                            most <max> (default 64) diagonals; alone in its sub-graph, followed by `template D1`
+ *   sub <id|all> template K1..K10 | B1 | D1 [tblock threads [row_reduce]]
  * (node names: exe_graph.hpp:36-57; strategies: parameter_set_strategy.hpp:10-25; K1..K10 are
  * the templates of code_builder.hpp:15-29 in the order DIRECT_ATOM, _WARP_COMPRESS,
  * _WARP_BLOCK_COMPRESS, DIRECT_ATOM_TOTAL_WARP_REDUCE, SHARED_MEMORY, _WARP_COMPRESS, _LONG_ROW,
