@@ -61,7 +61,10 @@ WORKLOADS["plong"] = ("profiling matrix: 60,000 rows of 1000..3000 non-zeros, fp
 # run replays them after its own timed region instead of searching again.
 COMMITTED_GRAPHS = {
     "c1": {"dense": "dense compress", "subs": [{"graph": "S2_K6_m64_c4", "nodes": ["row_padding 64 1", "blb_row_evenly 64", "tlb_col_fixed 4"], "template": "K6", "threads": 128, "row_reduce": 1}]},
-    "c2": {"dense": "dense compress", "subs": [{"graph": "S5_K3", "nodes": ["row_padding 32 1", "tlb_row"], "template": "K3", "threads": 128, "row_reduce": 1}]},
+    # c2: the diagonal-value operator of this build (DIA storage: no column index per non-zero); the best graph over the
+    # reference's own operators beside it
+    "c2": {"dense": "dense compress", "subs": [{"graph": "S0_D1", "nodes": ["diag_value 64"], "template": "D1", "threads": 128, "row_reduce": 1}]},
+    "c2_reference_operators": {"dense": "dense compress", "subs": [{"graph": "S5_K3", "nodes": ["row_padding 32 1", "tlb_row"], "template": "K3", "threads": 128, "row_reduce": 1}]},
     "c3": {"dense": "dense compress", "subs": [{"graph": "S9_K9_s16", "nodes": ["tlb_nnz 16"], "template": "K9", "threads": 128, "row_reduce": 2}]},
     # c4: the block-value operator of this build (one block-column index per 3 x 3 block); the best graph over the
     # reference's own operators is kept beside it, and the default run reports both
@@ -70,6 +73,7 @@ COMMITTED_GRAPHS = {
 }
 COMMITTED_GRAPHS["c4s"] = COMMITTED_GRAPHS["c4"]
 WORKLOADS["c4_reference_operators"] = WORKLOADS["c4"]
+WORKLOADS["c2_reference_operators"] = WORKLOADS["c2"]
 
 
 def profiled_traffic(workload: str, graph_desc) -> float | None:
@@ -692,7 +696,7 @@ def main():
     ap.add_argument("--threads", type=int, default=0, help="with --spec: thread_num_in_block")
     ap.add_argument("--graph", default=None, help="skip the search: a bench JSON line file (its config.graph is used) or the graph JSON itself")
     ap.add_argument("--committed", action="store_true", help="single-GPU workloads: replay the committed graph instead of searching")
-    ap.add_argument("--configs", default="c1,c2,c3,c4,c4_reference_operators", help="c5 at N = 1: single-GPU configurations to attach to the line")
+    ap.add_argument("--configs", default="c1,c2,c2_reference_operators,c3,c4,c4_reference_operators", help="c5 at N = 1: single-GPU configurations to attach to the line")
     ap.add_argument("--no-configs", action="store_true")
     ap.add_argument("--configs-budget-s", type=float, default=600.0, help="no further sub-configuration is started once the run has taken this long")
     ap.add_argument("--profile-launches", type=int, default=0, help="for ncu captures: build the plan, run this many SpMVs and exit (no timing, one short JSON line)")
