@@ -100,7 +100,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
     else:
         sort = args.sort != "no"  # (auto = yes: unpermuted rows were measured slower with every exchange form)
         desc = graph_with_tlb_size(args.tlb or 32, sort)
-    fmts, groups, chunks = [], [], []
+    fmts, groups, chunks, chunk_groups = [], [], [], []
     build_error = None
     # most rows first: with a separate store pass the exchange of the last chunk is the only one no kernel hides
     order = sorted(range(n_chunks), key=lambda c: -(int(cuts[c + 1]) - int(cuts[c])))
@@ -112,6 +112,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
                 yt.zero_()
 
             chunks.append((fz, lo, hi, (lambda xp, yp, mp: None)))
+            chunk_groups.append(None)
             continue
         mc = m.row_slice(lo, hi) if n_chunks > 1 else m
         try:
@@ -132,6 +133,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
             g.spmv_publish(xp, yp, mp)
 
         chunks.append((fn, lo, hi, pub))
+        chunk_groups.append(g)
         del mc
     all_ranks_ok(build_error is None, f"lowering / upload of the row block ({build_error})", dev)
     search_s = time.perf_counter() - t0
@@ -142,6 +144,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
         sh = ShardedSpmv(None, bounds, rank, world, torch.float32, dev, chunks=chunks, exchange=args.exchange)
         xa = sh.new_vector()
         xb = sh.new_vector()
+        native = getattr(args, "loop", "native") == "native" and build_error is None and sh.use_native_loop(ctx, chunk_groups)
         # parity of the first SpMV of this rank's slice (the caller's checker; bounded sizes only)
         parity = None
         y1 = sh.spmv_slice(x0).clone()
@@ -203,7 +206,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
         "ms_per_step": ms_step, "ms_per_spmv": ms_step / iters, "ms_compute_per_spmv_max": float(t[1].item()), "ms_per_step_median": float(t[2].item()),
         "gflops": 2.0 * nnz_all * iters / (ms_step * 1e-3) * 1e-9, "nnz": nnz_all, "rows": n, "iters": iters, "graph": desc,
         "search_s": search_s, "gen_s": gen_s, "parity": parity, "rows_local": r1 - r0, "nnz_local": nnz_local, "timed_wall_s": timed_wall_s,
-        "format_bytes": int(sum(g.format_bytes() for g in groups)), "launches_per_spmv": launches, "chunks": n_chunks, "exchange_used": sh._mode if world > 1 else "none",
+        "format_bytes": int(sum(g.format_bytes() for g in groups)), "launches_per_spmv": launches, "chunks": n_chunks, "exchange_used": sh._mode if world > 1 else "none", "loop": "native (asp_dist_spmv_iter)" if native else "python",
         "fallback_reason": getattr(sh, "fallback_reason", None), "barrier": "flag kernel" if sh._flags is not None else ("nccl all_reduce" if world > 1 else "none"),
         "end_rows_local": int(sum(g.end_rows() for g in groups)), "staged": bool(args.stage),
         "m_local": m, "group": groups, "ctx": ctx, "x0": x0, "sharded": sh, "fmt": fmts, "bufs": (xa, xb),

@@ -59,10 +59,21 @@ EXPORTS = [
     "asp_ctx_create", "asp_multicast_store", "asp_spmv_publish", "asp_plan_end_rows", "asp_rank_barrier", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_descs_validate", "asp_plan_destroy",
     "asp_plan_set_launch", "asp_plan_get_launch", "asp_plan_set_tuning", "asp_plan_format_bytes", "asp_plan_launches", "asp_spmv", "asp_spmv_host", "asp_time",
     "asp_synchronize", "asp_status_str", "asp_last_error", "asp_built_for_sm100a", "asp_spmv_host_static",
-    "asp_static_stage_bytes", "asp_search_gpu",
+    "asp_static_stage_bytes", "asp_search_gpu", "asp_dist_create", "asp_dist_destroy", "asp_dist_spmv", "asp_dist_spmv_iter", "asp_dist_status",
 ]
 
 _lib = None
+
+
+class DistChunk(C.Structure):
+    """asp_dist_chunk"""
+    _fields_ = [("plans", C.POINTER(C.c_void_p)), ("n_plans", C.c_int), ("row_lo", C.c_uint64), ("row_hi", C.c_uint64)]
+
+
+class DistDesc(C.Structure):
+    """asp_dist_desc"""
+    _fields_ = [("rank", C.c_int), ("world", C.c_int), ("value_is_f64", C.c_int), ("n", C.c_uint64), ("chunks", C.POINTER(DistChunk)),
+                ("n_chunks", C.c_int), ("flags_local", C.c_void_p), ("flags_multicast", C.c_void_p), ("max_polls", C.c_uint)]
 
 
 class AspError(RuntimeError):
@@ -128,6 +139,16 @@ def lib() -> C.CDLL:
     L.asp_last_error.restype = C.c_char_p
     L.asp_built_for_sm100a.argtypes = []
     L.asp_built_for_sm100a.restype = C.c_int
+    L.asp_dist_create.argtypes = [C.c_void_p, C.POINTER(DistDesc), C.POINTER(C.c_void_p)]
+    L.asp_dist_create.restype = C.c_int
+    L.asp_dist_destroy.argtypes = [C.c_void_p]
+    L.asp_dist_destroy.restype = None
+    L.asp_dist_spmv.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.asp_dist_spmv.restype = C.c_int
+    L.asp_dist_spmv_iter.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_int)]
+    L.asp_dist_spmv_iter.restype = C.c_int
+    L.asp_dist_status.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
+    L.asp_dist_status.restype = C.c_int
     _lib = L
     return L
 
@@ -290,6 +311,52 @@ class PlanGroup:
             if self._plans[i]:
                 lib().asp_plan_destroy(self._plans[i])
                 self._plans[i] = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class DistLoop:
+    """The sharded repeated SpMV of one rank as a native loop (asp_dist_*). `chunks`: [(PlanGroup or None,
+    first global row, end global row)] in the order they are computed; vectors and flags are device
+    pointers (ints) of symmetric memory the caller owns."""
+
+    def __init__(self, ctx: Context, chunks, n: int, rank: int = 0, world: int = 1, f64: bool = False, flags_local: int = 0, flags_multicast: int = 0,
+                 max_polls: int = 0):
+        self.ctx = ctx
+        self._groups = [g for g, _, _ in chunks]  # keep the plan groups alive
+        arr = (DistChunk * len(chunks))()
+        for i, (g, lo, hi) in enumerate(chunks):
+            arr[i].plans = C.cast(g._plans, C.POINTER(C.c_void_p)) if g is not None else None
+            arr[i].n_plans = g.n if g is not None else 0
+            arr[i].row_lo, arr[i].row_hi = int(lo), int(hi)
+        d = DistDesc(rank, world, 1 if f64 else 0, int(n), arr, len(chunks), flags_local or None, flags_multicast or None, max_polls)
+        self._h = C.c_void_p()
+        check(lib().asp_dist_create(ctx.handle, C.byref(d), C.byref(self._h)))
+
+    def spmv(self, d_x: int, d_y: int, d_y_multicast: int = 0) -> None:
+        check(lib().asp_dist_spmv(self._h, C.c_void_p(d_x), C.c_void_p(d_y), C.c_void_p(d_y_multicast or None)))
+
+    def iterate(self, d_x0: int, bufs, bufs_multicast, iters: int) -> int:
+        """x <- A x `iters` times from d_x0; returns the index (0 / 1) of the buffer that holds the result."""
+        b = (C.c_void_p * 2)(bufs[0], bufs[1])
+        m = (C.c_void_p * 2)(bufs_multicast[0] or None, bufs_multicast[1] or None) if bufs_multicast else None
+        last = C.c_int(-1)
+        check(lib().asp_dist_spmv_iter(self._h, C.c_void_p(d_x0), b, m, iters, C.byref(last)))
+        return last.value
+
+    def status(self) -> None:
+        """Waits for the stream; raises AspError (status 7) when a barrier gave up waiting for a rank."""
+        w = C.c_int(-1)
+        check(lib().asp_dist_status(self._h, C.byref(w)))
+
+    def close(self):
+        if self._h:
+            lib().asp_dist_destroy(self._h)
+            self._h = C.c_void_p()
 
     def __del__(self):
         try:

@@ -497,6 +497,7 @@ const char *asp_status_str(asp_status s)
     case ASP_ERR_ALLOC: return "allocation failed";
     case ASP_ERR_BOUNDS: return "format array out of bounds";
     case ASP_ERR_IMPLAUSIBLE: return "implausible throughput";
+    case ASP_ERR_TIMEOUT: return "bounded device-side wait expired";
     default: return "unknown";
     }
 }
@@ -1376,6 +1377,167 @@ asp_status asp_time(asp_ctx *ctx, asp_plan *const *plans, int n_plans, int warmu
     if (gflops) *gflops = (float)gf;
     if (gflops_up_bound > 0 && gf > gflops_up_bound) return fail(ASP_ERR_IMPLAUSIBLE, "throughput above the configured GFLOPS_UP_BOUND");
     return ASP_OK;
+}
+
+// ---- the sharded repeated SpMV as a native loop -------------------------------------------------
+struct asp_dist
+{
+    asp_ctx *ctx = nullptr;
+    int rank = 0, world = 1;
+    size_t es = 4;
+    uint64_t n = 0;
+    struct Chunk
+    {
+        std::vector<asp_plan *> plans;
+        uint64_t lo = 0, hi = 0;
+        cudaEvent_t done = nullptr; // the chunk's kernels have finished (recorded on the context's stream)
+    };
+    std::vector<Chunk> chunks;
+    cudaStream_t comm = nullptr;   // carries the store passes and the barrier, under the next chunk's kernels
+    cudaEvent_t exchanged = nullptr;
+    const void *flags_local = nullptr;
+    void *flags_mc = nullptr;
+    unsigned *status = nullptr;    // device word the barrier kernel reports to
+    unsigned epoch = 0, max_polls = 0;
+};
+
+asp_status asp_dist_create(asp_ctx *ctx, const asp_dist_desc *desc, asp_dist **out)
+{
+    if (!out) return fail(ASP_ERR_INVALID_ARG, "out is NULL");
+    *out = nullptr;
+    if (!ctx || !desc || !desc->chunks || desc->n_chunks <= 0) return fail(ASP_ERR_INVALID_ARG, "NULL argument or no chunks");
+    if (desc->world < 1 || desc->world > 32 || desc->rank < 0 || desc->rank >= desc->world) return fail(ASP_ERR_INVALID_ARG, "rank / world out of range (at most 32 ranks)");
+    if (desc->world > 1 && (!desc->flags_local || !desc->flags_multicast)) return fail(ASP_ERR_INVALID_ARG, "more than one rank needs the symmetric flag array");
+    std::unique_ptr<asp_dist, void (*)(asp_dist *)> d(new (std::nothrow) asp_dist(), asp_dist_destroy);
+    if (!d) return fail(ASP_ERR_ALLOC, "host allocation failed");
+    d->ctx = ctx;
+    d->rank = desc->rank;
+    d->world = desc->world;
+    d->es = desc->value_is_f64 ? 8 : 4;
+    d->n = desc->n;
+    d->flags_local = desc->flags_local;
+    d->flags_mc = desc->flags_multicast;
+    d->max_polls = desc->max_polls;
+    // the chunks must tile one contiguous row block and agree with their plan groups
+    std::vector<std::pair<uint64_t, uint64_t>> spans;
+    for (int c = 0; c < desc->n_chunks; c++)
+    {
+        const asp_dist_chunk &in = desc->chunks[c];
+        if (in.row_hi < in.row_lo || in.row_hi > desc->n) return fail(ASP_ERR_INVALID_ARG, "chunk rows outside the vector");
+        if (in.n_plans < 0 || (in.n_plans > 0 && !in.plans)) return fail(ASP_ERR_INVALID_ARG, "chunk without plans");
+        asp_dist::Chunk ch;
+        ch.lo = in.row_lo;
+        ch.hi = in.row_hi;
+        if (in.n_plans > 0)
+        {
+            GroupShape g;
+            asp_status gs = group_shape(in.plans, in.n_plans, &g);
+            if (gs != ASP_OK) return gs;
+            if (g.n_rows != in.row_hi - in.row_lo) return fail(ASP_ERR_INVALID_ARG, "a chunk's plan group has another number of rows than the chunk");
+            if (g.n_cols != desc->n) return fail(ASP_ERR_INVALID_ARG, "a chunk's plan group has another number of columns than the vector");
+            if (g.es != d->es) return fail(ASP_ERR_INVALID_ARG, "a chunk's plan group has another value type");
+            ch.plans.assign(in.plans, in.plans + in.n_plans);
+        }
+        if (ch.hi > ch.lo) spans.push_back({ch.lo, ch.hi});
+        d->chunks.push_back(std::move(ch));
+    }
+    std::sort(spans.begin(), spans.end());
+    for (size_t i = 1; i < spans.size(); i++)
+        if (spans[i].first != spans[i - 1].second) return fail(ASP_ERR_INVALID_ARG, "the chunks do not tile one contiguous row block");
+    ASP_ON_DEVICE(ctx);
+    for (auto &ch : d->chunks) ASP_CUDA(cudaEventCreateWithFlags(&ch.done, cudaEventDisableTiming));
+    if (d->world > 1)
+    {
+        ASP_CUDA(cudaStreamCreateWithFlags(&d->comm, cudaStreamNonBlocking));
+        ASP_CUDA(cudaEventCreateWithFlags(&d->exchanged, cudaEventDisableTiming));
+        ASP_CUDA(cudaMalloc((void **)&d->status, 256));
+        ASP_CUDA(cudaMemsetAsync(d->status, 0, 256, ctx->stream));
+    }
+    *out = d.release();
+    return ASP_OK;
+}
+
+void asp_dist_destroy(asp_dist *d)
+{
+    if (!d) return;
+    if (d->ctx)
+    {
+        DeviceGuard guard(d->ctx->device);
+        if (d->comm) cudaStreamSynchronize(d->comm);
+        for (auto &ch : d->chunks)
+            if (ch.done) cudaEventDestroy(ch.done);
+        if (d->exchanged) cudaEventDestroy(d->exchanged);
+        if (d->comm) cudaStreamDestroy(d->comm);
+        if (d->status) cudaFree(d->status);
+    }
+    delete d;
+}
+
+asp_status asp_dist_spmv(asp_dist *d, const void *d_x, void *d_y, void *d_y_multicast)
+{
+    if (!d || !d_x || !d_y) return fail(ASP_ERR_INVALID_ARG, "NULL argument");
+    if (d->world > 1 && !d_y_multicast) return fail(ASP_ERR_INVALID_ARG, "more than one rank needs the multicast address of y");
+    if (d_x == d_y) return fail(ASP_ERR_INVALID_ARG, "x and y must be different buffers");
+    asp_ctx *ctx = d->ctx;
+    ASP_ON_DEVICE(ctx);
+    for (auto &ch : d->chunks)
+    {
+        const size_t off = (size_t)ch.lo * d->es, bytes = (size_t)(ch.hi - ch.lo) * d->es;
+        if (bytes == 0) continue;
+        unsigned char *dst = (unsigned char *)d_y + off;
+        if (ch.plans.empty()) ASP_CUDA(cudaMemsetAsync(dst, 0, bytes, ctx->stream));
+        else
+        {
+            // rows without non-zeros are never stored by a kernel: clear the slice first
+            asp_status st = asp_spmv(ctx, ch.plans.data(), (int)ch.plans.size(), d_x, dst, 1);
+            if (st != ASP_OK) return st;
+        }
+        if (d->world == 1) continue;
+        ASP_CUDA(cudaEventRecord(ch.done, ctx->stream));
+        ASP_CUDA(cudaStreamWaitEvent(d->comm, ch.done, 0));
+        asp_status st = asp_multicast_store(dst, (unsigned char *)d_y_multicast + off, bytes, d->comm, 0);
+        if (st != ASP_OK) return fail(st, "multicast store pass refused (buffers must be congruent modulo 16)");
+    }
+    if (d->world == 1) return ASP_OK;
+    // every rank's stores are in every replica past the barrier; the next SpMV waits for it
+    asp_status st = asp_rank_barrier(d->flags_local, d->flags_mc, d->rank, d->world, ++d->epoch, d->status, d->max_polls, d->comm);
+    if (st != ASP_OK) return fail(st, "barrier kernel launch failed");
+    ASP_CUDA(cudaEventRecord(d->exchanged, d->comm));
+    ASP_CUDA(cudaStreamWaitEvent(ctx->stream, d->exchanged, 0));
+    return ASP_OK;
+}
+
+asp_status asp_dist_spmv_iter(asp_dist *d, const void *d_x0, void *const d_buf[2], void *const d_buf_multicast[2], int iters, int *final_buf)
+{
+    if (!d || !d_x0 || !d_buf || !d_buf[0] || !d_buf[1] || iters < 0) return fail(ASP_ERR_INVALID_ARG, "NULL argument or negative iteration count");
+    if (d->world > 1 && (!d_buf_multicast || !d_buf_multicast[0] || !d_buf_multicast[1])) return fail(ASP_ERR_INVALID_ARG, "more than one rank needs the multicast addresses of both buffers");
+    if (d_x0 == d_buf[0] || d_x0 == d_buf[1] || d_buf[0] == d_buf[1]) return fail(ASP_ERR_INVALID_ARG, "x0 and the two buffers must be three different vectors");
+    const void *x = d_x0;
+    int last = -1;
+    for (int i = 0; i < iters; i++)
+    {
+        const int b = i & 1;
+        asp_status st = asp_dist_spmv(d, x, d_buf[b], d->world > 1 ? d_buf_multicast[b] : nullptr);
+        if (st != ASP_OK) return st;
+        x = d_buf[b];
+        last = b;
+    }
+    if (final_buf) *final_buf = last;
+    return ASP_OK;
+}
+
+asp_status asp_dist_status(asp_dist *d, int *waiting_for_rank)
+{
+    if (!d) return fail(ASP_ERR_INVALID_ARG, "NULL argument");
+    if (waiting_for_rank) *waiting_for_rank = -1;
+    ASP_ON_DEVICE(d->ctx);
+    ASP_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    if (!d->status) return ASP_OK;
+    unsigned v = 0;
+    ASP_CUDA(cudaMemcpy(&v, d->status, sizeof(v), cudaMemcpyDeviceToHost));
+    if (v == 0) return ASP_OK;
+    if (waiting_for_rank) *waiting_for_rank = (int)v - 1;
+    return fail(ASP_ERR_TIMEOUT, "a barrier of the sharded SpMV gave up waiting for rank " + std::to_string((int)v - 1));
 }
 
 } // extern "C"

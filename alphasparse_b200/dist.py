@@ -190,6 +190,34 @@ class ShardedSpmv:
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._symm_keep.append((f, hdl))
 
+    def use_native_loop(self, ctx, groups, max_polls: int = 0) -> bool:
+        """Moves step_into() / iterate() behind the C ABI (asp_dist_create / asp_dist_spmv_iter): the same
+        chunk kernels, store passes and barrier kernel, enqueued by one native call per iteration loop.
+        `groups[c]` is the PlanGroup of the c-th chunk (None for a chunk without non-zeros). Only for the
+        multicast exchange with the flag barrier (or a single rank); call it after the vectors were made
+        and before the first step. Returns whether ALL ranks switched (agreed collectively)."""
+        from . import capi
+
+        self._native = None
+        ok = self.world == 1 or (self._mode == "multicast" and self._flags is not None)
+        loop = None
+        if ok:
+            try:
+                base = self.bounds[self.rank]
+                ch = [(g, base + lo, base + hi) for g, (_, lo, hi) in zip(groups, self.chunks)]
+                loop = capi.DistLoop(ctx, ch, self.n, self.rank, self.world, self._dtype == torch.float64,
+                                     self._flags.data_ptr() if self._flags is not None else 0, self._flags_mc or 0, max_polls)
+            except Exception as e:
+                self.native_error = repr(e)[:200]
+                ok = False
+        if self.world > 1 and not self._all_agree(ok):
+            ok = False
+        if ok:
+            self._native = loop
+        elif loop is not None:
+            loop.close()
+        return ok
+
     def _barrier(self) -> None:
         """All ranks' published rows are in every replica past this point (on the current stream)."""
         if self._flags is not None:
@@ -203,6 +231,8 @@ class ShardedSpmv:
 
     def check_barrier_status(self) -> None:
         """Raises if a barrier kernel gave up waiting for a rank (the wait is bounded by design)."""
+        if getattr(self, "_native", None) is not None:
+            self._native.status()  # raises AspError (status 7: a bounded wait expired)
         if self._status is not None and int(self._status.item()) != 0:
             raise RuntimeError(f"rank barrier timed out waiting for rank {int(self._status.item()) - 1}")
 
@@ -247,6 +277,9 @@ class ShardedSpmv:
         # (Running the chunks' kernels concurrently on prioritised streams was measured and lost:
         # the chunks then finish together and no exchange is hidden.)
         base = self.bounds[self.rank]
+        if getattr(self, "_native", None) is not None:
+            self._native.spmv(x.data_ptr(), x_next.data_ptr(), self._mc.get(x_next.data_ptr(), 0))
+            return
         if self._mode == "publish":
             mc = self._mc.get(x_next.data_ptr())
             if mc is None:
@@ -279,6 +312,10 @@ class ShardedSpmv:
         vectors x0 is only read (the results alternate between the two); with one, x0 itself is the
         second buffer and is overwritten from the second iteration on. The publishing exchange needs
         two, both from new_vector(): it relies on rows that are never written staying zero."""
+        if scratch2 is not None and getattr(self, "_native", None) is not None:
+            outs = (scratch, scratch2)
+            last = self._native.iterate(x0.data_ptr(), [t.data_ptr() for t in outs], [self._mc.get(t.data_ptr(), 0) for t in outs], iters)
+            return x0 if last < 0 else outs[last]
         if scratch2 is not None:
             a, outs = x0, (scratch, scratch2)
             for i in range(iters):

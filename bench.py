@@ -378,7 +378,7 @@ def run_c5(args, rank, world, local_rank, dist):
                        "row_chunks_per_rank": r["chunks"], "balance": args.balance, "staged_row_sums": r["staged"],
                        "exchange": "none (1 GPU)" if world == 1 else {"publish": "rows leave the SpMV kernel through the NVLink multicast address (multimem.st), end rows of the warps by a small kernel after it",
                                                                        "multicast": "multicast store pass per row chunk on a second stream, overlapped with the next chunk's kernel"}.get(r["exchange_used"], r["exchange_used"]),
-                       "barrier": r["barrier"], "exchange_fallback": r["fallback_reason"],
+                       "barrier": r["barrier"], "loop": r["loop"], "exchange_fallback": r["fallback_reason"],
                        "values": "x grows by about 8x per SpMV and overflows fp32 after ~40 of the 100: the later SpMVs multiply inf / NaN (same memory traffic); parity is checked on the first SpMV"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world), "traffic": profiled_traffic("c5", r["graph"]) if world == 1 else None,
                          "peak_kind": peak_kind, "algorithmic_bytes": b_alg, "launch": f"{iters} SpMV launches per step; peak = {world} x the measured copy bandwidth",
@@ -679,6 +679,8 @@ def main():
     ap.add_argument("--exchange", default="multicast", choices=["multicast", "publish", "allgather", "a2a"],
                     help="c5: how a rank's slice of the next x reaches the others: from inside the SpMV kernel (publish), by a multicast store pass per "
                          "chunk, or by NCCL (both multicast modes fall back to allgather where symmetric memory has no multicast address)")
+    ap.add_argument("--loop", default="native", choices=["native", "python"], help="c5: who enqueues the repeated SpMVs: the native loop behind the C ABI "
+                    "(asp_dist_spmv_iter; multicast exchange and single GPU) or the Python one (every exchange form)")
     ap.add_argument("--balance", default="6", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
                     "or a number w (a row with non-zeros weighs w non-zeros; measured at 4 GPUs: 6 evens out the ranks' kernel times to 3 %%, "
                     "nnz leaves the rank with the sparse tail 10 %% behind)")

@@ -27,7 +27,8 @@ typedef enum asp_status
     ASP_ERR_CUDA = 3,        /* a CUDA runtime call failed; asp_last_error() has the text   */
     ASP_ERR_ALLOC = 4,       /* host or device allocation failed                            */
     ASP_ERR_BOUNDS = 5,      /* a format array refers outside val/col/x/y                   */
-    ASP_ERR_IMPLAUSIBLE = 6  /* measured throughput above the configured sanity bound       */
+    ASP_ERR_IMPLAUSIBLE = 6, /* measured throughput above the configured sanity bound       */
+    ASP_ERR_TIMEOUT = 7      /* a bounded wait on the device expired (asp_dist_status)      */
 } asp_status;
 
 /* element types of format arrays; the reference narrows every index array to the smallest
@@ -263,6 +264,48 @@ uint64_t asp_plan_end_rows(const asp_plan *plan);
  * in the reference. */
 asp_status asp_rank_barrier(const void *flags_local, void *flags_multicast, int rank, int world, unsigned epoch, void *status_u32, unsigned max_polls,
                             void *stream);
+
+/* The sharded repeated SpMV (x <- A x, square matrix, x replicated on the GPUs of one NVLink domain, every rank
+ * owning a contiguous row block) as one native loop per rank; no counterpart in the reference, which is
+ * single-GPU (code_builder.cc:1483-1489). A rank's block is cut into row chunks, each with its own plan group
+ * built over ALL columns; the chunks are computed in the order given, and as soon as one is finished its rows
+ * are stored once through the NVLink multicast address of the result vector (asp_multicast_store) on a second
+ * stream, under the next chunk's kernels, so only the LAST chunk's exchange is exposed: put the chunk with
+ * the fewest rows last. One asp_rank_barrier per SpMV orders the ranks. The ranks may cut their blocks into
+ * different numbers of chunks. Vectors and the flag array are symmetric memory that the caller allocated,
+ * bound to multicast objects and zeroed (e.g. torch.distributed._symmetric_memory); the library sees plain
+ * pointers only. One rank per GPU. */
+typedef struct asp_dist asp_dist;
+typedef struct
+{
+    asp_plan *const *plans; /* the chunk's plan group; n_rows = row_hi - row_lo, n_cols = the vector length */
+    int n_plans;            /* 0: the chunk has no non-zeros, its rows are cleared */
+    uint64_t row_lo, row_hi; /* global rows [row_lo, row_hi) the group produces */
+} asp_dist_chunk;
+typedef struct
+{
+    int rank, world;       /* at most 32 ranks */
+    int value_is_f64;
+    uint64_t n;            /* length of the replicated vector */
+    const asp_dist_chunk *chunks; /* tile one contiguous row block, in the order they are computed */
+    int n_chunks;
+    const void *flags_local; /* world > 1: this GPU's replica and the multicast address of a symmetric array of */
+    void *flags_multicast;   /* at least `world` 32-bit words, zero at first, used by nothing else              */
+    unsigned max_polls;      /* bound of the barrier's wait, 0 = about a second */
+} asp_dist_desc;
+asp_status asp_dist_create(asp_ctx *ctx, const asp_dist_desc *desc, asp_dist **out);
+void asp_dist_destroy(asp_dist *d);
+/* y <- A x on every rank: d_y is this GPU's replica of the result vector, d_y_multicast the multicast address
+ * of the same vector (ignored when world == 1). Asynchronous on the context's stream, on which the result is
+ * complete in every replica. x and y must be different vectors. */
+asp_status asp_dist_spmv(asp_dist *d, const void *d_x, void *d_y, void *d_y_multicast);
+/* x <- A x, `iters` times, starting from d_x0 (only read); the results alternate between the two buffers
+ * (iteration i writes d_buf[i & 1]); *final_buf = index of the buffer that holds the last result (-1 when
+ * iters == 0). */
+asp_status asp_dist_spmv_iter(asp_dist *d, const void *d_x0, void *const d_buf[2], void *const d_buf_multicast[2], int iters, int *final_buf);
+/* Waits for the context's stream, then ASP_OK, or ASP_ERR_TIMEOUT with *waiting_for_rank = the rank a barrier
+ * gave up on (its wait is bounded by design: a rank that never arrives costs seconds, not a hung GPU). */
+asp_status asp_dist_status(asp_dist *d, int *waiting_for_rank);
 
 /* replaces execute_binary + perf_result parsing (executor.cc:6-59): CUDA-event timing of
  * `reps` SpMVs after `warmup`, x and y internal (x = 100 everywhere, as the generated main()

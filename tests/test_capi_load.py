@@ -43,6 +43,7 @@ def test_status_strings():
     L = capi.lib()
     assert L.asp_status_str(0) == b"ok"
     assert L.asp_status_str(5) == b"format array out of bounds"
+    assert L.asp_status_str(7) == b"bounded device-side wait expired"
 
 
 def test_argument_errors_of_the_multi_gpu_entry_points_need_no_device():
@@ -60,3 +61,10 @@ def test_argument_errors_of_the_multi_gpu_entry_points_need_no_device():
     assert L.asp_multicast_store(None, None, 16, None, 0) == 1
     assert L.asp_multicast_store(p, p, 0, None, 0) == 0          # nothing to store
     assert L.asp_plan_descs_validate(None, 0) == 1
+    # the native loop of the sharded SpMV
+    out = C.c_void_p(1)
+    assert L.asp_dist_create(None, None, C.byref(out)) == 1 and not out.value
+    assert L.asp_dist_spmv(None, p, p, p) == 1
+    assert L.asp_dist_spmv_iter(None, p, None, None, 1, None) == 1
+    assert L.asp_dist_status(None, None) == 1
+    L.asp_dist_destroy(None)

@@ -40,7 +40,8 @@ def _reference_iterations(m, x, iters):
     return ref
 
 
-def test_row_chunks_on_one_gpu_match_the_oracle(asp_ctx):
+@pytest.mark.parametrize("loop", ["python", "native"])
+def test_row_chunks_on_one_gpu_match_the_oracle(asp_ctx, loop):
     m, x = M.rmat(13, 16, seed=4)
     m.values *= 0.02
     keep = []
@@ -48,6 +49,8 @@ def test_row_chunks_on_one_gpu_match_the_oracle(asp_ctx):
     stream = torch.cuda.ExternalStream(asp_ctx.stream)
     with torch.cuda.stream(stream):
         sh = ShardedSpmv(None, [0, m.n_rows], 0, 1, torch.float32, "cuda", chunks=chunks)
+        if loop == "native":  # the same loop behind the C ABI (asp_dist_spmv_iter)
+            assert sh.use_native_loop(asp_ctx, [g for _, g in keep])
         x0 = torch.from_numpy(x).cuda()
         y = sh.spmv_slice(x0).clone()
         xf = sh.iterate(x0, 3, sh.new_vector(), sh.new_vector())
@@ -106,6 +109,8 @@ def _worker(rank, world, port, mode, out_dir):
     ctx = capi.Context(rank)
     keep = []
     # the multicast forms pair nothing across ranks: every rank cuts its block as it likes
+    native = mode == "native"
+    mode = "multicast" if native else mode
     n_chunks = 2 if mode in ("allgather", "a2a") else (1 if rank == 0 else 3)
     chunks = _chunks(ctx, blk, n_chunks, keep)
     stream = torch.cuda.ExternalStream(ctx.stream)
@@ -113,10 +118,23 @@ def _worker(rank, world, port, mode, out_dir):
     with torch.cuda.stream(stream):
         sh = ShardedSpmv(None, bounds, rank, world, torch.float32, torch.device("cuda", rank), chunks=chunks, exchange=mode)
         a, b = sh.new_vector(), sh.new_vector()
+        went_native = native and sh.use_native_loop(ctx, [g for _, g in keep], max_polls=20000)
         x0 = torch.from_numpy(x).cuda()
         xf = sh.iterate(x0, 3, a, b)  # x0 is only read; the results alternate between a and b
         torch.cuda.synchronize()
         sh.check_barrier_status()
+        if went_native:
+            # one more SpMV on rank 0 alone: its barrier runs out (bounded wait) and asp_dist_status names rank 1
+            xf = xf.clone()
+            dist.barrier()
+            if rank == 0:
+                sh.step_into(x0, a)
+                try:
+                    sh.check_barrier_status()
+                    timed_out = "no"
+                except capi.AspError as e:
+                    timed_out = str(e)
+            dist.barrier()
         if mode == "publish" and sh._flags is not None:
             # a barrier that one rank never joins runs out (bounded wait) and reports which rank was missing
             dist.barrier()
@@ -132,7 +150,7 @@ def _worker(rank, world, port, mode, out_dir):
             dist.barrier()
     np.save(os.path.join(out_dir, f"final_{rank}.npy"), xf.cpu().numpy())
     with open(os.path.join(out_dir, f"mode_{rank}.txt"), "w") as fh:
-        fh.write(f"{sh._mode};{'flags' if sh._flags is not None else 'nccl'};{timed_out}")
+        fh.write(f"{sh._mode};{'flags' if sh._flags is not None else 'nccl'};{timed_out};{'native' if native and went_native else 'python'}")
     del sh, a, b, xf
     for f, g in keep:
         g.close()
@@ -142,7 +160,7 @@ def _worker(rank, world, port, mode, out_dir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["allgather", "a2a", "multicast", "publish"])
+@pytest.mark.parametrize("mode", ["allgather", "a2a", "multicast", "publish", "native"])
 def test_two_ranks_agree_with_one(mode, tmp_path):
     import torch.multiprocessing as mp
 
@@ -156,3 +174,5 @@ def test_two_ranks_agree_with_one(mode, tmp_path):
     assert used[0][0] == used[1][0], used
     if mode == "publish" and used[0][0] == "publish" and used[0][1] == "flags":
         assert "rank 1" in used[0][2], used  # rank 0 waited for rank 1 in vain, and said so
+    if mode == "native" and used[0][3] == "native":
+        assert used[1][3] == "native" and "status 7" in used[0][2] and "rank 1" in used[0][2], used
