@@ -29,8 +29,8 @@ class ShardedSpmv:
     local rows [lo, hi) (relative to bounds[rank]); the ranges must tile the rank's block. They are
     computed and exchanged in list order, and only the last exchange is not hidden behind a kernel,
     so the chunk with the fewest rows belongs last. The ranks may cut their blocks into different
-    numbers of chunks, except with the pairwise exchanges ("a2a", "allgather", the gloo loop), which
-    pair the c-th chunks of all ranks.
+    numbers of chunks; the pairwise exchanges ("a2a", "allgather", the gloo loop) pair the c-th chunks
+    of all ranks and then exchange each block as one piece instead.
 
     exchange="publish": a chunk may carry a 4th entry `pub(x_ptr, y_ptr, y_multicast_ptr)` that computes
     AND publishes its rows from one kernel (PlanGroup.spmv_publish); then nothing is exchanged
@@ -99,7 +99,7 @@ class ShardedSpmv:
             if int(t.item()) != code:
                 self._mode = {3: "publish", 2: "multicast"}.get(int(t.item()), exchange if exchange in ("allgather", "a2a") else "allgather")
         if self._mode in ("allgather", "a2a", "bcast_loop") and not self._equal_chunks:
-            raise ValueError("the pairwise exchanges need the same number of chunks on every rank")
+            self._whole_blocks()
         self._epoch = 0
         self._flags = self._flags_mc = self._status = None
         self._dtype = dtype
@@ -126,11 +126,16 @@ class ShardedSpmv:
             pass
         return symm, gname, symm.empty(self.n, dtype=self._dtype, device=self.device)
 
+    def _whole_blocks(self) -> None:
+        """The pairwise exchanges pair the c-th chunks of all ranks: when the ranks cut their blocks into different
+        numbers of chunks, every rank's block is exchanged as ONE piece after its last chunk (no overlap then)."""
+        self._whole_block_exchange = True
+        self.span = [[(self.bounds[p], self.bounds[p + 1])] for p in range(self.world)]
+
     def _fall_back(self, why: str) -> None:
         # (called on every rank with the collectively agreed outcome, so all ranks take the same path)
         if not self._equal_chunks:
-            raise RuntimeError("no NVLink multicast (" + why[:120] + ") and the ranks cut their blocks into different numbers of chunks: "
-                               "the pairwise exchanges cannot pair them")
+            self._whole_blocks()
         self._mode = self._fallback_mode
         self.fallback_reason = why[:200]
 
@@ -291,6 +296,12 @@ class ShardedSpmv:
             self._barrier()
             return
         cur = torch.cuda.current_stream(self.device) if self._comm is not None else None
+        if getattr(self, "_whole_block_exchange", False):
+            for fn, lo, hi in self.chunks:
+                if hi > lo:
+                    fn(x, x_next[base + lo : base + hi])
+            self._exchange(0, x_next)
+            return
         for c, (fn, lo, hi) in enumerate(self.chunks):
             if hi > lo:
                 fn(x, x_next[base + lo : base + hi])

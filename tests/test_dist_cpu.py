@@ -164,6 +164,34 @@ def _symm_failure_worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
+def _unequal_chunks_worker(rank, world, port, out_dir):
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    bounds = [0, 5, 12]
+    base = bounds[rank]
+
+    def piece(lo, hi):
+        return (lambda xt, yt: yt.copy_(xt[base + lo : base + hi] * 3.0), lo, hi)
+
+    # rank 0 computes its block in one piece, rank 1 in three: a pairwise exchange cannot pair them
+    chunks = [piece(0, 5)] if rank == 0 else [piece(2, 7), piece(0, 2), piece(7, 7)]
+    sh = ShardedSpmv(None, bounds, rank, world, torch.float32, "cpu", chunks=chunks)
+    xt = torch.arange(12, dtype=torch.float32)
+    out = sh.iterate(xt.clone(), 2, sh.new_vector(), sh.new_vector())
+    with open(os.path.join(out_dir, f"whole_{rank}.txt"), "w") as fh:
+        fh.write(f"{out.tolist() == (xt * 9).tolist()};{getattr(sh, '_whole_block_exchange', False)}")
+    dist.destroy_process_group()
+
+
+def test_ranks_with_different_chunk_counts_exchange_whole_blocks(tmp_path):
+    world = 2
+    mp.spawn(_unequal_chunks_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert [open(tmp_path / f"whole_{r}.txt").read() for r in range(world)] == ["True;True"] * 2
+
+
 def test_a_local_allocation_failure_makes_every_rank_fall_back_together(tmp_path):
     world = 2
     mp.spawn(_symm_failure_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
