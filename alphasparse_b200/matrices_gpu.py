@@ -38,22 +38,44 @@ def _hash01(key: torch.Tensor, salt: int) -> torch.Tensor:
     return (m + 1.0) / float(1 << 24)
 
 
-def rmat_row_degrees(scale: int, edge_factor: int, seed: int, device, chunk_ids=None) -> torch.Tensor:
-    """Edges per row before duplicate removal over the given chunks (all chunks when None)."""
+def rmat_degrees(scale: int, edge_factor: int, seed: int, device, chunk_ids=None, columns: bool = True):
+    """(edges per row, edges per column) before duplicate removal over the given chunks (all chunks when None)."""
     n = 1 << scale
     total = n * edge_factor
     n_chunks = (total + CHUNK - 1) // CHUNK
     deg = torch.zeros(n, dtype=torch.int64, device=device)
+    cdeg = torch.zeros(n, dtype=torch.int64, device=device) if columns else None
     for cid in (range(n_chunks) if chunk_ids is None else chunk_ids):
         m = min(CHUNK, total - cid * CHUNK)
-        r, _ = _chunk_edges(scale, m, seed, cid, device)
+        r, c = _chunk_edges(scale, m, seed, cid, device)
         deg += torch.bincount(r, minlength=n)
-    return deg
+        if columns:
+            cdeg += torch.bincount(c, minlength=n)
+    return deg, cdeg
 
 
-def rmat_block(scale: int, edge_factor: int, seed: int, r0: int, r1: int, device):
+def rmat_row_degrees(scale: int, edge_factor: int, seed: int, device, chunk_ids=None) -> torch.Tensor:
+    """Edges per row before duplicate removal over the given chunks (all chunks when None)."""
+    return rmat_degrees(scale, edge_factor, seed, device, chunk_ids, columns=False)[0]
+
+
+def hotness_labels(col_degrees: torch.Tensor):
+    """Relabelling of the vertices of a square matrix by how often their column is read: the vertex with the
+    most column entries gets label 0. Returns (labels, inverse): labels[v] = new label of vertex v,
+    inverse[k] = vertex that carries label k (ties keep the original order, so the result depends on the
+    counts only). In the relabelled matrix P A P^T the entries of x that most gathers read are contiguous:
+    whole cache lines of x are hot, and the part of x that an L2 smaller than x keeps is the part that is read."""
+    inverse = torch.argsort(col_degrees, descending=True, stable=True)
+    labels = torch.empty_like(inverse)
+    labels[inverse] = torch.arange(inverse.shape[0], dtype=inverse.dtype, device=inverse.device)
+    return labels, inverse
+
+
+def rmat_block(scale: int, edge_factor: int, seed: int, r0: int, r1: int, device, labels=None, inverse=None):
     """CSR of rows [r0, r1) of the R-MAT matrix with GLOBAL column indices, as torch tensors on
-    `device`: (indptr int64 [r1-r0+1], indices int32-valued int64, values float32)."""
+    `device`: (indptr int64 [r1-r0+1], indices int32-valued int64, values float32). With `labels` /
+    `inverse` (hotness_labels) rows and columns are those of the relabelled matrix P A P^T: the same
+    edges and the same values (hashed from the ORIGINAL row and column), under new vertex numbers."""
     n = 1 << scale
     total = n * edge_factor
     n_chunks = (total + CHUNK - 1) // CHUNK
@@ -61,6 +83,8 @@ def rmat_block(scale: int, edge_factor: int, seed: int, r0: int, r1: int, device
     for cid in range(n_chunks):
         m = min(CHUNK, total - cid * CHUNK)
         r, c = _chunk_edges(scale, m, seed, cid, device)
+        if labels is not None:
+            r, c = labels[r], labels[c]
         if r0 > 0 or r1 < n:
             keep = (r >= r0) & (r < r1)
             r, c = r[keep], c[keep]
@@ -73,7 +97,7 @@ def rmat_block(scale: int, edge_factor: int, seed: int, r0: int, r1: int, device
     counts = torch.bincount(rows - r0, minlength=r1 - r0)
     indptr = torch.zeros(r1 - r0 + 1, dtype=torch.int64, device=device)
     torch.cumsum(counts, 0, out=indptr[1:])
-    vals = _hash01(key, seed * 7919 + 13)
+    vals = _hash01(key if inverse is None else inverse[rows] * n + inverse[cols], seed * 7919 + 13)
     return indptr, cols, vals
 
 

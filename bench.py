@@ -375,7 +375,7 @@ def run_c5(args, rank, world, local_rank, dist):
                        "rows": n, "nnz": nnz, "rows_rank0": r["rows_local"], "nnz_rank0": r["nnz_local"], "graph": r["graph"],
                        "l2": "inputs larger than L2", "build_s": round(r["search_s"], 1), "generate_s": round(r["gen_s"], 1),
                        "ms_per_spmv": r["ms_per_spmv"], "ms_per_step_median": r["ms_per_step_median"], "ms_compute_per_spmv_max_over_ranks": r["ms_compute_per_spmv_max"],
-                       "row_chunks_per_rank": r["chunks"], "balance": args.balance, "staged_row_sums": r["staged"],
+                       "row_chunks_per_rank": r["chunks"], "balance": args.balance, "relabel": r["relabel"], "staged_row_sums": r["staged"],
                        "exchange": "none (1 GPU)" if world == 1 else {"publish": "rows leave the SpMV kernel through the NVLink multicast address (multimem.st), end rows of the warps by a small kernel after it",
                                                                        "multicast": "multicast store pass per row chunk on a second stream, overlapped with the next chunk's kernel"}.get(r["exchange_used"], r["exchange_used"]),
                        "barrier": r["barrier"], "loop": r["loop"], "exchange_fallback": r["fallback_reason"],
@@ -387,7 +387,7 @@ def run_c5(args, rank, world, local_rank, dist):
             "clocks": clocks, "parity_max_rel_err": r["parity"],
         }
     # end to end (all ranks take part): x0 from pinned host memory in, final x out, every step
-    sh, (xa, xb) = r["sharded"], r["bufs"]
+    sh, iterate = r["sharded"], r["iterate"]
     hx = r["x0"].cpu().pin_memory()
     hy = torch.empty_like(hx).pin_memory()
     dev_x = torch.empty_like(r["x0"])
@@ -400,7 +400,7 @@ def run_c5(args, rank, world, local_rank, dist):
     with torch.cuda.stream(stream):
         for _ in range(Ke):
             dev_x.copy_(hx, non_blocking=True)
-            xf = sh.iterate(dev_x, iters, xa, xb)
+            xf = iterate(dev_x, iters)
             hy.copy_(xf, non_blocking=True)
             stream.synchronize()
     e2e_s = (time.perf_counter() - t0) / Ke
@@ -426,15 +426,15 @@ def run_c5(args, rank, world, local_rank, dist):
         if world == 1 and not args.no_cpu_baseline:
             gf, threads, passes, med = cpu_baseline(r["m_local"], hx.numpy(), budget_s=10.0, reps_min=2, reps_max=5)
             line["cpu_baseline"] = {"value": gf, "unit": "GFLOP/s", "cores": threads, "kind": "port",
-                                    "sample": f"{passes} SpMV passes over the whole matrix ({nnz} nnz, median {med * 1e3:.0f} ms each) out of the {iters} of a step; OpenMP row-parallel CSR loop"}
+                                    "sample": f"{passes} SpMV passes over the whole matrix as the GPU loop holds it ({r['relabel']}; {nnz} nnz, median {med * 1e3:.0f} ms each) out of the {iters} of a step; OpenMP row-parallel CSR loop"}
     # Tear down in dependency order: torch frees pinned blocks by recording an event on the stream
     # they were last used on, and that stream belongs to the context object.
     torch.cuda.synchronize()
     ctx = r["ctx"]
-    del hx, hy, dev_x, xf, stream, xa, xb, sh
+    del hx, hy, dev_x, xf, stream, sh, iterate
     for g in r["group"]:
         g.close()
-    for k in ("sharded", "x0", "group", "fmt", "m_local", "bufs"):
+    for k in ("sharded", "x0", "group", "fmt", "m_local", "bufs", "iterate", "labels"):
         r.pop(k, None)
     import gc
 
@@ -679,11 +679,13 @@ def main():
     ap.add_argument("--exchange", default="multicast", choices=["multicast", "publish", "allgather", "a2a"],
                     help="c5: how a rank's slice of the next x reaches the others: from inside the SpMV kernel (publish), by a multicast store pass per "
                          "chunk, or by NCCL (both multicast modes fall back to allgather where symmetric memory has no multicast address)")
+    ap.add_argument("--relabel", default="indegree", choices=["indegree", "none"], help="c5: renumber the vertices by column count, hottest first, and run the loop on "
+                    "P A P^T (x permuted on the way in, the result on the way out, inside every step): the hot part of x becomes contiguous")
     ap.add_argument("--loop", default="native", choices=["native", "python"], help="c5: who enqueues the repeated SpMVs: the native loop behind the C ABI "
                     "(asp_dist_spmv_iter; multicast exchange and single GPU) or the Python one (every exchange form)")
-    ap.add_argument("--balance", default="6", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
-                    "or a number w (a row with non-zeros weighs w non-zeros; measured at 4 GPUs: 6 evens out the ranks' kernel times to 3 %%, "
-                    "nnz leaves the rank with the sparse tail 10 %% behind)")
+    ap.add_argument("--balance", default="5", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
+                    "or a number w (a row with non-zeros weighs w non-zeros; on the relabelled matrix 4 to 6 keep the kernel times of the 4 or 8 "
+                    "row blocks within 5-10 %% of one another, nnz leaves the block with the sparse tail far behind)")
     ap.add_argument("--tlb", type=int, default=0, help="c5: non-zeros per thread of the CSR5-like format (default 32)")
     ap.add_argument("--sort", default="auto", choices=["auto", "yes", "no"], help="c5: put the rows without non-zeros last (a one-bin coarse sort) so that the format drops them (auto = yes); "
                     "no = every row is stored, unpermuted, which lets the publishing kernels send 16-byte multicast stores (measured slower)")

@@ -176,3 +176,42 @@ def test_two_ranks_agree_with_one(mode, tmp_path):
         assert "rank 1" in used[0][2], used  # rank 0 waited for rank 1 in vain, and said so
     if mode == "native" and used[0][3] == "native":
         assert used[1][3] == "native" and "status 7" in used[0][2] and "rank 1" in used[0][2], used
+
+
+def _bench_args(**kw):
+    import argparse
+
+    d = dict(scale=13, iters=3, balance="6", chunks=0, exchange="multicast", graph=None, full_search=False, search=False, sort="auto", tlb=0, stage=False,
+             cap_log2=0, generic_csr5=False, warmup=3, steps=1, loop="native", relabel="indegree", profile_launches=0)
+    d.update(kw)
+    return argparse.Namespace(**d)
+
+
+def _close(r):
+    torch.cuda.synchronize()
+    for g in r["group"]:
+        g.close()
+    for f in r["fmt"]:
+        f.close()
+
+
+def test_graph_workload_with_and_without_relabelling_gives_the_same_vector():
+    """The whole workload function on one GPU at a small scale: the loop on P A P^T (vertices renumbered by column
+    count, x permuted in and out) returns what the loop on A returns, and both first SpMVs match the oracle."""
+    check = lambda m, x, y: refdump.rel_err(y, *refdump.csr_ref(m, x))
+    finals = {}
+    for relabel in ("indegree", "none"):
+        r = bench_rmat.run(_bench_args(relabel=relabel), 0, 1, 0, None, None, check_fn=check)
+        assert r["parity"] <= refdump.TOL[np.dtype(np.float32)], (relabel, r["parity"])
+        assert r["loop"].startswith("native")
+        stream = torch.cuda.ExternalStream(r["ctx"].stream)
+        with torch.cuda.stream(stream):
+            finals[relabel] = r["iterate"](r["x0"], 3).clone()
+        torch.cuda.synchronize()
+        if relabel == "none":
+            m, x = r["m_local"], r["x0"].cpu().numpy()
+            ref = _reference_iterations(m, x, 3)
+        _close(r)
+    a, b = finals["indegree"].cpu().numpy().astype(np.float64), finals["none"].cpu().numpy().astype(np.float64)
+    assert np.max(np.abs(a - ref)) <= 1e-4 * np.max(np.abs(ref))
+    assert np.max(np.abs(b - ref)) <= 1e-4 * np.max(np.abs(ref))

@@ -1,0 +1,47 @@
+"""CPU suite: renumbering the vertices of the graph workload by column count gives P A P^T, the same edges and
+values under new numbers (the generator runs on the CPU here; its streams differ from the GPU's, the logic does not)."""
+import numpy as np
+import scipy.sparse as sp
+import torch
+
+from alphasparse_b200 import matrices_gpu
+
+
+def _csr(ip, cols, vals, n):
+    return sp.csr_matrix((vals.numpy(), cols.numpy(), ip.numpy()), shape=(ip.shape[0] - 1, n))
+
+
+def test_hotness_labels_sort_by_count_and_keep_ties_in_order():
+    cnt = torch.tensor([3, 9, 3, 0, 9, 1])
+    labels, inverse = matrices_gpu.hotness_labels(cnt)
+    assert inverse.tolist() == [1, 4, 0, 2, 5, 3]
+    assert labels.tolist() == [2, 0, 3, 5, 1, 4]
+    assert torch.equal(labels[inverse], torch.arange(6))
+
+
+def test_relabelled_blocks_are_the_permuted_matrix():
+    scale, ef, seed = 9, 8, 4
+    n = 1 << scale
+    dev = torch.device("cpu")
+    deg, cdeg = matrices_gpu.rmat_degrees(scale, ef, seed, dev)
+    assert int(deg.sum()) == int(cdeg.sum()) == n * ef
+    assert torch.equal(deg, matrices_gpu.rmat_row_degrees(scale, ef, seed, dev))
+    labels, inverse = matrices_gpu.hotness_labels(cdeg)
+    a = _csr(*matrices_gpu.rmat_block(scale, ef, seed, 0, n, dev), n)
+    # the relabelled matrix, generated in two row blocks
+    cut = 100
+    parts = [_csr(*matrices_gpu.rmat_block(scale, ef, seed, r0, r1, dev, labels, inverse), n) for r0, r1 in ((0, cut), (cut, n))]
+    b = sp.vstack(parts).tocsr()
+    assert b.nnz == a.nnz
+    # b[labels[i], labels[j]] == a[i, j]
+    lab = labels.numpy()
+    back = b[lab][:, lab]
+    assert (back != a).nnz == 0
+    # the hottest column of the original matrix is column 0 of the relabelled one, and column counts never increase
+    col_counts = np.asarray((b != 0).sum(axis=0)).ravel()
+    assert col_counts[0] == col_counts.max()
+    # x permuted the same way gives the permuted product
+    x = matrices_gpu.rmat_x(scale, seed, dev).numpy().astype(np.float64)
+    y = a.astype(np.float64) @ x
+    yp = b.astype(np.float64) @ x[inverse.numpy()]
+    assert np.allclose(yp[lab], y, rtol=1e-12, atol=0)
