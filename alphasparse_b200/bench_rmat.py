@@ -53,7 +53,9 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
         # it depends on the column counts only). The loop runs on P A P^T: x0 is permuted once on the way in, the
         # result once on the way out. With the hot entries of x contiguous, an L2 smaller than x (268 MB at scale
         # 26) keeps exactly the lines the gathers read; measured on row blocks of scale 26: 10-12 % less kernel time.
-        labels, inverse = matrices_gpu.hotness_labels(cdeg)
+        # Vertices whose row is empty come last: that suffix of every vector stays zero (the vectors are created
+        # zero-filled and nobody writes it), so it is neither computed nor exchanged.
+        labels, inverse = matrices_gpu.hotness_labels(cdeg, deg)
         deg = deg[inverse]  # degrees of the relabelled rows
     del cdeg
     # "nnz": equal non-zeros per rank; "bytes": equal algorithmic bytes, i.e. a row weighs as much
@@ -66,6 +68,8 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
     # without non-zeros cost nothing: the format drops them)
     w8 = int(round(row_weight * 8))
     bounds = balanced_bounds_from_degrees((deg * 8 + (deg > 0) * w8).cpu().numpy(), world)
+    n_active = int((deg > 0).sum().item()) if relabel else n  # relabelled: rows [n_active, n) have no non-zeros
+    bounds[-1] = n_active
     del deg
     r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
     # pass 2: this rank's row block (global columns), duplicates merged
@@ -87,7 +91,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
         # The store pass of a chunk costs in proportion to its rows, and only a rank's LAST pass is exposed: a rank
         # cuts its block into one chunk per 1/(2 world) of all rows it owns (nnz-balanced blocks of a skewed matrix
         # differ a hundred-fold in rows, so the hub ranks get one chunk and the rank with the sparse tail up to 8).
-        n_chunks = int(min(8, max(1, -(-(r1 - r0) * 2 * world // n))))
+        n_chunks = int(min(8, max(1, -(-(r1 - r0) * 2 * world // n_active))))
     else:
         n_chunks = 2  # the pairwise exchanges pair the c-th chunks of all ranks
     ctx = capi.Context(local_rank)
@@ -156,7 +160,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
     x_out = torch.empty_like(x0) if relabel else None
 
     with torch.cuda.stream(stream):
-        sh = ShardedSpmv(None, bounds, rank, world, torch.float32, dev, chunks=chunks, exchange=args.exchange)
+        sh = ShardedSpmv(None, bounds, rank, world, torch.float32, dev, chunks=chunks, exchange=args.exchange, n_total=n)
         xa = sh.new_vector()
         xb = sh.new_vector()
         native = getattr(args, "loop", "native") == "native" and build_error is None and sh.use_native_loop(ctx, chunk_groups)
@@ -182,6 +186,11 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
             torch.cuda.synchronize()
             return {"profile_only": True, "nnz": nnz_local, "rows": n, "graph": desc, "format_bytes": int(sum(g.format_bytes() for g in groups))}
         W, K = max(args.warmup, 3), max(args.steps, 1)
+        # the ranks enter the loop together: the barrier kernels wait for a late rank only for about a second, and the
+        # parity check above takes a different time on every rank
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
         for _ in range(W):
             iterate(x0, 2)
         torch.cuda.synchronize()

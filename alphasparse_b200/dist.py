@@ -39,11 +39,14 @@ class ShardedSpmv:
     writes (rows without non-zeros that a format dropped) stay zero in every replica.
     """
 
-    def __init__(self, local_spmv, bounds, rank: int, world: int, dtype, device, group=None, chunks=None, exchange: str = "allgather"):
+    def __init__(self, local_spmv, bounds, rank: int, world: int, dtype, device, group=None, chunks=None, exchange: str = "allgather",
+                 n_total: int | None = None):
         self.bounds = [int(b) for b in bounds]
         self.rank, self.world, self.group = rank, world, group
         self.rows = [self.bounds[p + 1] - self.bounds[p] for p in range(world)]
-        self.n = self.bounds[-1]
+        # length of the vectors; rows [bounds[-1], n_total) belong to nobody: no non-zeros, zero in every vector
+        self.n = int(n_total) if n_total is not None else self.bounds[-1]
+        assert self.n >= self.bounds[-1]
         self.device = torch.device(device)
         my_rows = self.rows[rank]
         self.chunks = [tuple(c) for c in chunks] if chunks is not None else [(local_spmv, 0, my_rows)]

@@ -59,13 +59,18 @@ def rmat_row_degrees(scale: int, edge_factor: int, seed: int, device, chunk_ids=
     return rmat_degrees(scale, edge_factor, seed, device, chunk_ids, columns=False)[0]
 
 
-def hotness_labels(col_degrees: torch.Tensor):
+def hotness_labels(col_degrees: torch.Tensor, row_degrees: torch.Tensor | None = None):
     """Relabelling of the vertices of a square matrix by how often their column is read: the vertex with the
     most column entries gets label 0. Returns (labels, inverse): labels[v] = new label of vertex v,
     inverse[k] = vertex that carries label k (ties keep the original order, so the result depends on the
     counts only). In the relabelled matrix P A P^T the entries of x that most gathers read are contiguous:
-    whole cache lines of x are hot, and the part of x that an L2 smaller than x keeps is the part that is read."""
+    whole cache lines of x are hot, and the part of x that an L2 smaller than x keeps is the part that is read.
+    With `row_degrees`, vertices whose row has no entries come last (in the same order among themselves): their
+    rows of A x are zero for every x, so a loop x <- A x neither computes nor exchanges that suffix."""
     inverse = torch.argsort(col_degrees, descending=True, stable=True)
+    if row_degrees is not None:
+        has_row = row_degrees[inverse] > 0
+        inverse = torch.cat([inverse[has_row], inverse[~has_row]])
     labels = torch.empty_like(inverse)
     labels[inverse] = torch.arange(inverse.shape[0], dtype=inverse.dtype, device=inverse.device)
     return labels, inverse

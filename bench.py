@@ -683,7 +683,7 @@ def main():
                     "P A P^T (x permuted on the way in, the result on the way out, inside every step): the hot part of x becomes contiguous")
     ap.add_argument("--loop", default="native", choices=["native", "python"], help="c5: who enqueues the repeated SpMVs: the native loop behind the C ABI "
                     "(asp_dist_spmv_iter; multicast exchange and single GPU) or the Python one (every exchange form)")
-    ap.add_argument("--balance", default="5", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
+    ap.add_argument("--balance", default="4", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
                     "or a number w (a row with non-zeros weighs w non-zeros; on the relabelled matrix 4 to 6 keep the kernel times of the 4 or 8 "
                     "row blocks within 5-10 %% of one another, nnz leaves the block with the sparse tail far behind)")
     ap.add_argument("--tlb", type=int, default=0, help="c5: non-zeros per thread of the CSR5-like format (default 32)")
