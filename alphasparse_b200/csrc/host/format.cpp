@@ -63,6 +63,58 @@ std::unique_ptr<Matrix> matrix_from_csr(u64 n_rows, u64 n_cols, const int64_t *i
     return m;
 }
 
+// Vertices of a square matrix renumbered by how often their column occurs, most frequent first (ties keep their
+// order), optionally with the vertices whose row is empty last; returns P A P^T (columns sorted inside every row).
+// Not an operator of the reference: for x <- A x loops on graphs, where the numbering is free and a numbering that
+// makes the often-read entries of x contiguous is worth 10-15 % of the SpMV time once x no longer fits the L2.
+std::unique_ptr<Matrix> relabel_by_column_count(const Matrix &m, bool empty_rows_last, std::vector<u32> &labels, u64 &n_active)
+{
+    const u64 n = m.n_rows;
+    std::vector<u64> cnt(n, 0);
+#pragma omp parallel for schedule(static)
+    for (long long k = 0; k < (long long)m.nnz; k++)
+    {
+#pragma omp atomic
+        cnt[m.col[k]]++;
+    }
+    std::vector<u32> order(n);
+    for (u64 i = 0; i < n; i++) order[i] = (u32)i;
+    std::stable_sort(order.begin(), order.end(), [&](u32 a, u32 b) { return cnt[a] > cnt[b]; });
+    n_active = 0;
+    for (u64 r = 0; r < n; r++) n_active += m.rowptr[r + 1] > m.rowptr[r] ? 1 : 0;
+    if (empty_rows_last) std::stable_partition(order.begin(), order.end(), [&](u32 v) { return m.rowptr[v + 1] > m.rowptr[v]; });
+    labels.assign(n, 0);
+    for (u64 k = 0; k < n; k++) labels[order[k]] = (u32)k;
+    std::unique_ptr<Matrix> out(new Matrix());
+    out->n_rows = out->n_cols = n;
+    out->nnz = m.nnz;
+    out->val_dt = m.val_dt;
+    out->rowptr.assign(n + 1, 0);
+    for (u64 k = 0; k < n; k++) out->rowptr[k + 1] = out->rowptr[k] + (m.rowptr[order[k] + 1] - m.rowptr[order[k]]);
+    out->col.resize(m.nnz);
+    out->val.es = m.val.es;
+    out->val.b.resize(m.nnz * m.val.es);
+    const size_t es = (size_t)m.val.es;
+#pragma omp parallel
+    {
+        std::vector<std::pair<u32, u64>> row; // (new column, position in the old row)
+#pragma omp for schedule(dynamic, 256)
+        for (long long k = 0; k < (long long)n; k++)
+        {
+            const u64 b = m.rowptr[order[k]], e = m.rowptr[order[k] + 1], o = out->rowptr[k];
+            row.clear();
+            for (u64 j = b; j < e; j++) row.push_back({labels[m.col[j]], j});
+            std::sort(row.begin(), row.end());
+            for (u64 j = 0; j < row.size(); j++)
+            {
+                out->col[o + j] = row[j].first;
+                memcpy(&out->val.b[(o + j) * es], &m.val.b[row[j].second * es], es);
+            }
+        }
+    }
+    return out;
+}
+
 // The `.mtx.coo` grammar of the reference (struct.cc:92-174): the first line that does not start with white space
 // is "rows cols ..."; every other such line is "row col value", 1-based, rows non-decreasing. The reference reads it
 // with getline + split + atol / stof, one line at a time; here the file is read in one piece, cut at line ends into

@@ -154,6 +154,7 @@ struct Matrix
 // ---- BEGIN_* nodes ---------------------------------------------------------------------------
 // BEGIN_MEMORY_CACHE_INPUT_FILE: from CSR arrays (row offsets int64, column indices u32, values)
 std::unique_ptr<Matrix> matrix_from_csr(u64 n_rows, u64 n_cols, const int64_t *indptr, const u32 *indices, const void *values, int val_dt);
+std::unique_ptr<Matrix> relabel_by_column_count(const Matrix &m, bool empty_rows_last, std::vector<u32> &labels, u64 &n_active);
 // BEGIN_INPUT_FILE: parse the `.mtx.coo` text grammar (struct.cc:92-174)
 std::unique_ptr<Matrix> matrix_from_coo_file(const std::string &path, int val_dt, std::string &err);
 

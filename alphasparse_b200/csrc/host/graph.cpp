@@ -301,6 +301,32 @@ asp_status asp_matrix_from_coo_file(const char *path, int val_dtype, asp_matrix 
     return ASP_OK;
 }
 
+asp_status asp_matrix_relabel_by_column_count(const asp_matrix *m, int empty_rows_last, asp_matrix **out, uint32_t *labels, uint64_t *n_active)
+{
+    if (!m || !out) return hfail(ASP_ERR_INVALID_ARG, "NULL argument");
+    *out = nullptr;
+    const Matrix &src = *m->m;
+    if (src.n_rows != src.n_cols) return hfail(ASP_ERR_INVALID_ARG, "renumbering vertices needs a square matrix");
+    if (src.is_sorted || src.is_blocked || src.is_compressed) return hfail(ASP_ERR_INVALID_ARG, "renumber the matrix before any dense-view node runs");
+    asp_matrix *h = new (std::nothrow) asp_matrix();
+    if (!h) return hfail(ASP_ERR_ALLOC, "host allocation failed");
+    try
+    {
+        std::vector<u32> lab;
+        u64 active = 0;
+        h->m = relabel_by_column_count(src, empty_rows_last != 0, lab, active);
+        if (labels) memcpy(labels, lab.data(), lab.size() * sizeof(u32));
+        if (n_active) *n_active = active;
+    }
+    catch (const std::bad_alloc &)
+    {
+        delete h;
+        return hfail(ASP_ERR_ALLOC, "host allocation failed");
+    }
+    *out = h;
+    return ASP_OK;
+}
+
 asp_status asp_partition_rows_by_nnz(uint64_t n_rows, const int64_t *indptr, int parts, uint64_t *bounds)
 {
     if (!indptr || !bounds || parts <= 0 || n_rows == 0) return hfail(ASP_ERR_INVALID_ARG, "NULL argument or parts <= 0");

@@ -22,7 +22,7 @@ HOST_EXPORTS = [
     "asp_matrix_from_csr", "asp_matrix_from_coo_file", "asp_matrix_destroy", "asp_matrix_rows", "asp_matrix_cols",
     "asp_matrix_nnz", "asp_graph_execute", "asp_format_destroy", "asp_format_num_subs", "asp_format_global_perm",
     "asp_format_sub_info", "asp_format_plan_descs", "asp_format_padding_rate", "asp_host_last_error",
-    "asp_dense_execute", "asp_matrix_num_subs", "asp_matrix_sub_rows", "asp_partition_rows_by_nnz", "asp_format_id", "asp_format_save", "asp_format_load",
+    "asp_dense_execute", "asp_matrix_num_subs", "asp_matrix_sub_rows", "asp_partition_rows_by_nnz", "asp_matrix_relabel_by_column_count", "asp_format_id", "asp_format_save", "asp_format_load",
     "asp_search", "asp_search_result_destroy", "asp_search_result_dense", "asp_search_result_num_subs", "asp_search_result_sub_spec",
     "asp_search_result_sub_name", "asp_search_result_sub_launch", "asp_search_result_ms", "asp_search_result_num_trials",
     "asp_search_result_trial", "asp_search_candidates", "asp_search_derive_tblock",
@@ -65,6 +65,8 @@ def _lib():
         L.asp_matrix_sub_rows.restype = C.c_int
         L.asp_partition_rows_by_nnz.argtypes = [C.c_uint64, C.c_void_p, C.c_int, C.c_void_p]
         L.asp_partition_rows_by_nnz.restype = C.c_int
+        L.asp_matrix_relabel_by_column_count.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.c_void_p, C.POINTER(C.c_uint64)]
+        L.asp_matrix_relabel_by_column_count.restype = C.c_int
         L.asp_format_destroy.argtypes = [C.c_void_p]
         L.asp_format_destroy.restype = None
         L.asp_format_num_subs.argtypes = [C.c_void_p]
@@ -152,6 +154,15 @@ class Matrix:
         h = C.c_void_p()
         _check(_lib().asp_matrix_from_coo_file(path.encode(), capi.DTYPE_OF_NP[np.dtype(dtype)], C.byref(h)))
         return Matrix(h)
+
+    def relabel_by_column_count(self, empty_rows_last: bool = True):
+        """(P A P^T as a new Matrix, labels, rows with non-zeros): vertices renumbered by column count, most frequent
+        first; labels[v] = new number of vertex v (asp_matrix_relabel_by_column_count)."""
+        n = self.shape[0]
+        labels = np.zeros(n, dtype=np.uint32)
+        h, active = C.c_void_p(), C.c_uint64()
+        _check(_lib().asp_matrix_relabel_by_column_count(self._h, 1 if empty_rows_last else 0, C.byref(h), labels.ctypes.data, C.byref(active)))
+        return Matrix(h), labels, int(active.value)
 
     @property
     def shape(self):

@@ -1,10 +1,15 @@
 """CPU suite: renumbering the vertices of the graph workload by column count gives P A P^T, the same edges and
 values under new numbers (the generator runs on the CPU here; its streams differ from the GPU's, the logic does not)."""
 import numpy as np
+import pytest
 import scipy.sparse as sp
 import torch
 
-from alphasparse_b200 import matrices_gpu
+import plan_interp
+import refdump
+from alphasparse_b200 import matrices as M, matrices_gpu
+from alphasparse_b200.graph import Matrix
+from native_manifest import NativeManifest
 
 
 def _csr(ip, cols, vals, n):
@@ -51,3 +56,36 @@ def test_relabelled_blocks_are_the_permuted_matrix():
     y = a.astype(np.float64) @ x
     yp = b.astype(np.float64) @ x[inverse.numpy()]
     assert np.allclose(yp[lab], y, rtol=1e-12, atol=0)
+
+
+@pytest.mark.parametrize("empty_last", [True, False])
+def test_host_operator_renumbers_a_matrix_and_the_lowered_format_gives_the_permuted_product(empty_last):
+    """asp_matrix_relabel_by_column_count on a host matrix: the result, lowered by the ordinary operators and walked
+    the way the kernels walk it, is P A P^T: y'[labels[v]] = (A x)[v] for x'[labels[v]] = x[v]."""
+    m, x = M.rmat(10, 8, seed=4)
+    hm = Matrix.from_csr(m)
+    m2, labels, n_active = hm.relabel_by_column_count(empty_last)
+    lens = m.row_lengths()
+    assert n_active == int((lens > 0).sum()) and m2.nnz == m.nnz and m2.shape == (m.n_rows, m.n_cols)
+    assert sorted(labels.tolist()) == list(range(m.n_rows))
+    counts = np.bincount(m.indices, minlength=m.n_cols)
+    inverse = np.argsort(labels)
+    if empty_last:
+        assert np.all(lens[inverse[:n_active]] > 0) and np.all(lens[inverse[n_active:]] == 0)
+        assert np.all(np.diff(counts[inverse[:n_active]]) <= 0) and np.all(np.diff(counts[inverse[n_active:]]) <= 0)
+    else:
+        assert np.all(np.diff(counts[inverse]) <= 0)  # most frequent column first
+    fmt = m2.execute("dense compress\nsub all tlb_nnz 8\nsub all template K9")
+    xp = np.zeros_like(x, dtype=np.float64)
+    xp[labels] = x
+    yp = plan_interp.interpret(NativeManifest(fmt, m.n_rows), xp)
+    y_ref, scale = refdump.csr_ref(m, x)
+    assert refdump.rel_err(yp[labels], y_ref, scale) <= 1e-12
+    fmt.close()
+    m2.close()
+    # a matrix that already went through a dense-view node is refused
+    cm = hm.dense("dense sort 1\ndense compress")
+    with pytest.raises(Exception):
+        cm.relabel_by_column_count()
+    cm.close()
+    hm.close()
