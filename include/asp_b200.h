@@ -274,7 +274,9 @@ asp_status asp_rank_barrier(const void *flags_local, void *flags_multicast, int 
  * the fewest rows last. One asp_rank_barrier per SpMV orders the ranks. The ranks may cut their blocks into
  * different numbers of chunks. Vectors and the flag array are symmetric memory that the caller allocated,
  * bound to multicast objects and zeroed (e.g. torch.distributed._symmetric_memory); the library sees plain
- * pointers only. One rank per GPU. */
+ * pointers only. One rank per GPU. The plans, the flag array and the context must outlive the asp_dist, which
+ * only refers to them. The ranks must enter a loop together (a host barrier after anything that takes a
+ * different time on every rank): the barrier kernel waits for a late rank only as long as max_polls allows. */
 typedef struct asp_dist asp_dist;
 typedef struct
 {
