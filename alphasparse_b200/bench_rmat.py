@@ -163,7 +163,7 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
         sh = ShardedSpmv(None, bounds, rank, world, torch.float32, dev, chunks=chunks, exchange=args.exchange, n_total=n)
         xa = sh.new_vector()
         xb = sh.new_vector()
-        native = getattr(args, "loop", "native") == "native" and build_error is None and sh.use_native_loop(ctx, chunk_groups)
+        native = getattr(args, "loop", "native") == "native" and build_error is None and sh.use_native_loop(ctx, chunk_groups, max_polls=20_000_000)  # (five times the default wait: a bench run shares its host with 7 other ranks)
 
         def iterate(x_caller, count):
             """x <- A x `count` times for a vector in the caller's numbering; returns the result in the same numbering."""
