@@ -186,6 +186,30 @@ def _unequal_chunks_worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
+def _suffix_worker(rank, world, port, out_dir):
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    bounds = [0, 5, 9]  # rows 9..11 belong to nobody: they have no non-zeros and stay zero in every vector
+    sh = ShardedSpmv(lambda xt, yt: yt.copy_(xt[bounds[rank] : bounds[rank + 1]] * 2.0 + xt[11]), bounds, rank, world, torch.float32, "cpu", n_total=12)
+    a, b = sh.new_vector(), sh.new_vector()
+    xt = torch.arange(12, dtype=torch.float32)
+    out = sh.iterate(xt, 2, a, b)
+    # first SpMV: y[i] = 2 x[i] + x[11] for i < 9, 0 beyond; second: the suffix of its input is zero
+    want = [(2.0 * (2.0 * i + 11.0)) for i in range(9)] + [0.0, 0.0, 0.0]
+    with open(os.path.join(out_dir, f"suffix_{rank}.txt"), "w") as fh:
+        fh.write(f"{out.tolist() == want};{a.shape[0]};{xt.tolist() == list(range(12))}")
+    dist.destroy_process_group()
+
+
+def test_rows_beyond_the_last_block_stay_zero(tmp_path):
+    world = 2
+    mp.spawn(_suffix_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert [open(tmp_path / f"suffix_{r}.txt").read() for r in range(world)] == ["True;12;True"] * 2
+
+
 def test_ranks_with_different_chunk_counts_exchange_whole_blocks(tmp_path):
     world = 2
     mp.spawn(_unequal_chunks_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
