@@ -380,7 +380,7 @@ def run_c5(args, rank, world, local_rank, dist):
                                                                        "multicast": "multicast store pass per row chunk on a second stream, overlapped with the next chunk's kernel"}.get(r["exchange_used"], r["exchange_used"]),
                        "barrier": r["barrier"], "loop": r["loop"], "exchange_fallback": r["fallback_reason"],
                        "values": "x grows by about 8x per SpMV and overflows fp32 after ~40 of the 100: the later SpMVs multiply inf / NaN (same memory traffic); parity is checked on the first SpMV"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world), "traffic": profiled_traffic("c5", r["graph"]) if world == 1 else None,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world), "traffic": profiled_traffic("c5", r["graph"]) if (world == 1 and args.scale == 26 and args.relabel == "indegree") else None,
                          "peak_kind": peak_kind, "algorithmic_bytes": b_alg, "launch": f"{iters} SpMV launches per step; peak = {world} x the measured copy bandwidth",
                          "note": "the gathers of x are bound by cache-line look-ups per SM (one per clock), not by DRAM: see profiles/"},
             "gpu_launches": int(K * iters * r["launches_per_spmv"]),
