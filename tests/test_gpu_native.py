@@ -148,3 +148,22 @@ def test_csr5_like_kernels_for_every_tlb_size_direct_and_staged(asp_ctx, mats, m
             refdump.assert_y(g.spmv_host(x), y_ref, scale, m.values.dtype, f"{mat} {templ} s={s} path={path} threads={threads}")
     g.close()
     fmt.close()
+
+
+def test_search_times_coinciding_launch_requests_once(asp_ctx):
+    """The launch sweep of the reference asks for CTA widths that the kernels fold into the same effective launch
+    (CSR5-like: 64..256 threads walk the same warps with more or fewer CTAs only up to the CTAs that have work).
+    The GPU timer measures every effective launch once and says how many requests it folded."""
+    m, x = M.uniform_random(4096, 16, seed=0)
+    lines = []
+    fmt, group, trials, desc = tuner.search(asp_ctx, m, quick=0, warmup=1, reps=3, log=lines.append)
+    tail = [l for l in lines if l.startswith("timer:")]
+    assert len(tail) == 1, lines[-3:]
+    measured, reused = [int(t) for t in tail[0].replace(",", "").split() if t.isdigit()]
+    assert measured > 0 and measured + reused >= len(trials), (tail, len(trials))
+    print(tail[0])
+    y = group.spmv_host(x)
+    y_ref, scale = refdump.csr_ref(m, x)
+    refdump.assert_y(y, y_ref, scale, m.values.dtype, f"search {desc}")
+    group.close()
+    fmt.close()
