@@ -59,7 +59,7 @@ EXPORTS = [
     "asp_ctx_create", "asp_multicast_store", "asp_spmv_publish", "asp_plan_end_rows", "asp_rank_barrier", "asp_ctx_destroy", "asp_ctx_stream", "asp_plan_group_create", "asp_plan_descs_validate", "asp_plan_destroy",
     "asp_plan_set_launch", "asp_plan_get_launch", "asp_plan_set_tuning", "asp_plan_format_bytes", "asp_plan_launches", "asp_spmv", "asp_spmv_host", "asp_time",
     "asp_synchronize", "asp_status_str", "asp_last_error", "asp_built_for_sm100a", "asp_spmv_host_static",
-    "asp_static_stage_bytes", "asp_search_gpu", "asp_dist_create", "asp_dist_destroy", "asp_dist_spmv", "asp_dist_spmv_iter", "asp_dist_status",
+    "asp_static_stage_bytes", "asp_search_gpu", "asp_spmv_host_pipelined", "asp_dist_create", "asp_dist_destroy", "asp_dist_spmv", "asp_dist_spmv_iter", "asp_dist_status",
 ]
 
 _lib = None
@@ -68,6 +68,11 @@ _lib = None
 class DistChunk(C.Structure):
     """asp_dist_chunk"""
     _fields_ = [("plans", C.POINTER(C.c_void_p)), ("n_plans", C.c_int), ("row_lo", C.c_uint64), ("row_hi", C.c_uint64)]
+
+
+class HostChunk(C.Structure):
+    """asp_host_chunk"""
+    _fields_ = [("plans", C.POINTER(C.c_void_p)), ("n_plans", C.c_int), ("row_lo", C.c_uint64), ("row_hi", C.c_uint64), ("col_hi", C.c_uint64)]
 
 
 class DistDesc(C.Structure):
@@ -139,6 +144,8 @@ def lib() -> C.CDLL:
     L.asp_last_error.restype = C.c_char_p
     L.asp_built_for_sm100a.argtypes = []
     L.asp_built_for_sm100a.restype = C.c_int
+    L.asp_spmv_host_pipelined.argtypes = [C.c_void_p, C.POINTER(HostChunk), C.c_int, C.c_void_p, C.c_void_p]
+    L.asp_spmv_host_pipelined.restype = C.c_int
     L.asp_dist_create.argtypes = [C.c_void_p, C.POINTER(DistDesc), C.POINTER(C.c_void_p)]
     L.asp_dist_create.restype = C.c_int
     L.asp_dist_destroy.argtypes = [C.c_void_p]
@@ -363,3 +370,14 @@ class DistLoop:
             self.close()
         except Exception:
             pass
+
+
+def spmv_host_pipelined(ctx: Context, chunks, h_x_ptr: int, h_y_ptr: int) -> None:
+    """asp_spmv_host_pipelined: `chunks` = [(PlanGroup, first row, end row, col_hi)] in ascending row order; h_x / h_y are host
+    pointers (pinned memory for real overlap)."""
+    arr = (HostChunk * len(chunks))()
+    for i, (g, lo, hi, col_hi) in enumerate(chunks):
+        arr[i].plans = C.cast(g._plans, C.POINTER(C.c_void_p))
+        arr[i].n_plans = g.n
+        arr[i].row_lo, arr[i].row_hi, arr[i].col_hi = int(lo), int(hi), int(col_hi)
+    check(lib().asp_spmv_host_pipelined(ctx.handle, arr, len(chunks), C.c_void_p(h_x_ptr), C.c_void_p(h_y_ptr)))

@@ -138,6 +138,9 @@ struct asp_ctx
     // scratch x / y used by asp_time and asp_spmv_host; grown on demand
     void *x = nullptr, *y = nullptr;
     size_t x_bytes = 0, y_bytes = 0;
+    // copy streams and events of the pipelined host SpMV, created on first use
+    cudaStream_t h2d = nullptr, d2h = nullptr;
+    std::vector<cudaEvent_t> pipe_events;
 };
 
 struct asp_plan
@@ -560,6 +563,11 @@ void asp_ctx_destroy(asp_ctx *c)
         if (c->ev_join[i]) cudaEventDestroy(c->ev_join[i]);
         if (c->aux[i]) cudaStreamDestroy(c->aux[i]);
     }
+    if (c->h2d) cudaStreamSynchronize(c->h2d);
+    if (c->d2h) cudaStreamSynchronize(c->d2h);
+    for (cudaEvent_t e : c->pipe_events) cudaEventDestroy(e);
+    if (c->h2d) cudaStreamDestroy(c->h2d);
+    if (c->d2h) cudaStreamDestroy(c->d2h);
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
@@ -1220,6 +1228,74 @@ asp_status asp_spmv_host(asp_ctx *ctx, asp_plan *const *plans, int n_plans, cons
     if (st != ASP_OK) return st;
     ASP_CUDA(cudaMemcpyAsync(h_y, ctx->y, yb, cudaMemcpyDeviceToHost, ctx->stream));
     ASP_CUDA(cudaStreamSynchronize(ctx->stream));
+    return ASP_OK;
+}
+
+asp_status asp_spmv_host_pipelined(asp_ctx *ctx, const asp_host_chunk *chunks, int n_chunks, const void *h_x, void *h_y)
+{
+    if (!ctx || !chunks || n_chunks <= 0 || !h_x || !h_y) return fail(ASP_ERR_INVALID_ARG, "NULL argument or no chunks");
+    // the chunks tile the rows in ascending order; every group spans all columns of the same matrix
+    uint64_t n_rows = 0, n_cols = 0;
+    size_t es = 0;
+    for (int c = 0; c < n_chunks; c++)
+    {
+        const asp_host_chunk &ch = chunks[c];
+        if (!ch.plans || ch.n_plans <= 0) return fail(ASP_ERR_INVALID_ARG, "chunk without plans");
+        if (ch.row_lo != n_rows || ch.row_hi <= ch.row_lo) return fail(ASP_ERR_INVALID_ARG, "the chunks must tile the rows in ascending order");
+        GroupShape g;
+        asp_status gs = group_shape(ch.plans, ch.n_plans, &g);
+        if (gs != ASP_OK) return gs;
+        if (g.n_rows != ch.row_hi - ch.row_lo) return fail(ASP_ERR_INVALID_ARG, "a chunk's plan group has another number of rows than the chunk");
+        if (c == 0)
+        {
+            n_cols = g.n_cols;
+            es = g.es;
+        }
+        else if (g.n_cols != n_cols || g.es != es) return fail(ASP_ERR_INVALID_ARG, "the chunks belong to different matrices");
+        if (ch.col_hi == 0 || ch.col_hi > n_cols) return fail(ASP_ERR_INVALID_ARG, "col_hi outside the matrix");
+        n_rows = ch.row_hi;
+    }
+    ASP_ON_DEVICE(ctx);
+    asp_status st = ensure_xy(ctx, n_cols * es, n_rows * es);
+    if (st != ASP_OK) return st;
+    if (!ctx->h2d) ASP_CUDA(cudaStreamCreateWithFlags(&ctx->h2d, cudaStreamNonBlocking));
+    if (!ctx->d2h) ASP_CUDA(cudaStreamCreateWithFlags(&ctx->d2h, cudaStreamNonBlocking));
+    while (ctx->pipe_events.size() < 2 * (size_t)n_chunks + 1)
+    {
+        cudaEvent_t e = nullptr;
+        ASP_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        ctx->pipe_events.push_back(e);
+    }
+    // whatever ran on the context's stream before (an earlier SpMV reading x, writing y) is finished first
+    cudaEvent_t start = ctx->pipe_events[2 * (size_t)n_chunks];
+    ASP_CUDA(cudaEventRecord(start, ctx->stream));
+    ASP_CUDA(cudaStreamWaitEvent(ctx->h2d, start, 0));
+    uint64_t uploaded = 0; // x[0, uploaded) is on its way to the device
+    for (int c = 0; c < n_chunks; c++)
+    {
+        const asp_host_chunk &ch = chunks[c];
+        cudaEvent_t x_in = ctx->pipe_events[2 * (size_t)c], y_done = ctx->pipe_events[2 * (size_t)c + 1];
+        if (ch.col_hi > uploaded)
+        {
+            ASP_CUDA(cudaMemcpyAsync((unsigned char *)ctx->x + uploaded * es, (const unsigned char *)h_x + uploaded * es, (ch.col_hi - uploaded) * es,
+                                     cudaMemcpyHostToDevice, ctx->h2d));
+            uploaded = ch.col_hi;
+            ASP_CUDA(cudaEventRecord(x_in, ctx->h2d));
+            ASP_CUDA(cudaStreamWaitEvent(ctx->stream, x_in, 0));
+        }
+        unsigned char *y = (unsigned char *)ctx->y + ch.row_lo * es;
+        st = asp_spmv(ctx, ch.plans, ch.n_plans, ctx->x, y, 1);
+        if (st != ASP_OK) break;
+        ASP_CUDA(cudaEventRecord(y_done, ctx->stream));
+        ASP_CUDA(cudaStreamWaitEvent(ctx->d2h, y_done, 0));
+        ASP_CUDA(cudaMemcpyAsync((unsigned char *)h_y + ch.row_lo * es, y, (ch.row_hi - ch.row_lo) * es, cudaMemcpyDeviceToHost, ctx->d2h));
+    }
+    // nothing is left in flight when the call returns, also after an error
+    cudaError_t e1 = cudaStreamSynchronize(ctx->h2d), e2 = cudaStreamSynchronize(ctx->stream), e3 = cudaStreamSynchronize(ctx->d2h);
+    if (st != ASP_OK) return st;
+    if (e1 != cudaSuccess) return cuda_fail(e1, "host-to-device copies");
+    if (e2 != cudaSuccess) return cuda_fail(e2, "kernels");
+    if (e3 != cudaSuccess) return cuda_fail(e3, "device-to-host copies");
     return ASP_OK;
 }
 

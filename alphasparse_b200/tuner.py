@@ -179,3 +179,24 @@ def build(ctx: capi.Context, m: CsrMatrix, desc: dict):
     cm.close()
     hm.close()
     return fmt, group
+
+
+def build_row_chunks(ctx: capi.Context, m: CsrMatrix, desc: dict, n_chunks: int, align: int = 1):
+    """The matrix cut into `n_chunks` row chunks of about equal size (boundaries at multiples of `align`), each lowered
+    and uploaded on its own with the graph `desc` and global column indices: what asp_spmv_host_pipelined and the
+    sharded loop take. Returns [(Format, PlanGroup, first row, end row, 1 + the largest column the chunk reads)]."""
+    import numpy as np
+
+    step = -(-m.n_rows // n_chunks)
+    step = -(-step // align) * align
+    out = []
+    lo = 0
+    while lo < m.n_rows:
+        hi = min(m.n_rows, lo + step)
+        sub = m.row_slice(lo, hi)
+        if sub.nnz == 0:
+            raise ValueError(f"rows [{lo}, {hi}) have no non-zeros: cut the chunks differently")
+        fmt, group = build(ctx, sub, desc)
+        out.append((fmt, group, lo, hi, int(np.max(sub.indices)) + 1))
+        lo = hi
+    return out

@@ -321,8 +321,54 @@ def run_single(ctx, name: str, graph_desc, peak: float, log=None, searched=None)
            "traffic": profiled_traffic(name, graph_desc), "parity_max_rel_err": parity, "reps_per_batch": reps, "batches_ms": [round(b, 5) for b in batches],
            "padding_rate": round(max(fmt.padding_rate(i) for i in range(fmt.n_subs)), 4), "format_MB": round(group.format_bytes() / 1e6, 1),
            "generate_s": round(gen_s, 1), "build_s": round(build_s, 1), "trials": len(trials)}
+    if name.split("_")[0] in ("c2", "c4") and "_reference_" not in name:
+        try:
+            out["host_to_host"] = host_to_host(ctx, m, x, group, graph_desc, y_ref, scale)
+        except Exception as e:  # an extra: never takes the configuration's line down
+            out["host_to_host"] = {"error": repr(e)[:200]}
     keep = {"m": m, "x": x, "fmt": fmt, "group": group, "dx": dx, "dy": dy, "stream": stream, "zero_y": zero_y}
     return out, keep
+
+
+def host_to_host(ctx, m, x, group, graph_desc, y_ref, scale, n_chunks: int = 16):
+    """One SpMV with x and y in pinned HOST memory, through the plain call (copy in, kernel, copy out in series:
+    asp_spmv_host) and through the pipelined one (row chunks, x as a growing prefix, y leaving chunk by chunk:
+    asp_spmv_host_pipelined); milliseconds per call, median of 7."""
+    import torch
+
+    from alphasparse_b200 import capi, tuner
+
+    rd = oracle()
+    hx = torch.from_numpy(np.ascontiguousarray(x)).pin_memory()
+    hy = torch.empty(m.n_rows, dtype=hx.dtype).pin_memory()
+
+    def med(fn):
+        ts = []
+        for _ in range(9):
+            t0 = time.perf_counter()
+            fn()
+            ts.append((time.perf_counter() - t0) * 1e3)
+        return float(np.median(ts[2:]))
+
+    L = capi.lib()
+    import ctypes as C
+
+    plain = med(lambda: capi.check(L.asp_spmv_host(ctx.handle, group._plans, group.n, C.c_void_p(hx.data_ptr()), C.c_void_p(hy.data_ptr()))))
+    err_plain = rd.rel_err(hy.numpy(), y_ref, scale)
+    chunks = tuner.build_row_chunks(ctx, m, graph_desc, n_chunks, align=96)
+    try:
+        arg = [(g, lo, hi, ch) for _, g, lo, hi, ch in chunks]
+        hy.fill_(0)
+        piped = med(lambda: capi.spmv_host_pipelined(ctx, arg, hx.data_ptr(), hy.data_ptr()))
+        err_piped = rd.rel_err(hy.numpy(), y_ref, scale)
+    finally:
+        for f, g, *_ in chunks:
+            g.close()
+            f.close()
+    es = hx.element_size()
+    return {"ms_plain_call": plain, "ms_pipelined_call": piped, "row_chunks": len(chunks), "parity_plain": err_plain, "parity_pipelined": err_piped,
+            "h2d_bytes": int(m.n_cols * es), "d2h_bytes": int(m.n_rows * es),
+            "note": "x and y in pinned host memory; one direction of PCIe moves x or y in bytes / bandwidth, the plain call pays both in series"}
 
 
 def release(keep):
@@ -644,7 +690,8 @@ def run_one_config(args, rank, world, local_rank, dist):
                        "rows": m.n_rows, "nnz": m.nnz, "graph": out["graph"], "l2": "inputs larger than L2 (format arrays %.0f MB)" % out["format_MB"],
                        "search_s": round(search_s, 2), "trials": out["trials"], "padding_rate": out["padding_rate"],
                        "ms_per_spmv_median_of_batches": ms_med, "reps_per_batch": reps, "batches_ms": [round(b, 5) for b in batches],
-                       **({"us_per_spmv_from_a_cuda_graph_of_100": graph_us} if graph_us is not None else {})},
+                       **({"us_per_spmv_from_a_cuda_graph_of_100": graph_us} if graph_us is not None else {}),
+                       **({"host_to_host": out["host_to_host"]} if "host_to_host" in out else {})},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": profiled_traffic(args.workload, out["graph"]), "peak_kind": peak_kind, "algorithmic_bytes": b_alg,
                          "frac_median_of_batches": b_alg / (ms_med * 1e-3) * 1e-9 / peak,

@@ -220,6 +220,25 @@ asp_status asp_spmv(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const voi
  * reference's a.out run (host arrays in, host y out) without the text files. */
 asp_status asp_spmv_host(asp_ctx *ctx, asp_plan *const *plans, int n_plans, const void *h_x, void *h_y);
 
+/* asp_spmv_host for matrices whose rows read a bounded band of columns (stencils, finite elements in a
+ * band-reducing numbering): the rows are cut into chunks, each with its own plan group built over ALL columns
+ * (global column indices, n_rows = the chunk's rows), and chunk k declares col_hi, an exclusive upper bound of
+ * the columns its rows read. x is uploaded as a growing prefix: chunk k's kernel starts as soon as x[0, col_hi)
+ * is on the device, and its rows of y leave for the host while the next chunk's part of x is still arriving, on
+ * three streams (copy in, kernels, copy out). With h_x and h_y in pinned memory a host-to-host SpMV then costs
+ * about one PCIe direction instead of two in series. A wrong col_hi makes a kernel read entries of x that are not
+ * there yet (stale values of an earlier call): declare the maximum column + 1, or n_cols when in doubt. The
+ * chunks must tile [0, n_rows) in ascending order. Returns when y is complete. No counterpart in the reference
+ * (its generated program copies x in, runs, copies y out: code_builder.cc:2119-2129, 1534-1557). */
+typedef struct
+{
+    asp_plan *const *plans;
+    int n_plans;
+    uint64_t row_lo, row_hi; /* rows [row_lo, row_hi) of the matrix */
+    uint64_t col_hi;         /* every column these rows read is < col_hi */
+} asp_host_chunk;
+asp_status asp_spmv_host_pipelined(asp_ctx *ctx, const asp_host_chunk *chunks, int n_chunks, const void *h_x, void *h_y);
+
 /* No counterpart in the reference. asp_spmv_host for callers that must not trigger a device
  * allocation (a solver whose own pool owns all device memory; a loop that cannot afford the
  * device-wide synchronisation of cudaMalloc / cudaFree): x and y are staged in a fixed device

@@ -68,3 +68,4 @@ def test_argument_errors_of_the_multi_gpu_entry_points_need_no_device():
     assert L.asp_dist_spmv_iter(None, p, None, None, 1, None) == 1
     assert L.asp_dist_status(None, None) == 1
     L.asp_dist_destroy(None)
+    assert L.asp_spmv_host_pipelined(None, None, 0, p, p) == 1
