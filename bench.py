@@ -323,11 +323,14 @@ def run_single(ctx, name: str, graph_desc, peak: float, log=None, searched=None)
            "generate_s": round(gen_s, 1), "build_s": round(build_s, 1), "trials": len(trials)}
     if name.split("_")[0] in ("c2", "c4") and "_reference_" not in name:
         try:
-            out["host_to_host"] = host_to_host(ctx, m, x, group, graph_desc, y_ref, scale)
+            out["host_to_host"] = host_to_host(ctx, m, x, group, graph_desc, y_ref, scale, HOST_CHUNKS)
         except Exception as e:  # an extra: never takes the configuration's line down
             out["host_to_host"] = {"error": repr(e)[:200]}
     keep = {"m": m, "x": x, "fmt": fmt, "group": group, "dx": dx, "dy": dy, "stream": stream, "zero_y": zero_y}
     return out, keep
+
+
+HOST_CHUNKS = 4  # measured: 4 chunks 0.96 ms, 8 chunks 0.98, 16 chunks 1.14 (c2; per-chunk copies of 2 MB are latency-bound)
 
 
 def host_to_host(ctx, m, x, group, graph_desc, y_ref, scale, n_chunks: int = 16):
@@ -728,6 +731,7 @@ def main():
                          "chunk, or by NCCL (both multicast modes fall back to allgather where symmetric memory has no multicast address)")
     ap.add_argument("--relabel", default="indegree", choices=["indegree", "none"], help="c5: renumber the vertices by column count, hottest first, and run the loop on "
                     "P A P^T (x permuted on the way in, the result on the way out, inside every step): the hot part of x becomes contiguous")
+    ap.add_argument("--host-chunks", type=int, default=0, help="c2 / c4: row chunks of the pipelined host-to-host call (0: default)")
     ap.add_argument("--loop", default="native", choices=["native", "python"], help="c5: who enqueues the repeated SpMVs: the native loop behind the C ABI "
                     "(asp_dist_spmv_iter; multicast exchange and single GPU) or the Python one (every exchange form)")
     ap.add_argument("--balance", default="4", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
@@ -755,6 +759,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
+    if args.host_chunks > 0:
+        global HOST_CHUNKS
+        HOST_CHUNKS = args.host_chunks
     if args.steps is None:
         args.steps = 5 if args.workload == "c5" else 200
     if args.warmup is None:
