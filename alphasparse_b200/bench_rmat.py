@@ -61,7 +61,9 @@ def run(args, rank: int, world: int, local_rank: int, dist, log, check_fn=None):
     # "nnz": equal non-zeros per rank; "bytes": equal algorithmic bytes, i.e. a row weighs as much
     # as one non-zero (4 B of y + 4 B of row structure against 4 B value + 4 B index); a number w:
     # a row weighs w non-zeros
-    row_weight = {"nnz": 0.0, "bytes": 1.0}.get(args.balance)
+    import math
+
+    row_weight = {"nnz": 0.0, "bytes": 1.0, "auto": 3.0 + 1.5 * math.log2(max(world, 2) / 2.0)}.get(args.balance)
     if row_weight is None:
         row_weight = float(args.balance)
     # (weights are scaled by 8 so that fractional row weights survive the integer prefix sums; rows

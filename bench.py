@@ -734,8 +734,9 @@ def main():
     ap.add_argument("--host-chunks", type=int, default=0, help="c2 / c4: row chunks of the pipelined host-to-host call (0: default)")
     ap.add_argument("--loop", default="native", choices=["native", "python"], help="c5: who enqueues the repeated SpMVs: the native loop behind the C ABI "
                     "(asp_dist_spmv_iter; multicast exchange and single GPU) or the Python one (every exchange form)")
-    ap.add_argument("--balance", default="6", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
-                    "or a number w (a row with non-zeros weighs w non-zeros; measured: 8 GPUs 0.55 ms per SpMV with 6 against 0.65 with 4, "
+    ap.add_argument("--balance", default="auto", help="c5: what the row blocks of the ranks have equal amounts of: nnz, bytes (a row weighs one non-zero), "
+                    "a number w (a row with non-zeros weighs w non-zeros), or auto (w = 3 + 1.5 log2(N / 2): 3 at 2 GPUs, 4.5 at 4, 6 at 8: the more ranks, the "
+                    "larger the share of the exchange that the rank with the sparse tail carries, and the more slack it needs; measured: 8 GPUs 0.55 ms per SpMV with 6 against 0.65 with 4, "
                     "4 GPUs 1.03 with 5 against 1.08 with 8: the rank that owns the sparse tail also has the large exchange and must not be the slowest)")
     ap.add_argument("--tlb", type=int, default=0, help="c5: non-zeros per thread of the CSR5-like format (default 32)")
     ap.add_argument("--sort", default="auto", choices=["auto", "yes", "no"], help="c5: put the rows without non-zeros last (a one-bin coarse sort) so that the format drops them (auto = yes); "
