@@ -3,13 +3,16 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c1|c2|c3|c4|c4s] [--impl reference]
 
 Default workload (every N, N = 1 included): the sharded graph configuration, R-MAT scale 26
-(67,108,864 rows, ~1.06e9 non-zeros, fp32) generated on the GPUs, nnz-balanced row blocks, x
+(67,108,864 rows, ~1.06e9 non-zeros, fp32) generated on the GPUs, cost-balanced row blocks, x
 replicated, ONE STEP = 100 repeated SpMVs (x <- A x). Strong scaling: the matrix is the same at every
-N. With N > 1 every rank cuts its block into row chunks and stores each finished chunk once through an
-NVLink multicast address (NVSwitch replicates it) on a second stream, under the next chunk's kernel; one
-bounded-wait barrier kernel per SpMV orders the ranks (--exchange: the other forms that were measured).
-At N = 1 the line also carries `configs`: the four single-GPU configurations (c1..c4) replayed with the
-graphs the search picked for them, each with its own time, roofline fraction and parity.
+N. The loop runs on P A P^T, the vertices renumbered by column count (--relabel): a step takes x0 in the
+matrix's own numbering, permutes it in, iterates, and permutes the result out. With N > 1 every rank
+cuts its block into row chunks and stores each finished chunk once through an NVLink multicast address
+(NVSwitch replicates it) on a second stream, under the next chunk's kernel; one bounded-wait barrier
+kernel per SpMV orders the ranks (--exchange: the other forms that were measured); the loop is enqueued
+by one native call (asp_dist_spmv_iter, --loop). At N = 1 the line also carries `configs`: the
+single-GPU configurations (c1..c4) replayed with the graphs the search picked for them, each with its
+own time, roofline fraction and parity (c2 and c4 also with the host-to-host calls, plain and pipelined).
 
 --workload c1|c2|c3|c4|c4s runs one single-GPU configuration as the main line (a step is one SpMV);
 the graph is searched on the GPU (asp_search_gpu) unless --graph / --spec fixes it.
