@@ -89,3 +89,30 @@ def test_host_operator_renumbers_a_matrix_and_the_lowered_format_gives_the_permu
         cm.relabel_by_column_count()
     cm.close()
     hm.close()
+
+
+def test_host_operator_on_random_matrices_with_empty_rows_and_unused_columns():
+    """Drawn matrices (fp64, rows without non-zeros, columns nobody reads, one long row): labels are a permutation,
+    P A P^T has the same multiset of values per relabelled row, and the product commutes with the permutation."""
+    rng = np.random.default_rng(11)
+    for trial in range(6):
+        n = int(rng.integers(40, 400))
+        lens = rng.integers(0, 7, size=n)
+        lens[rng.integers(0, n)] = n // 2  # one long row
+        lens[rng.integers(0, n, size=n // 5)] = 0
+        if lens.sum() == 0:
+            lens[0] = 3
+        m, x = M.from_row_lengths(lens, n, seed=100 + trial, dtype=np.float64)
+        hm = Matrix.from_csr(m)
+        m2, labels, n_active = hm.relabel_by_column_count(True)
+        assert sorted(labels.tolist()) == list(range(n)) and n_active == int((lens > 0).sum())
+        fmt = m2.execute("dense compress\nsub all tlb_nnz 4\nsub all template K9")
+        xp = np.zeros(n)
+        xp[labels] = x
+        yp = plan_interp.interpret(NativeManifest(fmt, n), xp)
+        y_ref, scale = refdump.csr_ref(m, x)
+        assert refdump.rel_err(yp[labels], y_ref, scale) <= 1e-12
+        assert np.all(yp[n_active:] == 0)
+        fmt.close()
+        m2.close()
+        hm.close()
