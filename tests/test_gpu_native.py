@@ -208,3 +208,23 @@ def test_pipelined_host_spmv_matches_the_oracle(asp_ctx, case):
     for f, g, *_ in chunks:
         g.close()
         f.close()
+
+
+@pytest.mark.parametrize("templ", ["K9", "K10"])
+@pytest.mark.parametrize("s", [1, 2, 3, 4, 5, 6, 7, 8, 16, 32])
+def test_csr5_like_small_exhaustive_on_the_gpu(asp_ctx, templ, s):
+    """The small shapes of the CPU suite's exhaustive test through the kernels (specialised for TLB size 4 / 8 / 16 / 32,
+    generic otherwise; column indices fit 16 bits here, so sizes 4 .. 32 also run the generic kernel's narrow-column
+    path), and a wide copy of each shape (more than 65536 columns) that takes the specialised kernels."""
+    shapes = [
+        [1, s, s + 1, 0, 2 * s, 32 * s, 32 * s + 1, 0, 0, 3, 70 * s, 1, 31 * s, s - 1 if s > 1 else 1],
+        [70 * s],
+        [0, 0, 5, 0, 33 * s, 0],
+        list(range(1, 40)),
+        [64 * s] * 3 + [1] * 50,
+    ]
+    for n_cols in (70 * 32 + 7, 70000):
+        for k, lens in enumerate(shapes):
+            m, x = M.from_row_lengths(np.array(lens, dtype=np.int64), n_cols, seed=50 + k, dtype=np.float32)
+            for dense in ("dense compress", "dense sort 1\ndense compress"):
+                run(asp_ctx, m, x, f"{dense}\nsub all tlb_nnz {s}\nsub all template {templ}", f"{templ} s={s} shape {k} cols {n_cols} {dense!r}")

@@ -89,3 +89,25 @@ def test_explicit_row_division_with_a_template_per_strip():
     for bad in ("dense rowdiv 0 10\ndense compress", "dense rowdiv 500 400\ndense compress", "dense rowdiv 900\ndense compress"):
         with pytest.raises(Exception):
             hm.dense(bad)
+
+
+@pytest.mark.parametrize("templ", ["K9", "K10"])
+@pytest.mark.parametrize("s", [1, 2, 3, 4, 5, 6, 7, 8, 16, 32])
+def test_csr5_like_small_exhaustive(templ, s):
+    """Small cases for the two CSR5-like templates at every TLB size 1..8 (and 16, 32): rows of 1 .. 70 threads' worth of
+    non-zeros, rows that end exactly on a thread or warp boundary, rows without non-zeros between them, a matrix that
+    is one long row. Where the reference's emitted kernels store a thread's partial instead of the row total
+    (unaligned_warp_reduce_same_TLB_size_op.cc:1152-1250), the arrays walked the way the native kernels walk them must
+    give the CSR result."""
+    n_cols = 70 * 32 + 7
+    shapes = [
+        [1, s, s + 1, 0, 2 * s, 32 * s, 32 * s + 1, 0, 0, 3, 70 * s, 1, 31 * s, s - 1 if s > 1 else 1],
+        [70 * s],
+        [0, 0, 5, 0, 33 * s, 0],
+        list(range(1, 40)),
+        [64 * s] * 3 + [1] * 50,
+    ]
+    for k, lens in enumerate(shapes):
+        m, x = M.from_row_lengths(np.array(lens, dtype=np.int64), n_cols, seed=50 + k, dtype=np.float64)
+        for dense in ("dense compress", "dense sort 1\ndense compress"):
+            check(m, x, f"{dense}\nsub all tlb_nnz {s}\nsub all template {templ}", f"{templ} s={s} shape {k} {dense!r}")
