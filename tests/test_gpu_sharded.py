@@ -215,3 +215,27 @@ def test_graph_workload_with_and_without_relabelling_gives_the_same_vector():
     a, b = finals["indegree"].cpu().numpy().astype(np.float64), finals["none"].cpu().numpy().astype(np.float64)
     assert np.max(np.abs(a - ref)) <= 1e-4 * np.max(np.abs(ref))
     assert np.max(np.abs(b - ref)) <= 1e-4 * np.max(np.abs(ref))
+
+
+def test_twenty_iterations_of_a_rescaled_graph_match_the_oracle(asp_ctx):
+    """x <- A x twenty times on an R-MAT block whose values are scaled so that x neither overflows nor dies out
+    (the bench's own values make x overflow after ~40 SpMVs, so its parity is checked on the first one): the native
+    loop's last vector against twenty CPU SpMVs, each rounded to fp32 as the GPU rounds it."""
+    m, x = M.rmat(13, 16, seed=4)
+    m.values *= 1.0 / 8.0
+    keep = []
+    chunks = _chunks(asp_ctx, m, 3, keep)
+    stream = torch.cuda.ExternalStream(asp_ctx.stream)
+    with torch.cuda.stream(stream):
+        sh = ShardedSpmv(None, [0, m.n_rows], 0, 1, torch.float32, "cuda", chunks=chunks)
+        assert sh.use_native_loop(asp_ctx, [g for _, g in keep])
+        x0 = torch.from_numpy(x).cuda()
+        xf = sh.iterate(x0, 20, sh.new_vector(), sh.new_vector())
+        torch.cuda.synchronize()
+    ref = _reference_iterations(m, x, 20)
+    got = xf.cpu().numpy().astype(np.float64)
+    assert np.isfinite(ref).all() and np.max(np.abs(ref)) > 1e-20
+    assert np.max(np.abs(got - ref)) <= 2e-4 * np.max(np.abs(ref))
+    for f, g in keep:
+        g.close()
+        f.close()
