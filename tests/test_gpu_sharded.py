@@ -239,3 +239,36 @@ def test_twenty_iterations_of_a_rescaled_graph_match_the_oracle(asp_ctx):
     for f, g in keep:
         g.close()
         f.close()
+
+
+def test_native_loop_clears_a_chunk_without_non_zeros(asp_ctx):
+    """asp_dist_* straight through the binding: two chunks with plan groups and one without any non-zeros (no plan
+    group: its rows are cleared every SpMV, also when the buffer held something else before)."""
+    n = 3000
+    lens = np.concatenate([np.random.default_rng(5).integers(1, 9, size=2000), np.zeros(400, dtype=np.int64), np.full(600, 3)])
+    m, x = M.from_row_lengths(lens, n, seed=9)
+    m.values *= 0.1
+    parts = [(0, 2000), (2000, 2400), (2400, 3000)]
+    built = [tuner.build(asp_ctx, m.row_slice(lo, hi), bench_rmat.graph_with_tlb_size(8, sort=False)) if m.indptr[hi] > m.indptr[lo] else (None, None) for lo, hi in parts]
+    assert built[1] == (None, None)
+    loop = capi.DistLoop(asp_ctx, [(g, lo, hi) for (f, g), (lo, hi) in zip(built, parts)], n)
+    stream = torch.cuda.ExternalStream(asp_ctx.stream)
+    with torch.cuda.stream(stream):
+        x0 = torch.from_numpy(x).cuda()
+        a, b = torch.full((n,), 7.0, device="cuda"), torch.full((n,), -3.0, device="cuda")  # dirty buffers
+        last = loop.iterate(x0.data_ptr(), [a.data_ptr(), b.data_ptr()], None, 3)
+        loop.status()
+        torch.cuda.synchronize()
+    assert last == 0
+    ref = _reference_iterations(m, x, 3)
+    got = a.cpu().numpy().astype(np.float64)
+    assert np.all(got[2000:2400] == 0)
+    assert np.max(np.abs(got - ref)) <= 1e-4 * np.max(np.abs(ref))
+    # the same vector as x and y is refused
+    with pytest.raises(capi.AspError):
+        loop.spmv(a.data_ptr(), a.data_ptr())
+    loop.close()
+    for f, g in built:
+        if g is not None:
+            g.close()
+            f.close()
