@@ -228,3 +228,22 @@ def test_csr5_like_small_exhaustive_on_the_gpu(asp_ctx, templ, s):
             m, x = M.from_row_lengths(np.array(lens, dtype=np.int64), n_cols, seed=50 + k, dtype=np.float32)
             for dense in ("dense compress", "dense sort 1\ndense compress"):
                 run(asp_ctx, m, x, f"{dense}\nsub all tlb_nnz {s}\nsub all template {templ}", f"{templ} s={s} shape {k} cols {n_cols} {dense!r}")
+
+
+def test_renumbered_matrix_runs_like_the_original(asp_ctx):
+    """asp_matrix_relabel_by_column_count, then the ordinary lowering and kernels: y'[labels[v]] is the original y[v],
+    and the rows without non-zeros are the suffix of y' (R-MAT: half of the rows are empty, the hub columns get the
+    low numbers)."""
+    m, x = M.rmat(17, 8, seed=4)
+    hm = Matrix.from_csr(m)
+    m2, labels, n_active = hm.relabel_by_column_count(True)
+    fmt = m2.execute("dense sort 1073741824\ndense compress\nsub all tlb_nnz 32\nsub all template K9")
+    g = fmt.upload(asp_ctx)
+    xp = np.zeros_like(x)
+    xp[labels] = x
+    yp = g.spmv_host(xp)
+    y_ref, scale = refdump.csr_ref(m, x)
+    refdump.assert_y(yp[labels], y_ref, scale, m.values.dtype, "renumbered R-MAT")
+    assert n_active == int((m.row_lengths() > 0).sum()) and np.all(yp[n_active:] == 0)
+    for o in (g, fmt, m2, hm):
+        o.close()
