@@ -200,3 +200,26 @@ def build_row_chunks(ctx: capi.Context, m: CsrMatrix, desc: dict, n_chunks: int,
         out.append((fmt, group, lo, hi, int(np.max(sub.indices)) + 1))
         lo = hi
     return out
+
+
+def write_trials_jsonl(path: str, m: CsrMatrix, trials, peak_gbs: float | None = None, append: bool = False) -> int:
+    """One JSON object per timed point of a search (the reference prints to stdout and keeps ML rows in a CSV,
+    machine_learning_data_set_collector.cc): dense-view graph, sub-matrix, candidate, launch, milliseconds, padding
+    rate, and the derived GFLOP/s, algorithmic GB/s and, with `peak_gbs`, the roofline fraction. Returns the number
+    of lines written."""
+    import json
+
+    b_alg = m.algorithmic_bytes()
+    n = 0
+    with open(path, "a" if append else "w") as fh:
+        for t in trials:
+            rec = {"dense": t.dense, "sub": t.sub, "graph": t.name, "threads": t.launch[0], "row_reduce": t.launch[1], "ms": t.ms,
+                   "padding_rate": t.padding_rate, "rows": m.n_rows, "nnz": m.nnz, "dtype": str(m.values.dtype)}
+            if t.ms > 0:
+                rec["gflops"] = 2.0 * m.nnz / (t.ms * 1e-3) * 1e-9
+                rec["algorithmic_GBs"] = b_alg / (t.ms * 1e-3) * 1e-9
+                if peak_gbs:
+                    rec["roofline_frac"] = rec["algorithmic_GBs"] / peak_gbs
+            fh.write(json.dumps(rec) + "\n")
+            n += 1
+    return n

@@ -157,3 +157,19 @@ def test_interrupted_search_resumes_from_its_checkpoint(tmp_path):
     calls.clear()
     d3, t3, _ = tuner.search_with_timer(m, model, quick=True, checkpoint=ck)
     assert 0 < len(calls) < n_first and d3 == d1 and len(t3) == len(t1)
+
+
+def test_trial_log_is_one_json_object_per_timed_point(tmp_path):
+    import json
+
+    m, _ = M.uniform_random(2000, 12, seed=3)
+    desc, trials, ms = tuner.search_with_timer(m, model_timer())
+    path = str(tmp_path / "trials.jsonl")
+    assert tuner.write_trials_jsonl(path, m, trials, peak_gbs=6455.6) == len(trials)
+    recs = [json.loads(l) for l in open(path)]
+    assert len(recs) == len(trials) and all({"graph", "threads", "ms", "gflops", "algorithmic_GBs", "roofline_frac", "padding_rate"} <= set(r) for r in recs)
+    best = min(recs, key=lambda r: r["ms"])
+    assert best["graph"] == desc["subs"][0]["graph"] and abs(best["ms"] - ms) <= 1e-4 * ms
+    assert abs(best["gflops"] - 2.0 * m.nnz / (best["ms"] * 1e-3) * 1e-9) < 1e-6
+    # appending keeps what is there
+    assert tuner.write_trials_jsonl(path, m, trials[:3], append=True) == 3 and sum(1 for _ in open(path)) == len(trials) + 3
